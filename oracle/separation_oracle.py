@@ -1,0 +1,186 @@
+"""CPU restatement of the reference's cost-volume separation ops.  TEST INFRASTRUCTURE ONLY.
+
+This file is the checker for the CUDA path and the timed CPU baseline; the
+product (``separableflowthesis_b200``) never imports it.  It restates, with
+dense torch CPU tensor algebra, what the reference's five ``MemorySaver.*``
+native ops compute (libs/MemorySaver/src/MemorySaver_cuda.cpp:105-112) in the
+formulation the reference's own dense path uses
+(core/corr.py:251-302 ``CorrBlock.corr_compute`` and core/corr.py:40-165
+``CorrBlock.separate``: matmul -> max/mean over one displacement axis ->
+einsum with the attention weights).
+
+Parity pin: ``tests/golden/make_golden.py`` imports the reference's own
+``CorrBlock`` and ``AlternateCorrBlockSepflow`` (core/corr.py) in a container
+that has the reference checkout, runs them on seeded inputs (with these
+functions plugged under the reference's own ``functions/MemorySaver.py``
+wrappers for the memory-saving block) and stores the outputs; the CPU test
+suite checks this file against those stored vectors.
+
+Conventions (identical to the reference ops):
+  F1   (B, H1, W1, C)   image-1 features, already scaled by 1/sqrt(C) by the caller
+                        (core/corr.py:419)
+  F2   (B, H2, W2, C)   image-2 features of one pyramid level (core/corr.py:422)
+  S[b,i,j,u,v] = sum_c F1[b,i,j,c] * F2[b,u,v,c]   (never stored by the product)
+  MA_u (B, H1, W1, 2, H2): [...,0,u] = max_v S, [...,1,u] = mean_v S
+  MA_v (B, H1, W1, 2, W2): [...,0,v] = max_u S, [...,1,v] = mean_u S
+  AM_u (B, H1, W1, 1, H2) int32 = argmax_v S (lowest v on ties,
+        MemorySaver_kernel_forward.cu:498-507), AM_v likewise over u
+  A_u  (B, H1, W1, Kc, W2), A_v (B, H1, W1, Kc, H2): attention weights
+  C_u  (B, H1, W1, Kc, H2) = sum_v S * A_u ; C_v (B, H1, W1, Kc, W2) = sum_u S * A_v
+        (MemorySaver_kernel_forward.cu:712-726)
+
+Every function works on row chunks of image 1 so that the dense volume of one
+chunk, not of the whole image, is what lives in host memory.
+"""
+from __future__ import annotations
+
+import torch
+
+__all__ = [
+    "corr_volume",
+    "max_avg_forward",
+    "max_argmax_avg_forward",
+    "max_argmax_avg_backward",
+    "compression_forward",
+    "compression_backward",
+    "top2_margins",
+]
+
+
+def _row_chunks(H1: int, W1: int, H2: int, W2: int, budget_elems: int = 1 << 26):
+    """Yield (r0, r1) image-1 row ranges whose dense volume stays under ``budget_elems``."""
+    per_row = max(1, W1 * H2 * W2)
+    step = max(1, budget_elems // per_row)
+    r0 = 0
+    while r0 < H1:
+        yield r0, min(H1, r0 + step)
+        r0 += step
+
+
+def corr_volume(F1: torch.Tensor, F2: torch.Tensor) -> torch.Tensor:
+    """S (B,H1,W1,H2,W2) as in core/corr.py:286-289 (scale already folded into F1)."""
+    B, H1, W1, C = F1.shape
+    _, H2, W2, _ = F2.shape
+    S = torch.matmul(F1.reshape(B, H1 * W1, C), F2.reshape(B, H2 * W2, C).transpose(1, 2))
+    return S.reshape(B, H1, W1, H2, W2)
+
+
+def _first_argmax(S: torch.Tensor, dim: int) -> torch.Tensor:
+    """Index of the maximum along ``dim`` with the LOWEST index winning ties.
+
+    The reference kernel updates on strict ``<`` while scanning upward
+    (MemorySaver_kernel_forward.cu:498-507), hence first occurrence.
+    """
+    m = S.max(dim=dim, keepdim=True).values
+    n = S.shape[dim]
+    shape = [1] * S.dim()
+    shape[dim] = n
+    idx = torch.arange(n, dtype=torch.int64).reshape(shape)
+    cand = torch.where(S == m, idx, torch.full_like(idx, n))
+    return cand.min(dim=dim).values
+
+
+def max_argmax_avg_forward(F1: torch.Tensor, F2: torch.Tensor):
+    """Restates MemorySaver.max_argmax_avg_forward (MemorySaver_cuda.cpp:23-34;
+    kernel MemorySaver_kernel_forward.cu:328-533).  Returns [MA_u, MA_v, AM_u, AM_v]."""
+    B, H1, W1, C = F1.shape
+    _, H2, W2, _ = F2.shape
+    MA_u = F1.new_empty(B, H1, W1, 2, H2)
+    MA_v = F1.new_empty(B, H1, W1, 2, W2)
+    AM_u = torch.empty(B, H1, W1, 1, H2, dtype=torch.int32)
+    AM_v = torch.empty(B, H1, W1, 1, W2, dtype=torch.int32)
+    for r0, r1 in _row_chunks(H1, W1, H2, W2):
+        S = corr_volume(F1[:, r0:r1], F2)
+        MA_u[:, r0:r1, :, 0] = S.max(dim=4).values
+        MA_u[:, r0:r1, :, 1] = S.mean(dim=4)
+        MA_v[:, r0:r1, :, 0] = S.max(dim=3).values
+        MA_v[:, r0:r1, :, 1] = S.mean(dim=3)
+        AM_u[:, r0:r1, :, 0] = _first_argmax(S, 4).to(torch.int32)
+        AM_v[:, r0:r1, :, 0] = _first_argmax(S, 3).to(torch.int32)
+    return [MA_u, MA_v, AM_u, AM_v]
+
+
+def max_avg_forward(F1: torch.Tensor, F2: torch.Tensor):
+    """Restates MemorySaver.max_avg_forward (MemorySaver_cuda.cpp:10-21; kernel
+    MemorySaver_kernel_forward.cu:128-313).  Returns [MA_u, MA_v]."""
+    return max_argmax_avg_forward(F1, F2)[:2]
+
+
+def _maxavg_G(AM_u, AM_v, gMA_u, gMA_v, H2, W2):
+    """Dense gradient of the loss w.r.t. S for a chunk of image-1 rows:
+    one-hot of the argmax times the max-gradient plus the spread mean-gradient
+    (MemorySaver_kernel_max_avg_argmax_backward.cu:200-251)."""
+    B, h, W1 = AM_u.shape[:3]
+    G = gMA_u.new_zeros(B, h, W1, H2, W2)
+    G += (gMA_u[..., 1, :] / W2).unsqueeze(-1)
+    G += (gMA_v[..., 1, :] / H2).unsqueeze(-2)
+    G.scatter_add_(4, AM_u[..., 0, :].to(torch.int64).unsqueeze(-1), gMA_u[..., 0, :].unsqueeze(-1))
+    G.scatter_add_(3, AM_v[..., 0, :].to(torch.int64).unsqueeze(-2), gMA_v[..., 0, :].unsqueeze(-2))
+    return G
+
+
+def max_argmax_avg_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v):
+    """Restates MemorySaver.max_argmax_avg_backward (MemorySaver_cuda.cpp:55-78;
+    kernel MemorySaver_kernel_max_avg_argmax_backward.cu:47-317).  Returns [gF1, gF2]."""
+    B, H1, W1, C = F1.shape
+    _, H2, W2, _ = F2.shape
+    gF1 = torch.zeros_like(F1)
+    gF2 = torch.zeros_like(F2)
+    F2f = F2.reshape(B, H2 * W2, C)
+    for r0, r1 in _row_chunks(H1, W1, H2, W2):
+        G = _maxavg_G(AM_u[:, r0:r1], AM_v[:, r0:r1], gMA_u[:, r0:r1], gMA_v[:, r0:r1], H2, W2)
+        Gf = G.reshape(B, (r1 - r0) * W1, H2 * W2)
+        gF1[:, r0:r1] = torch.matmul(Gf, F2f).reshape(B, r1 - r0, W1, C)
+        gF2 += torch.matmul(Gf.transpose(1, 2), F1[:, r0:r1].reshape(B, -1, C)).reshape(B, H2, W2, C)
+    return [gF1, gF2]
+
+
+def compression_forward(F1, F2, A_u, A_v):
+    """Restates MemorySaver.compression_forward for ANY Kc (MemorySaver_cuda.cpp:36-53).
+    The reference kernel hard-codes Kc=2 (MemorySaver_kernel_forward.cu:20,1061); for other
+    Kc the definition is the dense einsum of core/corr.py:128,140.  Returns [C_u, C_v]."""
+    B, H1, W1, C = F1.shape
+    _, H2, W2, _ = F2.shape
+    Kc = A_u.shape[3]
+    C_u = F1.new_empty(B, H1, W1, Kc, H2)
+    C_v = F1.new_empty(B, H1, W1, Kc, W2)
+    for r0, r1 in _row_chunks(H1, W1, H2, W2):
+        S = corr_volume(F1[:, r0:r1], F2)
+        C_u[:, r0:r1] = torch.einsum("bijuv,bijkv->bijku", S, A_u[:, r0:r1])
+        C_v[:, r0:r1] = torch.einsum("bijuv,bijku->bijkv", S, A_v[:, r0:r1])
+    return [C_u, C_v]
+
+
+def compression_backward(F1, F2, A_u, A_v, gC_u, gC_v):
+    """Restates MemorySaver.compression_backward (MemorySaver_cuda.cpp:80-103; kernel
+    MemorySaver_kernel_compression_backward.cu:417-508).  Returns [gF1, gF2, gA_u, gA_v]."""
+    B, H1, W1, C = F1.shape
+    _, H2, W2, _ = F2.shape
+    gF1 = torch.zeros_like(F1)
+    gF2 = torch.zeros_like(F2)
+    gA_u = torch.empty_like(A_u)
+    gA_v = torch.empty_like(A_v)
+    F2f = F2.reshape(B, H2 * W2, C)
+    for r0, r1 in _row_chunks(H1, W1, H2, W2):
+        S = corr_volume(F1[:, r0:r1], F2)
+        gA_u[:, r0:r1] = torch.einsum("bijuv,bijku->bijkv", S, gC_u[:, r0:r1])
+        gA_v[:, r0:r1] = torch.einsum("bijuv,bijkv->bijku", S, gC_v[:, r0:r1])
+        G = torch.einsum("bijku,bijkv->bijuv", gC_u[:, r0:r1], A_u[:, r0:r1])
+        G = G + torch.einsum("bijku,bijkv->bijuv", A_v[:, r0:r1], gC_v[:, r0:r1])
+        Gf = G.reshape(B, (r1 - r0) * W1, H2 * W2)
+        gF1[:, r0:r1] = torch.matmul(Gf, F2f).reshape(B, r1 - r0, W1, C)
+        gF2 += torch.matmul(Gf.transpose(1, 2), F1[:, r0:r1].reshape(B, -1, C)).reshape(B, H2, W2, C)
+    return [gF1, gF2, gA_u, gA_v]
+
+
+def top2_margins(F1: torch.Tensor, F2: torch.Tensor):
+    """Gap between the largest and second-largest entry of S along v (per (p,u)) and
+    along u (per (p,v)), computed in float64.  An argmax is required to be bit-exact only
+    where this gap exceeds the operand-rounding tolerance of the device path."""
+    S = corr_volume(F1.double(), F2.double())
+    def gap(dim):
+        if S.shape[dim] < 2:
+            return torch.full(S.max(dim=dim).values.shape, float("inf"), dtype=torch.float64)
+        t = S.topk(2, dim=dim).values
+        return t.select(dim, 0) - t.select(dim, 1)
+    return gap(4), gap(3)
