@@ -1,0 +1,110 @@
+/*
+ * sepflow_b200 -- C ABI of the B200 (sm_100a) cost-volume separation library.
+ *
+ * Drop-in boundary for the native ops of the reference's memory-saving separation path: each entry
+ * point below does what one function of the reference's pybind11 module `MemorySaver` does
+ * (libs/MemorySaver/src/MemorySaver_cuda.cpp:105-112), but takes plain device pointers and sizes
+ * and writes into caller-provided output buffers.
+ *
+ * Conventions shared by all entry points
+ *   - All tensors are contiguous row-major fp32 (argmax tensors int32) in device memory, 16-byte aligned.
+ *       F1  (B, H1, W1, C)  image-1 features, already multiplied by 1/sqrt(C) by the caller (core/corr.py:419)
+ *       F2  (B, H2, W2, C)  image-2 features of one pyramid level (core/corr.py:422)
+ *     With S[b,i,j,u,v] = sum_c F1[b,i,j,c] * F2[b,u,v,c] (never stored):
+ *       MA_u (B,H1,W1,2,H2)  [..,0,u] = max_v S   [..,1,u] = mean_v S
+ *       MA_v (B,H1,W1,2,W2)  [..,0,v] = max_u S   [..,1,v] = mean_u S
+ *       AM_u (B,H1,W1,1,H2), AM_v (B,H1,W1,1,W2)  int32 argmax, lowest index on ties
+ *       A_u  (B,H1,W1,Kc,W2), A_v (B,H1,W1,Kc,H2) attention weights
+ *       C_u  (B,H1,W1,Kc,H2) = sum_v S*A_u,  C_v (B,H1,W1,Kc,W2) = sum_u S*A_v
+ *   - Outputs need no initialisation by the caller (the reference pre-fills with -inf / 0,
+ *     MemorySaver_kernel_forward.cu:916-927; here every element is written by the kernels).
+ *   - Limits: C a multiple of 4 with 4 <= C <= 256; any H1, W1, H2, W2, Kc >= 1 (Kc >= 0 is not
+ *     needed by the max/avg entry points and ignored there).
+ *   - `workspace` is scratch device memory of at least sfb_workspace_bytes(op, shape) bytes, 256-byte
+ *     aligned; its first word is a device status word (0 = ok) that bounded device-side waits set
+ *     instead of hanging.  Calls that share a workspace must be ordered on one stream.
+ *   - `stream` is a cudaStream_t (NULL = legacy default stream).  Work is enqueued, not synchronised.
+ *   - Return value: SFB_OK or an error code; sfb_last_error() has the message of this thread's last error.
+ *   - The contraction runs on the tensor cores with TF32 operands (round-to-nearest) and FP32
+ *     accumulation; the reference kernels use FP32 FMAs.
+ */
+#ifndef SEPFLOW_B200_H_
+#define SEPFLOW_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct sfb_shape {
+  int32_t B, H1, W1, H2, W2, C, Kc;
+} sfb_shape;
+
+enum {
+  SFB_OK = 0,
+  SFB_ERR_INVALID_ARGUMENT = 1,    /* null pointer, misaligned pointer, non-positive size */
+  SFB_ERR_UNSUPPORTED_SHAPE = 2,   /* C outside the supported range */
+  SFB_ERR_WORKSPACE_TOO_SMALL = 3,
+  SFB_ERR_CUDA = 4,                /* a CUDA runtime / driver call failed */
+  SFB_ERR_DEVICE_TIMEOUT = 5       /* sfb_device_status: a bounded device-side wait gave up */
+};
+
+enum {
+  SFB_OP_MAX_AVG_FORWARD = 0,          /* also covers the argmax variant */
+  SFB_OP_COMPRESSION_FORWARD = 1,
+  SFB_OP_MAX_ARGMAX_AVG_BACKWARD = 2,
+  SFB_OP_COMPRESSION_BACKWARD = 3,
+  SFB_OP_CORR_VOLUME = 4
+};
+
+/* Scratch bytes an op needs for `shape` (0 if the shape is invalid). */
+size_t sfb_workspace_bytes(int op, const sfb_shape* shape);
+
+/* Replaces MemorySaver.max_avg_forward (MemorySaver_cuda.cpp:10-21 -> MemorySaver_kernel_forward.cu:901-949). */
+int sfb_max_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, const sfb_shape* shape,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces MemorySaver.max_argmax_avg_forward (MemorySaver_cuda.cpp:23-34 -> MemorySaver_kernel_forward.cu:962-1016). */
+int sfb_max_argmax_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u,
+                               int32_t* AM_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                               void* stream);
+
+/* Replaces MemorySaver.max_argmax_avg_backward (MemorySaver_cuda.cpp:55-78 ->
+ * MemorySaver_kernel_max_avg_argmax_backward.cu:1198-1221).  gF1 (B,H1,W1,C), gF2 (B,H2,W2,C). */
+int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
+                                const float* gMA_u, const float* gMA_v, float* gF1, float* gF2,
+                                const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces MemorySaver.compression_forward (MemorySaver_cuda.cpp:36-53 -> MemorySaver_kernel_forward.cu:1029-1074)
+ * for any Kc >= 1 (the reference kernel is compiled for Kc = 2 only, MemorySaver_kernel_forward.cu:20,1061). */
+int sfb_compression_forward(const float* F1, const float* F2, const float* A_u, const float* A_v, float* C_u,
+                            float* C_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* Replaces MemorySaver.compression_backward (MemorySaver_cuda.cpp:80-103 ->
+ * MemorySaver_kernel_compression_backward.cu:651-666).  gA_u like A_u, gA_v like A_v. */
+int sfb_compression_backward(const float* F1, const float* F2, const float* A_u, const float* A_v,
+                             const float* gC_u, const float* gC_v, float* gF1, float* gF2, float* gA_u,
+                             float* gA_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
+/* Test aid with no counterpart in the reference ops: writes the dense volume S (B,H1,W1,H2,W2) of a
+ * SMALL problem through the same tensor-core pipeline (the reference builds it with torch.matmul,
+ * core/corr.py:286-289). */
+int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* Synchronises `stream`, reads the workspace's device status word into *device_status and returns
+ * SFB_OK if it is 0, SFB_ERR_DEVICE_TIMEOUT otherwise. */
+int sfb_device_status(const void* workspace, void* stream, int32_t* device_status);
+
+const char* sfb_status_string(int code);
+const char* sfb_last_error(void);
+int sfb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SEPFLOW_B200_H_ */

@@ -1,0 +1,71 @@
+"""ctypes binding of the C ABI in ``include/sepflow_b200.h``.
+
+There is no fallback: if the CUDA library has not been built, importing the ops fails with a
+message that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "csrc", "libsepflow_b200.so")
+
+SFB_OK = 0
+SFB_ERR_INVALID_ARGUMENT = 1
+SFB_ERR_UNSUPPORTED_SHAPE = 2
+SFB_ERR_WORKSPACE_TOO_SMALL = 3
+SFB_ERR_CUDA = 4
+SFB_ERR_DEVICE_TIMEOUT = 5
+
+OP_MAX_AVG_FORWARD = 0
+OP_COMPRESSION_FORWARD = 1
+OP_MAX_ARGMAX_AVG_BACKWARD = 2
+OP_COMPRESSION_BACKWARD = 3
+OP_CORR_VOLUME = 4
+
+# Every symbol include/sepflow_b200.h declares.
+EXPORTED_SYMBOLS = (
+    "sfb_workspace_bytes", "sfb_max_avg_forward", "sfb_max_argmax_avg_forward",
+    "sfb_max_argmax_avg_backward", "sfb_compression_forward", "sfb_compression_backward",
+    "sfb_corr_volume", "sfb_device_status", "sfb_status_string", "sfb_last_error", "sfb_version",
+)
+
+
+class SfbShape(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("B", "H1", "W1", "H2", "W2", "C", "Kc")]
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once and declare the argument types of every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m separableflowthesis_b200.build` "
+            "(needs nvcc; there is no CPU or PyTorch fallback for these ops)")
+    lib = ctypes.CDLL(LIB_PATH)
+    P, SZ, SH = ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(SfbShape)
+    tail = [SH, P, SZ, P]  # shape, workspace, workspace_bytes, stream
+    lib.sfb_workspace_bytes.restype = SZ
+    lib.sfb_workspace_bytes.argtypes = [ctypes.c_int, SH]
+    for name, nptr in (("sfb_max_avg_forward", 4), ("sfb_max_argmax_avg_forward", 6),
+                       ("sfb_max_argmax_avg_backward", 8), ("sfb_compression_forward", 6),
+                       ("sfb_compression_backward", 10), ("sfb_corr_volume", 3)):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [P] * nptr + tail
+    lib.sfb_device_status.restype = ctypes.c_int
+    lib.sfb_device_status.argtypes = [P, P, ctypes.POINTER(ctypes.c_int32)]
+    lib.sfb_status_string.restype = ctypes.c_char_p
+    lib.sfb_status_string.argtypes = [ctypes.c_int]
+    lib.sfb_last_error.restype = ctypes.c_char_p
+    lib.sfb_last_error.argtypes = []
+    lib.sfb_version.restype = ctypes.c_int
+    lib.sfb_version.argtypes = []
+    _lib = lib
+    return lib

@@ -1,0 +1,66 @@
+"""Call site of the separation ops: a drop-in for ``AlternateCorrBlockSepflow`` of the reference
+(core/corr.py:335-510), producing the two separated 3D cost volumes for all pyramid levels without
+ever holding the 4D correlation volume.
+
+Differences from the reference that do not change results: the scaled channels-last copy of
+``fmap1`` is made once instead of once per level (core/corr.py:419 recomputes it inside the loop).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .functions import ComputeMaxArgmaxAvgFunction, ComputeMaxAvgFunction, ComputeSelfCompressionFunction
+
+
+class AlternateCorrBlockSepflow:
+    """Separation of the correlation volume of ``fmap1`` (B,C,H,W) against the average-pooled pyramid
+    of ``fmap2``; ``guid`` must be None because non-local 4D filtering needs the stored volume
+    (core/corr.py:356-358)."""
+
+    def __init__(self, fmap1, fmap2, guid, num_levels=4, radius=4, support_backward=False):
+        if guid is not None:
+            raise Exception("Cannot use NLF while not storing the 4d correlation volume")
+        self.max_avg_function = ComputeMaxArgmaxAvgFunction if support_backward else ComputeMaxAvgFunction
+        self.num_levels = num_levels
+        self.radius = radius
+        self.fmap1_l0 = fmap1
+        self.pyramid = [fmap2]
+        for _ in range(num_levels - 1):
+            fmap2 = F.avg_pool2d(fmap2, 2, stride=2)
+            self.pyramid.append(fmap2)
+
+    def separate_level(self, F1, level, attention_weights):
+        """One pyramid level: returns (sep_u (B,K,W2,H1,W1), sep_v (B,K,H2,H1,W1)) before upsampling."""
+        F2 = self.pyramid[level].permute(0, 2, 3, 1).contiguous()
+        maxavg_u, maxavg_v = self.max_avg_function.apply(F1, F2)
+        # naming follows the reference: sep_v holds the per-u channels, sep_u the per-v channels
+        sep_v = maxavg_u.permute(0, 3, 4, 1, 2).contiguous()
+        sep_u = maxavg_v.permute(0, 3, 4, 1, 2).contiguous()
+        if attention_weights is not None:
+            attention1, attention2 = attention_weights
+            a_u = attention1(sep_u).softmax(dim=2).permute(0, 3, 4, 1, 2).contiguous()
+            a_v = attention2(sep_v).softmax(dim=2).permute(0, 3, 4, 1, 2).contiguous()
+            c_u, c_v = ComputeSelfCompressionFunction.apply(F1, F2, a_u, a_v)
+            sep_v = torch.cat((sep_v, c_u.permute(0, 3, 4, 1, 2)), dim=1)
+            sep_u = torch.cat((sep_u, c_v.permute(0, 3, 4, 1, 2)), dim=1)
+        return sep_u, sep_v
+
+    def separate(self, attention_weights):
+        """All levels, each trilinearly resampled to the level-0 displacement range and concatenated
+        over channels: sep_u (B, K*levels, W, H, W), sep_v (B, K*levels, H, H, W) (core/corr.py:384-477)."""
+        batch, fdim, h1, w1 = self.fmap1_l0.shape
+        F1 = self.fmap1_l0.permute(0, 2, 3, 1).contiguous() / math.sqrt(fdim)
+        sep_u_lvls, sep_v_lvls = [], []
+        for level in range(self.num_levels):
+            sep_u, sep_v = self.separate_level(F1, level, attention_weights)
+            sep_u_lvls.append(F.interpolate(sep_u, [w1, h1, w1], mode="trilinear", align_corners=True))
+            sep_v_lvls.append(F.interpolate(sep_v, [h1, h1, w1], mode="trilinear", align_corners=True))
+        return torch.cat(sep_u_lvls, dim=1), torch.cat(sep_v_lvls, dim=1)
+
+    def __call__(self, coords, sep=False, attention_weights=None):
+        if sep:
+            return self.separate(attention_weights)
+        raise NotImplementedError("Missing the cpp/cuda part for lookup of the 4d correlation volume without storing it")

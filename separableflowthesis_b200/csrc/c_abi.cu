@@ -1,0 +1,353 @@
+// C-ABI entry points (include/sepflow_b200.h): argument validation, workspace carving, TMA tensor
+// map encoding and the launch sequence of each op.  No torch types, no allocation.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/sepflow_b200.h"
+#include "kernels.h"
+
+namespace {
+
+using namespace sfb;
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// cuTensorMapEncodeTiled is looked up at run time so the library loads (and its symbols can be
+// inspected) on machines without a CUDA driver.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Tiled fp32 tensor map, 128-byte swizzle, innermost box = 32 channels (128 bytes), zero fill out of bounds.
+// dims/box are innermost-first; strides are implied by a contiguous tensor.
+int make_map(CUtensorMap* tm, const float* base, int rank, const uint64_t* dims, const uint32_t* box,
+             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+  cuuint64_t gdim[5], gstride[4];
+  cuuint32_t bdim[5], estride[5];
+  uint64_t stride = sizeof(float);
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estride[i] = 1;
+    stride *= dims[i];
+    if (i < rank - 1) gstride[i] = stride;  // byte stride of dimension i+1
+  }
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), gdim, gstride,
+                  bdim, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SFB_OK;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct Workspace {
+  int* status;
+  float* F1r;
+  float* F2r;
+  float* aux;
+  size_t bytes;
+};
+
+Workspace carve(const Dims& d, void* base, bool with_aux) {
+  Workspace w;
+  size_t off = 0;
+  char* p = static_cast<char*>(base);
+  w.status = reinterpret_cast<int*>(p + off);
+  off += 256;
+  w.F1r = reinterpret_cast<float*>(p + off);
+  off += align_up((size_t)d.B * d.N1() * d.C * sizeof(float), 256);
+  w.F2r = reinterpret_cast<float*>(p + off);
+  off += align_up((size_t)d.B * d.N2() * d.C * sizeof(float), 256);
+  w.aux = nullptr;
+  if (with_aux) {
+    w.aux = reinterpret_cast<float*>(p + off);
+    off += align_up((size_t)d.B * d.aux_rows() * d.C * sizeof(float), 256);
+  }
+  w.bytes = off;
+  return w;
+}
+
+int check_shape(const sfb_shape* s, bool need_kc, Dims* d) {
+  if (s == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "shape is NULL");
+  if (s->B < 1 || s->H1 < 1 || s->W1 < 1 || s->H2 < 1 || s->W2 < 1)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "B, H1, W1, H2, W2 must be >= 1 (got %d %d %d %d %d)", s->B, s->H1, s->W1,
+                s->H2, s->W2);
+  if (s->C < 4 || s->C > MAX_C || (s->C % 4) != 0)
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "feature dimension C=%d unsupported: need a multiple of 4 in [4, %d]", s->C,
+                MAX_C);
+  if (need_kc && s->Kc < 1) return fail(SFB_ERR_INVALID_ARGUMENT, "Kc must be >= 1 (got %d)", s->Kc);
+  if ((long long)s->H1 * s->W1 > (1ll << 30) || (long long)s->H2 * s->W2 > (1ll << 30))
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image has more than 2^30 pixels");
+  d->B = s->B; d->H1 = s->H1; d->W1 = s->W1; d->H2 = s->H2; d->W2 = s->W2; d->C = s->C;
+  d->Kc = need_kc ? s->Kc : 0;
+  return SFB_OK;
+}
+
+int check_ptr(const void* p, const char* name) {
+  if (p == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "%s is NULL", name);
+  if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return fail(SFB_ERR_INVALID_ARGUMENT, "%s is not 16-byte aligned", name);
+  return SFB_OK;
+}
+#define SFB_CHECK_PTR(p)                       \
+  do {                                         \
+    int rc_ = check_ptr((p), #p);              \
+    if (rc_ != SFB_OK) return rc_;             \
+  } while (0)
+#define SFB_TRY(expr)                          \
+  do {                                         \
+    int rc_ = (expr);                          \
+    if (rc_ != SFB_OK) return rc_;             \
+  } while (0)
+#define SFB_CUDA(expr)                                                                           \
+  do {                                                                                           \
+    cudaError_t e_ = (expr);                                                                     \
+    if (e_ != cudaSuccess) return fail(SFB_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_));  \
+  } while (0)
+
+int check_workspace(const Dims& d, void* ws, size_t ws_bytes, bool with_aux, Workspace* out) {
+  if (ws == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "workspace is NULL");
+  if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "workspace is not 256-byte aligned");
+  *out = carve(d, ws, with_aux);
+  if (ws_bytes < out->bytes)
+    return fail(SFB_ERR_WORKSPACE_TOO_SMALL, "workspace has %zu bytes, %zu needed", ws_bytes, out->bytes);
+  return SFB_OK;
+}
+
+// Tensor maps over the rounded copies.
+// `swizzle` is the 16-byte-atom 128B swizzle for K-major operands (rows = pixels of the tile) and the
+// 32-byte-atom variant for MN-major TF32 operands (the only layout tcgen05.mma accepts for those).
+int map_f1_rows(CUtensorMap* tm, const Dims& d, const float* F1r, uint32_t rows,
+                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {  // (C, N1, B)
+  const uint64_t dims[3] = {(uint64_t)d.C, (uint64_t)d.N1(), (uint64_t)d.B};
+  const uint32_t box[3] = {KBLK, rows, 1};
+  return make_map(tm, F1r, 3, dims, box, swizzle);
+}
+int map_f2_tile(CUtensorMap* tm, const Dims& d, const float* F2r, uint32_t ut, uint32_t vt,
+                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {  // (C, W2, H2, B)
+  const uint64_t dims[4] = {(uint64_t)d.C, (uint64_t)d.W2, (uint64_t)d.H2, (uint64_t)d.B};
+  const uint32_t box[4] = {KBLK, vt, ut, 1};
+  return make_map(tm, F2r, 4, dims, box, swizzle);
+}
+int map_aux(CUtensorMap* tm, const Dims& d, const float* aux) {  // (C, H2+W2, B)
+  const uint64_t dims[3] = {(uint64_t)d.C, (uint64_t)d.aux_rows(), (uint64_t)d.B};
+  const uint32_t box[3] = {KBLK, (uint32_t)(SWEEP_UT * SWEEP_VT), 1};
+  return make_map(tm, aux, 3, dims, box);
+}
+
+int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u, int32_t* AM_v,
+                       bool with_argmax, const sfb_shape* shape, void* ws, size_t ws_bytes, void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, false, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(MA_u); SFB_CHECK_PTR(MA_v);
+  if (with_argmax) { SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v); }
+  Workspace w;
+  SFB_TRY(check_workspace(d, ws, ws_bytes, true, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2, tm_aux;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_TRY(map_aux(&tm_aux, d, w.aux));
+  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st));
+  SweepArgs a;
+  memset(&a, 0, sizeof(a));
+  a.d = d;
+  a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
+  a.ma_u = MA_u; a.ma_v = MA_v; a.am_u = AM_u; a.am_v = AM_v;
+  a.status = w.status;
+  SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_aux, st));
+  return SFB_OK;
+}
+
+// C_u-like output = sum_v S * w_u, C_v-like output = sum_u S * w_v, at most KC_MAX_PER_SWEEP channels per sweep.
+int run_compress_sweeps(const Dims& d, const Workspace& w, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
+                        const float* w_u, const float* w_v, float* c_u, float* c_v, cudaStream_t st) {
+  for (int k0 = 0; k0 < d.Kc; k0 += KC_MAX_PER_SWEEP) {
+    SweepArgs a;
+    memset(&a, 0, sizeof(a));
+    a.d = d;
+    a.mode = SWEEP_COMPRESS;
+    a.k0 = k0;
+    a.kc = (d.Kc - k0 < KC_MAX_PER_SWEEP) ? d.Kc - k0 : KC_MAX_PER_SWEEP;
+    a.w_u = w_u; a.w_v = w_v; a.c_u = c_u; a.c_v = c_v;
+    a.status = w.status;
+    SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st));
+  }
+  return SFB_OK;
+}
+
+int run_grad_pair(const Dims& d, const Workspace& w, GradArgs a, float* gF1, float* gF2, cudaStream_t st) {
+  CUtensorMap tm_y;
+  a.d = d;
+  a.status = w.status;
+  // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2.
+  SFB_TRY(map_f2_tile(&tm_y, d, w.F2r, GG_UT, GG_VT, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  a.image2_major = 0;
+  a.out = gF1;
+  SFB_CUDA(launch_grad_gemm(a, tm_y, st));
+  // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1.
+  SFB_TRY(map_f1_rows(&tm_y, d, w.F1r, GG_KJ, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  a.image2_major = 1;
+  a.out = gF2;
+  SFB_CUDA(launch_grad_gemm(a, tm_y, st));
+  return SFB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t sfb_workspace_bytes(int op, const sfb_shape* shape) {
+  Dims d;
+  if (check_shape(shape, false, &d) != SFB_OK) return 0;
+  if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_CORR_VOLUME) return 0;
+  return carve(d, nullptr, op == SFB_OP_MAX_AVG_FORWARD).bytes;
+}
+
+int sfb_max_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, const sfb_shape* shape,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  return run_maxavg_forward(F1, F2, MA_u, MA_v, nullptr, nullptr, false, shape, workspace, workspace_bytes, stream);
+}
+
+int sfb_max_argmax_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u,
+                               int32_t* AM_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  return run_maxavg_forward(F1, F2, MA_u, MA_v, AM_u, AM_v, true, shape, workspace, workspace_bytes, stream);
+}
+
+int sfb_compression_forward(const float* F1, const float* F2, const float* A_u, const float* A_v, float* C_u,
+                            float* C_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(C_u); SFB_CHECK_PTR(C_v);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st));
+  return run_compress_sweeps(d, w, tm_f1, tm_f2, A_u, A_v, C_u, C_v, st);
+}
+
+int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
+                                const float* gMA_u, const float* gMA_v, float* gF1, float* gF2,
+                                const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, false, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v);
+  SFB_CHECK_PTR(gMA_u); SFB_CHECK_PTR(gMA_v); SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st));
+  GradArgs a;
+  memset(&a, 0, sizeof(a));
+  a.mode = GRAD_MAXAVG;
+  a.am_u = AM_u; a.am_v = AM_v; a.gma_u = gMA_u; a.gma_v = gMA_v;
+  return run_grad_pair(d, w, a, gF1, gF2, st);
+}
+
+int sfb_compression_backward(const float* F1, const float* F2, const float* A_u, const float* A_v,
+                             const float* gC_u, const float* gC_v, float* gF1, float* gF2, float* gA_u,
+                             float* gA_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(gC_u); SFB_CHECK_PTR(gC_v);
+  SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2); SFB_CHECK_PTR(gA_u); SFB_CHECK_PTR(gA_v);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st));
+  // gA_v[p,k,u] = sum_v S * gC_v[p,k,v]  and  gA_u[p,k,v] = sum_u S * gC_u[p,k,u]: the forward
+  // compression sweep with the upstream gradients in the role of the weights.
+  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, gC_v, gC_u, gA_v, gA_u, st));
+  GradArgs a;
+  memset(&a, 0, sizeof(a));
+  a.mode = GRAD_COMPRESS;
+  a.a_u = A_u; a.a_v = A_v; a.gc_u = gC_u; a.gc_v = gC_v;
+  return run_grad_pair(d, w, a, gF1, gF2, st);
+}
+
+int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, false, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(S);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st));
+  SweepArgs a;
+  memset(&a, 0, sizeof(a));
+  a.d = d;
+  a.mode = SWEEP_DUMP;
+  a.dump = S;
+  a.status = w.status;
+  SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st));
+  return SFB_OK;
+}
+
+int sfb_device_status(const void* workspace, void* stream, int32_t* device_status) {
+  if (workspace == nullptr || device_status == nullptr)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "workspace or device_status is NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t v = 0;
+  SFB_CUDA(cudaMemcpyAsync(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost, st));
+  SFB_CUDA(cudaStreamSynchronize(st));
+  *device_status = v;
+  if (v != 0) return fail(SFB_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (device status %d)", (int)v);
+  return SFB_OK;
+}
+
+const char* sfb_status_string(int code) {
+  switch (code) {
+    case SFB_OK: return "ok";
+    case SFB_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case SFB_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+    case SFB_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case SFB_ERR_CUDA: return "CUDA error";
+    case SFB_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+const char* sfb_last_error(void) { return g_err; }
+
+int sfb_version(void) { return 100; }
+
+}  // extern "C"

@@ -1,0 +1,64 @@
+// Internal launcher interface between the C-ABI layer (c_abi.cu) and the kernel files.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sfb {
+
+// Problem size of one op call (one pyramid level).  N1 = H1*W1 image-1 pixels, N2 = H2*W2.
+struct Dims {
+  int B, H1, W1, H2, W2, C, Kc;
+  __host__ __device__ int N1() const { return H1 * W1; }
+  __host__ __device__ int N2() const { return H2 * W2; }
+  __host__ __device__ int aux_rows() const { return H2 + W2; }
+};
+
+// Tile constants shared by host and device code.
+constexpr int TILE_M = 128;   // TMEM lanes = rows of one accumulator tile
+constexpr int KBLK = 32;      // fp32 elements in one 128-byte swizzled row
+constexpr int MAX_KB = 8;     // feature dimension C <= MAX_KB * KBLK
+constexpr int MAX_C = MAX_KB * KBLK;
+constexpr int SWEEP_UT = 8;   // image-2 rows per correlation tile
+constexpr int SWEEP_VT = 16;  // image-2 columns per correlation tile
+constexpr int GG_UT = 2;      // image-2 rows per K-block of the gradient GEMM (image-1-major form)
+constexpr int GG_VT = 16;
+constexpr int GG_KJ = 32;     // K extent (pixels of the other image) of one gradient-GEMM block
+constexpr int KC_MAX_PER_SWEEP = 4;  // attention channels handled by one compression sweep
+
+enum SweepMode : int { SWEEP_MAXAVG = 0, SWEEP_MAXARGAVG = 1, SWEEP_COMPRESS = 2, SWEEP_DUMP = 3 };
+enum GradMode : int { GRAD_MAXAVG = 0, GRAD_COMPRESS = 1 };
+
+struct SweepArgs {
+  Dims d;
+  int mode;
+  int k0, kc;            // compression: first channel and number of channels (<= KC_MAX_PER_SWEEP) of this launch
+  // max/avg outputs
+  float* ma_u; float* ma_v; int32_t* am_u; int32_t* am_v;
+  // compression: weights (B,N1,Kc,W2) / (B,N1,Kc,H2) and outputs (B,N1,Kc,H2) / (B,N1,Kc,W2)
+  const float* w_u; const float* w_v; float* c_u; float* c_v;
+  float* dump;           // SWEEP_DUMP: dense S (B,N1,H2,W2), test use only
+  int* status;           // device status word
+};
+
+struct GradArgs {
+  Dims d;
+  int mode;
+  int image2_major;      // 0: rows = image-1 pixels, output gF1; 1: rows = image-2 pixels, output gF2
+  // GRAD_MAXAVG inputs
+  const int32_t* am_u; const int32_t* am_v; const float* gma_u; const float* gma_v;
+  // GRAD_COMPRESS inputs
+  const float* a_u; const float* a_v; const float* gc_u; const float* gc_v;
+  float* out;            // gF1 (B,N1,C) or gF2 (B,N2,C)
+  int* status;
+};
+
+// Rounds F1/F2 to TF32 (round-to-nearest) into the workspace copies, optionally builds the
+// row/column mean rows of F2, and clears the status word.
+cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
+                           int* status, cudaStream_t stream);
+cudaError_t launch_sweep(const SweepArgs& a, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
+                         const CUtensorMap& tm_aux, cudaStream_t stream);
+cudaError_t launch_grad_gemm(const GradArgs& a, const CUtensorMap& tm_y, cudaStream_t stream);
+
+}  // namespace sfb

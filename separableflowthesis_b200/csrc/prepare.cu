@@ -1,0 +1,62 @@
+// Operand preparation (HBM-bound, a few percent of an op's time):
+//  * copies of F1 and F2 rounded to TF32 with round-to-nearest.  tcgen05.mma kind::tf32 ignores the
+//    low 13 mantissa bits of its fp32 operands, i.e. truncates; truncation shrinks every product by
+//    ~2^-10 and would put a bias of that relative size on every S value, rounding does not.
+//  * the "aux" rows of F2 used for the mean channels: row u of aux = mean over v of F2[u,v,:],
+//    row H2+v = mean over u of F2[u,v,:]  (mean_v S[p,u,v] = F1[p] . mean_v F2[u,v], the same sum the
+//    reference accumulates cell by cell, MemorySaver_kernel_forward.cu:286-290).
+#include <algorithm>
+
+#include "kernels.h"
+#include "sm100_primitives.cuh"
+
+namespace sfb {
+
+__global__ void round_copy_kernel(const float4* __restrict__ in, float4* __restrict__ out, size_t n4) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 v = __ldg(in + i);
+    v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w);
+    out[i] = v;
+  }
+}
+
+// grid (H2 + W2, B), block = min(C, 256) threads over channels.
+__global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict__ aux, int H2, int W2, int C) {
+  const int r = blockIdx.x, b = blockIdx.y;
+  const float* base = F2 + (size_t)b * H2 * W2 * C;
+  float* dst = aux + ((size_t)b * (H2 + W2) + r) * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    if (r < H2) {
+      const float* row = base + (size_t)r * W2 * C + c;
+      for (int v = 0; v < W2; ++v) acc += __ldg(row + (size_t)v * C);
+      acc /= (float)W2;
+    } else {
+      const float* col = base + (size_t)(r - H2) * C + c;
+      for (int u = 0; u < H2; ++u) acc += __ldg(col + (size_t)u * W2 * C);
+      acc /= (float)H2;
+    }
+    dst[c] = round_tf32(acc);
+  }
+}
+
+cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
+                           int* status, cudaStream_t stream) {
+  cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  if (err != cudaSuccess) return err;
+  const size_t n1 = (size_t)d.B * d.N1() * d.C / 4, n2 = (size_t)d.B * d.N2() * d.C / 4;  // C % 4 == 0
+  const int threads = 256;
+  auto blocks = [&](size_t n) { return (unsigned)std::min<size_t>((n + threads - 1) / threads, 148 * 16); };
+  round_copy_kernel<<<blocks(n1), threads, 0, stream>>>(reinterpret_cast<const float4*>(F1),
+                                                        reinterpret_cast<float4*>(F1r), n1);
+  round_copy_kernel<<<blocks(n2), threads, 0, stream>>>(reinterpret_cast<const float4*>(F2),
+                                                        reinterpret_cast<float4*>(F2r), n2);
+  if (aux != nullptr) {
+    const dim3 grid(d.H2 + d.W2, d.B);
+    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2, aux, d.H2, d.W2, d.C);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace sfb

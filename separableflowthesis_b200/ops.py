@@ -1,0 +1,170 @@
+"""The five native ops, under the names and signatures of the reference's pybind11 module
+``MemorySaver`` (libs/MemorySaver/src/MemorySaver_cuda.cpp:105-112): tensors in, a list of freshly
+allocated tensors out.  Each function validates its inputs the way the reference's CHECK_INPUT does
+(CUDA + contiguous, MemorySaver_cuda.cpp:6-8; plus the shape/dtype checks the reference lacks),
+allocates the outputs and calls the C ABI of ``libsepflow_b200.so`` on the current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, List, Tuple
+
+import torch
+
+from . import _lib
+
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _check(t: torch.Tensor, name: str, dtype: torch.dtype, ndim: int) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if t.dim() != ndim:
+        raise RuntimeError(f"{name} must have {ndim} dimensions, got {t.dim()}")
+
+
+def _check_pair(F1: torch.Tensor, F2: torch.Tensor) -> _lib.SfbShape:
+    _check(F1, "img1_features_l0", torch.float32, 4)
+    _check(F2, "img2_features_lk", torch.float32, 4)
+    if F1.device != F2.device:
+        raise RuntimeError("img1_features_l0 and img2_features_lk must be on the same device")
+    if F1.shape[0] != F2.shape[0] or F1.shape[3] != F2.shape[3]:
+        raise RuntimeError(f"batch / feature dimensions differ: {tuple(F1.shape)} vs {tuple(F2.shape)}")
+    B, H1, W1, C = F1.shape
+    _, H2, W2, _ = F2.shape
+    return _lib.SfbShape(B, H1, W1, H2, W2, C, 0)
+
+
+def _check_like(t: torch.Tensor, name: str, shape, dtype, device) -> None:
+    _check(t, name, dtype, len(shape))
+    if tuple(t.shape) != tuple(shape):
+        raise RuntimeError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+    if t.device != device:
+        raise RuntimeError(f"{name} is on {t.device}, expected {device}")
+
+
+def _workspace(nbytes: int, device: torch.device, stream: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _call(name: str, op: int, shape: _lib.SfbShape, device: torch.device, tensors) -> None:
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        nbytes = lib.sfb_workspace_bytes(op, ctypes.byref(shape))
+        if nbytes == 0:
+            # run the entry point anyway so that the library reports the precise reason
+            nbytes = 256
+        ws = _workspace(nbytes, device, stream)
+        rc = getattr(lib, name)(*[ctypes.c_void_p(t.data_ptr()) for t in tensors], ctypes.byref(shape),
+                                ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(ws.numel()),
+                                ctypes.c_void_p(stream))
+        if rc != _lib.SFB_OK:
+            raise RuntimeError(f"{name}: {lib.sfb_status_string(rc).decode()}: {lib.sfb_last_error().decode()}")
+        if os.environ.get("SFB_CHECK_DEVICE_STATUS", "0") == "1":
+            dev_status = ctypes.c_int32(0)
+            rc = lib.sfb_device_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(stream),
+                                       ctypes.byref(dev_status))
+            if rc != _lib.SFB_OK:
+                raise RuntimeError(f"{name}: {lib.sfb_last_error().decode()}")
+
+
+def max_avg_forward(img1_features_l0: torch.Tensor, img2_features_lk: torch.Tensor) -> List[torch.Tensor]:
+    """MemorySaver.max_avg_forward (MemorySaver_cuda.cpp:10-21): returns [MA_u, MA_v]."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    MA_u = torch.empty(s.B, s.H1, s.W1, 2, s.H2, dtype=torch.float32, device=F1.device)
+    MA_v = torch.empty(s.B, s.H1, s.W1, 2, s.W2, dtype=torch.float32, device=F1.device)
+    _call("sfb_max_avg_forward", _lib.OP_MAX_AVG_FORWARD, s, F1.device, (F1, F2, MA_u, MA_v))
+    return [MA_u, MA_v]
+
+
+def max_argmax_avg_forward(img1_features_l0: torch.Tensor, img2_features_lk: torch.Tensor) -> List[torch.Tensor]:
+    """MemorySaver.max_argmax_avg_forward (MemorySaver_cuda.cpp:23-34): returns [MA_u, MA_v, AM_u, AM_v]."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    MA_u = torch.empty(s.B, s.H1, s.W1, 2, s.H2, dtype=torch.float32, device=F1.device)
+    MA_v = torch.empty(s.B, s.H1, s.W1, 2, s.W2, dtype=torch.float32, device=F1.device)
+    AM_u = torch.empty(s.B, s.H1, s.W1, 1, s.H2, dtype=torch.int32, device=F1.device)
+    AM_v = torch.empty(s.B, s.H1, s.W1, 1, s.W2, dtype=torch.int32, device=F1.device)
+    _call("sfb_max_argmax_avg_forward", _lib.OP_MAX_AVG_FORWARD, s, F1.device, (F1, F2, MA_u, MA_v, AM_u, AM_v))
+    return [MA_u, MA_v, AM_u, AM_v]
+
+
+def max_argmax_avg_backward(img1_features_l0, img2_features_lk, argmax_output_u, argmax_output_v,
+                            grad_MaxAvg_u, grad_MaxAvg_v) -> List[torch.Tensor]:
+    """MemorySaver.max_argmax_avg_backward (MemorySaver_cuda.cpp:55-78): returns [gF1, gF2]."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_like(argmax_output_u, "argmax_output_u", (s.B, s.H1, s.W1, 1, s.H2), torch.int32, dev)
+    _check_like(argmax_output_v, "argmax_output_v", (s.B, s.H1, s.W1, 1, s.W2), torch.int32, dev)
+    _check_like(grad_MaxAvg_u, "grad_MaxAvg_u", (s.B, s.H1, s.W1, 2, s.H2), torch.float32, dev)
+    _check_like(grad_MaxAvg_v, "grad_MaxAvg_v", (s.B, s.H1, s.W1, 2, s.W2), torch.float32, dev)
+    gF1 = torch.empty_like(F1)
+    gF2 = torch.empty_like(F2)
+    _call("sfb_max_argmax_avg_backward", _lib.OP_MAX_ARGMAX_AVG_BACKWARD, s, dev,
+          (F1, F2, argmax_output_u, argmax_output_v, grad_MaxAvg_u, grad_MaxAvg_v, gF1, gF2))
+    return [gF1, gF2]
+
+
+def _check_attention(s: _lib.SfbShape, A_u, A_v, dev, names=("attention_weights_u", "attention_weights_v")):
+    _check(A_u, names[0], torch.float32, 5)
+    s.Kc = A_u.shape[3]
+    _check_like(A_u, names[0], (s.B, s.H1, s.W1, s.Kc, s.W2), torch.float32, dev)
+    _check_like(A_v, names[1], (s.B, s.H1, s.W1, s.Kc, s.H2), torch.float32, dev)
+    if s.Kc < 1:
+        raise RuntimeError("attention weights need at least one channel")
+
+
+def compression_forward(img1_features_l0, img2_features_lk, attention_weights_u, attention_weights_v) -> List[torch.Tensor]:
+    """MemorySaver.compression_forward (MemorySaver_cuda.cpp:36-53), any Kc >= 1: returns [C_u, C_v]."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_attention(s, attention_weights_u, attention_weights_v, dev)
+    C_u = torch.empty(s.B, s.H1, s.W1, s.Kc, s.H2, dtype=torch.float32, device=dev)
+    C_v = torch.empty(s.B, s.H1, s.W1, s.Kc, s.W2, dtype=torch.float32, device=dev)
+    _call("sfb_compression_forward", _lib.OP_COMPRESSION_FORWARD, s, dev,
+          (F1, F2, attention_weights_u, attention_weights_v, C_u, C_v))
+    return [C_u, C_v]
+
+
+def compression_backward(img1_features_l0, img2_features_lk, attention_weights_u, attention_weights_v,
+                         grad_compressed_output_u, grad_compressed_output_v) -> List[torch.Tensor]:
+    """MemorySaver.compression_backward (MemorySaver_cuda.cpp:80-103): returns [gF1, gF2, gA_u, gA_v]."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_attention(s, attention_weights_u, attention_weights_v, dev)
+    _check_like(grad_compressed_output_u, "grad_compressed_output_u", (s.B, s.H1, s.W1, s.Kc, s.H2), torch.float32, dev)
+    _check_like(grad_compressed_output_v, "grad_compressed_output_v", (s.B, s.H1, s.W1, s.Kc, s.W2), torch.float32, dev)
+    gF1 = torch.empty_like(F1)
+    gF2 = torch.empty_like(F2)
+    gA_u = torch.empty_like(attention_weights_u)
+    gA_v = torch.empty_like(attention_weights_v)
+    _call("sfb_compression_backward", _lib.OP_COMPRESSION_BACKWARD, s, dev,
+          (F1, F2, attention_weights_u, attention_weights_v, grad_compressed_output_u, grad_compressed_output_v,
+           gF1, gF2, gA_u, gA_v))
+    return [gF1, gF2, gA_u, gA_v]
+
+
+def corr_volume(img1_features_l0, img2_features_lk) -> torch.Tensor:
+    """Test aid: the dense volume S (B,H1,W1,H2,W2) of a small problem, through the tensor-core pipeline."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    S = torch.empty(s.B, s.H1, s.W1, s.H2, s.W2, dtype=torch.float32, device=F1.device)
+    _call("sfb_corr_volume", _lib.OP_CORR_VOLUME, s, F1.device, (F1, F2, S))
+    return S

@@ -1,0 +1,59 @@
+"""CPU: the C-ABI library loads without a GPU, exports every symbol include/sepflow_b200.h
+declares, and rejects bad arguments before touching CUDA."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from separableflowthesis_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build_library()
+    return _lib.load()
+
+
+def test_exports_every_declared_symbol(lib):
+    header = open(os.path.join(ROOT, "include", "sepflow_b200.h")).read()
+    declared = set(re.findall(r"\b(sfb_[a-z_0-9]+)\s*\(", header))
+    assert declared == set(_lib.EXPORTED_SYMBOLS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.sfb_version() >= 100
+
+
+def test_workspace_query(lib):
+    s = _lib.SfbShape(2, 48, 64, 48, 64, 256, 2)
+    fwd = lib.sfb_workspace_bytes(_lib.OP_MAX_AVG_FORWARD, ctypes.byref(s))
+    bwd = lib.sfb_workspace_bytes(_lib.OP_COMPRESSION_BACKWARD, ctypes.byref(s))
+    feat = 2 * 48 * 64 * 256 * 4
+    assert bwd >= 2 * feat and fwd >= bwd + 2 * (48 + 64) * 256 * 4
+    bad = _lib.SfbShape(2, 48, 64, 48, 64, 258, 2)
+    assert lib.sfb_workspace_bytes(_lib.OP_MAX_AVG_FORWARD, ctypes.byref(bad)) == 0
+    assert lib.sfb_workspace_bytes(99, ctypes.byref(s)) == 0
+
+
+def test_argument_validation(lib):
+    s = _lib.SfbShape(1, 4, 4, 4, 4, 32, 2)
+    P = ctypes.c_void_p
+    buf = (ctypes.c_char * 4096)()
+    a16 = (ctypes.addressof(buf) + 255) // 256 * 256
+    rc = lib.sfb_max_avg_forward(None, P(a16), P(a16), P(a16), ctypes.byref(s), P(a16), 1 << 20, None)
+    assert rc == _lib.SFB_ERR_INVALID_ARGUMENT and b"F1 is NULL" in lib.sfb_last_error()
+    rc = lib.sfb_max_avg_forward(P(a16 + 4), P(a16), P(a16), P(a16), ctypes.byref(s), P(a16), 1 << 20, None)
+    assert rc == _lib.SFB_ERR_INVALID_ARGUMENT and b"aligned" in lib.sfb_last_error()
+    rc = lib.sfb_max_avg_forward(P(a16), P(a16), P(a16), P(a16), ctypes.byref(s), P(a16), 16, None)
+    assert rc == _lib.SFB_ERR_WORKSPACE_TOO_SMALL
+    bad_c = _lib.SfbShape(1, 4, 4, 4, 4, 300, 2)
+    rc = lib.sfb_compression_forward(P(a16), P(a16), P(a16), P(a16), P(a16), P(a16), ctypes.byref(bad_c), P(a16),
+                                     1 << 20, None)
+    assert rc == _lib.SFB_ERR_UNSUPPORTED_SHAPE
+    no_k = _lib.SfbShape(1, 4, 4, 4, 4, 32, 0)
+    rc = lib.sfb_compression_forward(P(a16), P(a16), P(a16), P(a16), P(a16), P(a16), ctypes.byref(no_k), P(a16),
+                                     1 << 20, None)
+    assert rc == _lib.SFB_ERR_INVALID_ARGUMENT
+    assert lib.sfb_status_string(_lib.SFB_ERR_DEVICE_TIMEOUT) == b"device-side wait timed out"

@@ -1,0 +1,75 @@
+"""CPU: the host-side mirror of the reference call site (separableflowthesis_b200/corr.py and
+functions.py) with the oracle plugged in where the CUDA ops go, against the golden vectors of the
+reference's dense CorrBlock.  This tests glue (permutes, conv+softmax, concatenation, upsampling,
+autograd wiring); the CUDA ops themselves are tested in the gpu-marked files."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import separableflowthesis_b200 as sfb
+from separableflowthesis_b200 import functions
+from oracle import separation_oracle as orc
+
+
+def _t(x):
+    return torch.from_numpy(np.ascontiguousarray(x))
+
+
+@pytest.fixture()
+def oracle_backend(monkeypatch):
+    monkeypatch.setattr(functions, "MemorySaver", orc)
+
+
+def test_block_matches_reference_dense_path(golden_dir, oracle_backend):
+    g = np.load(os.path.join(golden_dir, "block_dense_b2_c16_9x11_k2.npz"))
+    f1 = _t(g["f1"]).requires_grad_(True)
+    f2 = _t(g["f2"]).requires_grad_(True)
+    convs = []
+    for i in range(2):
+        conv = torch.nn.Conv3d(2, g["w0"].shape[0], 3, padding=1).double()
+        with torch.no_grad():
+            conv.weight.copy_(_t(g[f"w{i}"]))
+            conv.bias.copy_(_t(g[f"b{i}"]))
+        convs.append(conv)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True)
+    sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(convs))
+    assert (sep_u - _t(g["sep_u"])).abs().max().item() < 1e-11
+    assert (sep_v - _t(g["sep_v"])).abs().max().item() < 1e-11
+    gen = torch.Generator().manual_seed(int(g["loss_seed"]))
+    wu = torch.randn(sep_u.shape, generator=gen, dtype=torch.float64)
+    wv = torch.randn(sep_v.shape, generator=gen, dtype=torch.float64)
+    ((sep_u * wu).sum() + (sep_v * wv).sum()).backward()
+    assert (f1.grad - _t(g["g_f1"])).abs().max().item() < 1e-10
+    assert (f2.grad - _t(g["g_f2"])).abs().max().item() < 1e-10
+    for i, conv in enumerate(convs):
+        assert (conv.weight.grad - _t(g[f"g_w{i}"])).abs().max().item() < 1e-10
+        assert (conv.bias.grad - _t(g[f"g_b{i}"])).abs().max().item() < 1e-10
+
+
+def test_inference_block_has_no_backward(oracle_backend):
+    f1 = torch.randn(1, 8, 4, 6, dtype=torch.float64, requires_grad=True)
+    f2 = torch.randn(1, 8, 4, 6, dtype=torch.float64)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=2, support_backward=False)
+    sep_u, sep_v = blk(None, sep=True, attention_weights=None)
+    assert sep_u.shape == (1, 4, 6, 4, 6) and sep_v.shape == (1, 4, 4, 4, 6)
+    with pytest.raises(NotImplementedError):
+        sep_u.sum().backward()
+
+
+def test_block_error_behaviour(oracle_backend):
+    f = torch.randn(1, 8, 4, 6)
+    with pytest.raises(Exception, match="NLF"):
+        sfb.AlternateCorrBlockSepflow(f, f, guid=torch.zeros(1))
+    blk = sfb.AlternateCorrBlockSepflow(f, f, None, num_levels=2)
+    with pytest.raises(NotImplementedError):
+        blk(None, sep=False)
+
+
+def test_ops_reject_cpu_and_malformed_tensors():
+    F1 = torch.randn(1, 4, 4, 8)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        sfb.MemorySaver.max_avg_forward(F1, F1)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        sfb.MemorySaver.compression_forward(F1, F1, F1, F1)
