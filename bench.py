@@ -1,0 +1,451 @@
+#!/usr/bin/env python
+"""Benchmark of the cost-volume separation hot path: cells/s of forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 1..5] [--impl ours|reference]
+
+One "step" is one pass of the four ops over one batch of synthetic feature maps:
+max/argmax/avg forward, compression forward, compression backward, max/avg backward (forward-only
+configs run the first two).  A "cell" is one entry of the virtual volume S (B*H1*W1*H2*W2 per step).
+Default workload: BASELINE config 5 (B=8, 135x240, C=256, Kc=4, fwd+bwd), the configuration the
+throughput target is quoted on; it fits one GPU.  With N > 1 ranks (torchrun) the same job is split
+by batch, then by image-1 rows (strong scaling); rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# (B, H, W, Kc, backward) of BASELINE.json's configs; C = 256 everywhere
+CONFIGS = {
+    1: dict(B=1, H=48, W=64, Kc=0, bwd=False, name="config1: B=1 48x64 C=256 fwd max/avg only"),
+    2: dict(B=2, H=48, W=64, Kc=2, bwd=True, name="config2: B=2 48x64 C=256 Kc=2 fwd+bwd"),
+    3: dict(B=4, H=55, W=128, Kc=4, bwd=False, name="config3: B=4 55x128 C=256 Kc=4 fwd"),
+    4: dict(B=8, H=47, W=156, Kc=2, bwd=True, name="config4: B=8 47x156 C=256 Kc=2 fwd+bwd (fp32 operands)"),
+    5: dict(B=8, H=135, W=240, Kc=4, bwd=True, name="config5: B=8 135x240 C=256 Kc=4 fwd+bwd"),
+}
+C_FEAT = 256
+SEED = 1234  # the reference's default seed (train.py:52)
+
+# DRAM bytes per cell (dram__bytes_read.sum + dram__bytes_write.sum of one launch / cells of that launch)
+# from the ncu captures summarised under profiles/; traffic grows in proportion to the cells swept.
+DRAM_BYTES_PER_CELL = {}
+try:
+    with open(os.path.join(ROOT, "profiles", "dram_bytes_per_cell.json")) as _f:
+        DRAM_BYTES_PER_CELL = json.load(_f)
+except OSError:
+    pass
+
+
+def flops_per_cell(cfg) -> int:
+    """Algorithmic tensor work: 2*C per necessary contraction; forward 1 (no attention) or 2,
+    backward 3 (S recompute for the attention gradients, gF1, gF2)."""
+    n = 1 if cfg["Kc"] == 0 else 2
+    if cfg["bwd"]:
+        n += 3
+    return n * 2 * C_FEAT
+
+
+# --------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.out = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.flush()
+        self.out.seek(0)
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.out.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        self.out.close()
+        os.unlink(self.out.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------- workload
+def make_job(cfg, shard, device):
+    """Seeded N(0,1) features of this rank's shard (drawn for the whole job, then sliced, so every
+    world size sees the same data), softmaxed random attention weights and N(0,1) upstream gradients."""
+    B, H, W, Kc = cfg["B"], cfg["H"], cfg["W"], cfg["Kc"]
+    g = torch.Generator().manual_seed(SEED)
+    f1 = torch.randn(B, C_FEAT, H, W, generator=g)
+    f2 = torch.randn(B, C_FEAT, H, W, generator=g)
+    f1 = f1[shard.b0:shard.b1, :, shard.r0:shard.r1].contiguous()
+    f2 = f2[shard.b0:shard.b1].contiguous()
+    job = {"f1_nchw": f1, "f2_nchw": f2}
+    F1 = (f1.permute(0, 2, 3, 1).contiguous() / C_FEAT ** 0.5).to(device)
+    F2 = f2.permute(0, 2, 3, 1).contiguous().to(device)
+    b, h = F1.shape[0], F1.shape[1]
+    gd = torch.Generator(device=device).manual_seed(SEED + 1 + shard.rank)
+    job.update(F1=F1, F2=F2)
+    if Kc > 0:
+        job["A_u"] = torch.randn(b, h, W, Kc, W, generator=gd, device=device).softmax(-1)
+        job["A_v"] = torch.randn(b, h, W, Kc, H, generator=gd, device=device).softmax(-1)
+    if cfg["bwd"]:
+        job["gMA_u"] = torch.randn(b, h, W, 2, H, generator=gd, device=device)
+        job["gMA_v"] = torch.randn(b, h, W, 2, W, generator=gd, device=device)
+        if Kc > 0:
+            job["gC_u"] = torch.randn(b, h, W, Kc, H, generator=gd, device=device)
+            job["gC_v"] = torch.randn(b, h, W, Kc, W, generator=gd, device=device)
+    job["cells"] = b * h * W * H * W
+    return job
+
+
+def run_ops(ms, cfg, job):
+    """The hot path on device-resident inputs; returns something small that depends on the results."""
+    F1, F2 = job["F1"], job["F2"]
+    if cfg["bwd"]:
+        MA_u, MA_v, AM_u, AM_v = ms.max_argmax_avg_forward(F1, F2)
+    else:
+        MA_u, MA_v = ms.max_avg_forward(F1, F2)
+    out = [MA_u, MA_v]
+    if cfg["Kc"] > 0:
+        out += ms.compression_forward(F1, F2, job["A_u"], job["A_v"])
+    if cfg["bwd"]:
+        if cfg["Kc"] > 0:
+            out += ms.compression_backward(F1, F2, job["A_u"], job["A_v"], job["gC_u"], job["gC_v"])
+        out += ms.max_argmax_avg_backward(F1, F2, AM_u, AM_v, job["gMA_u"], job["gMA_v"])
+    return out
+
+
+def launches_per_step(cfg) -> int:
+    """Kernels of this library launched by one step (the prepare step is 2 rounding copies, plus the
+    F2 mean rows for the max/avg forward)."""
+    n = 3 + 1                                   # max/avg forward: prepare(3) + sweep
+    sweeps = (cfg["Kc"] + 3) // 4
+    if cfg["Kc"] > 0:
+        n += 2 + sweeps                         # compression forward
+    if cfg["bwd"]:
+        if cfg["Kc"] > 0:
+            n += 2 + sweeps + 2                 # compression backward: prepare, sweep(s), 2 gradient GEMMs
+        n += 2 + 2                              # max/avg backward: prepare, 2 gradient GEMMs
+    return n
+
+
+class E2E:
+    """The call a user of the reference makes: channels-first feature maps in host memory ->
+    AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
+    gradients -> loss-sized results back on the host."""
+
+    def __init__(self, cfg, job, device):
+        import separableflowthesis_b200 as sfb
+        self.sfb, self.cfg, self.device = sfb, cfg, device
+        self.h1 = job["f1_nchw"].pin_memory()
+        self.h2 = job["f2_nchw"].pin_memory()
+        self.att = None
+        if cfg["Kc"] > 0:
+            g = torch.Generator().manual_seed(SEED + 99)
+            self.att = []
+            for _ in range(2):
+                conv = torch.nn.Conv3d(2, cfg["Kc"], 3, padding=1)
+                with torch.no_grad():
+                    conv.weight.copy_(torch.randn(conv.weight.shape, generator=g) * 0.02)
+                    conv.bias.copy_(torch.randn(conv.bias.shape, generator=g) * 0.02)
+                self.att.append(conv.to(device))
+        self.up = None
+        self.host_out = torch.empty(1024, dtype=torch.float32).pin_memory()
+        self.h2d = self.h1.numel() * 4 + self.h2.numel() * 4
+        self.d2h = 0
+
+    def step(self):
+        cfg, dev = self.cfg, self.device
+        f1 = self.h1.to(dev, non_blocking=True)
+        f2 = self.h2.to(dev, non_blocking=True)
+        if cfg["bwd"]:
+            f1.requires_grad_(True)
+            f2.requires_grad_(True)
+        blk = self.sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=1, support_backward=cfg["bwd"])
+        with torch.set_grad_enabled(cfg["bwd"]):
+            sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(self.att) if self.att else None)
+        if cfg["bwd"]:
+            if self.up is None:
+                gd = torch.Generator(device=dev).manual_seed(SEED + 7)
+                self.up = (torch.randn(sep_u.shape, generator=gd, device=dev),
+                           torch.randn(sep_v.shape, generator=gd, device=dev))
+            params = [p for c in (self.att or []) for p in c.parameters()]
+            for p in params:
+                p.grad = None
+            torch.autograd.backward([sep_u, sep_v], list(self.up))
+            from separableflowthesis_b200 import sharding
+            flat = sharding.reduce_parameter_grads(params)  # NCCL all-reduce when world_size > 1
+            pieces = [f1.grad.sum().reshape(1), f2.grad.sum().reshape(1)]
+            if flat is not None:
+                pieces.append(flat[:1000])
+            res = torch.cat(pieces)
+        else:
+            res = torch.stack((sep_u.sum(), sep_v.sum()))
+        self.host_out[:res.numel()].copy_(res, non_blocking=True)
+        self.d2h = res.numel() * 4
+        torch.cuda.current_stream().synchronize()
+        return float(self.host_out[0])
+
+
+# --------------------------------------------------------------------------------------- CPU baseline
+def cpu_sample(cfg, rows, threads):
+    """One bounded sample of the workload through the oracle on the host cores: `rows` image-1 rows of
+    one sample against the whole of image 2 (identical math, work is linear in image-1 rows)."""
+    from oracle import separation_oracle as orc
+    torch.set_num_threads(threads)
+    H, W, Kc = cfg["H"], cfg["W"], cfg["Kc"]
+    g = torch.Generator().manual_seed(SEED)
+    F1 = torch.randn(1, rows, W, C_FEAT, generator=g) / C_FEAT ** 0.5
+    F2 = torch.randn(1, H, W, C_FEAT, generator=g)
+    A_u = torch.randn(1, rows, W, max(Kc, 1), W, generator=g).softmax(-1)
+    A_v = torch.randn(1, rows, W, max(Kc, 1), H, generator=g).softmax(-1)
+    gMA_u = torch.randn(1, rows, W, 2, H, generator=g)
+    gMA_v = torch.randn(1, rows, W, 2, W, generator=g)
+    gC_u = torch.randn(1, rows, W, max(Kc, 1), H, generator=g)
+    gC_v = torch.randn(1, rows, W, max(Kc, 1), W, generator=g)
+
+    def run():
+        fw = orc.max_argmax_avg_forward(F1, F2)
+        if Kc > 0:
+            orc.compression_forward(F1, F2, A_u, A_v)
+        if cfg["bwd"]:
+            if Kc > 0:
+                orc.compression_backward(F1, F2, A_u, A_v, gC_u, gC_v)
+            orc.max_argmax_avg_backward(F1, F2, fw[2], fw[3], gMA_u, gMA_v)
+    return run, rows * W * H * W
+
+
+def time_cpu(cfg, budget_s, steps=None, warmup=1):
+    threads = os.cpu_count() or 1
+    rows = 1
+    run, cells = cpu_sample(cfg, rows, threads)
+    t0 = time.perf_counter()
+    run()
+    t1 = time.perf_counter() - t0
+    n_steps = steps if steps is not None else 3
+    # grow the sample so that the whole measurement takes about budget_s
+    rows = int(max(1, min(cfg["H"], budget_s / max(t1, 1e-3) / (n_steps + warmup))))
+    run, cells = cpu_sample(cfg, rows, threads)
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(n_steps):
+        run()
+    dt = (time.perf_counter() - t0) / n_steps
+    return dict(value=cells / dt, unit="cells/s", cores=threads, kind="port",
+                sample=f"{rows} of {cfg['H']} image-1 rows of one sample ({cells} cells) per step, {n_steps} steps, "
+                       f"oracle (dense torch CPU fp32 matmul/einsum + max/mean), {threads} threads"), dt, n_steps
+
+
+# --------------------------------------------------------------------------------------- main
+def measure_tf32_peak(device):
+    """cuBLAS TF32 GEMM 8192^3 through torch.matmul, best of 10 (burst) and back to back for ~1 s."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    n = 8192
+    a = torch.randn(n, n, device=device)
+    b = torch.randn(n, n, device=device)
+    for _ in range(3):
+        a @ b
+    best = float("inf")
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); a @ b; e1.record(); e1.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(10, int(1000.0 / best))
+    e0.record()
+    for _ in range(reps):
+        a @ b
+    e1.record(); e1.synchronize()
+    sustained = e0.elapsed_time(e1) / reps
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    fl = 2.0 * n ** 3
+    return fl / best / 1e9, fl / sustained / 1e9  # TFLOP/s
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    unit = "cells/s"
+    metric = "separated cost-volume cells/sec (fwd+bwd)" if cfg["bwd"] else "separated cost-volume cells/sec (fwd)"
+
+    if args.impl == "reference":
+        # The reference's own path cannot travel (Python + a CUDA extension that needs its checkout);
+        # the timed CPU arm is the oracle port of its dense einsum path on all host cores, rank 0 only.
+        if rank != 0:
+            return
+        base, dt, n_steps = time_cpu(cfg, budget_s=60.0, steps=args.steps, warmup=max(1, min(args.warmup, 2)))
+        line = {"impl": "reference", "metric": metric, "value": base["value"], "unit": unit, "n_gpus": args.gpus,
+                "steps": n_steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": {"workload": cfg["name"], "timed": base["sample"]},
+                "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch.distributed as dist
+    from separableflowthesis_b200 import _lib, ops as ms, sharding
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    shard = sharding.make_shard(cfg["B"], cfg["H"], world, rank)
+    job = make_job(cfg, shard, device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def sum_over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return t.item()
+
+    total_cells = sum_over_ranks(float(job["cells"]))
+
+    # ---- device-resident throughput ("value") ----
+    for _ in range(args.warmup):
+        run_ops(ms, cfg, job)
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        run_ops(ms, cfg, job)
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = ms_total / args.steps
+    value = total_cells / (ms_per_step * 1e-3)
+
+    # ---- per-kernel device time of the same steps (separate pass: events around every launch) ----
+    _lib.kernel_timing(True)
+    for _ in range(min(args.steps, 3)):
+        run_ops(ms, cfg, job)
+    torch.cuda.synchronize()
+    report = _lib.kernel_timing_report()
+    _lib.kernel_timing(False)
+    roofline, kernels = None, []
+    if rank == 0 and report:
+        tot = sum(r[1] for r in report)
+        kernels = [{"kernel": n, "launches": l, "ms_per_launch": t / l, "share": t / tot} for n, t, l in report]
+        name, t, l = max((r for r in report if not r[0].startswith("prepare")), key=lambda r: r[1])
+        tf32_burst, tf32_sust = measure_tf32_peak(device)
+        fl = 2.0 * C_FEAT * job["cells"]            # one contraction over this rank's cells per launch
+        achieved = fl / (t / l * 1e-3) / 1e12
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        bpc = DRAM_BYTES_PER_CELL.get(name)
+        roofline = {"bound": "tensor", "kernel": name, "achieved": achieved, "peak": tf32_sust, "unit": "TFLOP/s",
+                    "frac": achieved / tf32_sust, "traffic": (bpc * job["cells"]) if bpc else None,
+                    "peak_source": "cuBLAS TF32 8192^3 via torch.matmul measured in this run, sustained (~1 s loop); "
+                                   f"burst {tf32_burst:.1f}; MEASURED_PEAKS.json has no TF32 entry "
+                                   f"(its bf16: {peaks.get('bf16_tflops')} burst / {peaks.get('bf16_tflops_sustained')} sustained)",
+                    "algorithmic_flop_per_launch": fl, "ms_per_launch": t / l}
+
+    # ---- end to end through the public API with host buffers ----
+    e2e = None
+    if not args.no_e2e:
+        runner = E2E(cfg, job, device)
+        for _ in range(min(args.warmup, 3)):
+            runner.step()
+        barrier()
+        e0.record()
+        n_e2e = max(2, min(args.steps, 5))
+        for _ in range(n_e2e):
+            runner.step()
+        e1.record()
+        barrier()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / n_e2e
+        e2e = {"value": total_cells / (ms_e2e * 1e-3), "unit": unit, "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": int(sum_over_ranks(float(runner.h2d))),
+               "d2h_bytes_per_step": int(sum_over_ranks(float(runner.d2h))),
+               "path": "pinned host f1,f2 (B,C,H,W) -> AlternateCorrBlockSepflow(num_levels=1).separate with "
+                       "Conv3d attention -> autograd backward -> all-reduce of attention-parameter grads -> host"}
+        del runner
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu, _, _ = time_cpu(cfg, budget_s=15.0)
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "tf32 operands (fp32 in HBM), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": cfg["name"], "cells_per_step": total_cells, "flop_per_cell": flops_per_cell(cfg),
+                   "sharding": f"batch x rows = {shard.g_batch} x {shard.g_rows}",
+                   "l2": "inputs larger than L2" if args.config >= 3 else "inputs smaller than L2 (launch-bound case)"},
+        "useful_tflops": value * flops_per_cell(cfg) / 1e12,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(cfg) * args.steps,
+        "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,
+    }
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

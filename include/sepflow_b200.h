@@ -100,6 +100,15 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
  * SFB_OK if it is 0, SFB_ERR_DEVICE_TIMEOUT otherwise. */
 int sfb_device_status(const void* workspace, void* stream, int32_t* device_status);
 
+/* Per-kernel timing, off by default; no counterpart in the reference ops (its scripts time whole calls
+ * with torch.utils.benchmark, scripts/test_maxavg_cuda.py:237-265).  While enabled, every kernel launch
+ * is bracketed by CUDA events on the stream it is launched on.  sfb_kernel_timing_enable(1) starts a
+ * fresh measurement, (0) stops; sfb_kernel_timing_read waits for the recorded events and returns the
+ * accumulated device time and launch count of kernel `kernel` (0 <= kernel < sfb_kernel_timing_count()). */
+int sfb_kernel_timing_enable(int on);
+int sfb_kernel_timing_count(void);
+int sfb_kernel_timing_read(int kernel, const char** name, double* total_ms, int64_t* launches);
+
 const char* sfb_status_string(int code);
 const char* sfb_last_error(void);
 int sfb_version(void);

@@ -75,7 +75,7 @@ def _first_argmax(S: torch.Tensor, dim: int) -> torch.Tensor:
     n = S.shape[dim]
     shape = [1] * S.dim()
     shape[dim] = n
-    idx = torch.arange(n, dtype=torch.int64).reshape(shape)
+    idx = torch.arange(n, dtype=torch.int64, device=S.device).reshape(shape)
     cand = torch.where(S == m, idx, torch.full_like(idx, n))
     return cand.min(dim=dim).values
 
@@ -87,8 +87,8 @@ def max_argmax_avg_forward(F1: torch.Tensor, F2: torch.Tensor):
     _, H2, W2, _ = F2.shape
     MA_u = F1.new_empty(B, H1, W1, 2, H2)
     MA_v = F1.new_empty(B, H1, W1, 2, W2)
-    AM_u = torch.empty(B, H1, W1, 1, H2, dtype=torch.int32)
-    AM_v = torch.empty(B, H1, W1, 1, W2, dtype=torch.int32)
+    AM_u = torch.empty(B, H1, W1, 1, H2, dtype=torch.int32, device=F1.device)
+    AM_v = torch.empty(B, H1, W1, 1, W2, dtype=torch.int32, device=F1.device)
     for r0, r1 in _row_chunks(H1, W1, H2, W2):
         S = corr_volume(F1[:, r0:r1], F2)
         MA_u[:, r0:r1, :, 0] = S.max(dim=4).values
@@ -180,7 +180,7 @@ def top2_margins(F1: torch.Tensor, F2: torch.Tensor):
     S = corr_volume(F1.double(), F2.double())
     def gap(dim):
         if S.shape[dim] < 2:
-            return torch.full(S.max(dim=dim).values.shape, float("inf"), dtype=torch.float64)
+            return torch.full(S.max(dim=dim).values.shape, float("inf"), dtype=torch.float64, device=S.device)
         t = S.topk(2, dim=dim).values
         return t.select(dim, 0) - t.select(dim, 1)
     return gap(4), gap(3)

@@ -29,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "sfb_workspace_bytes", "sfb_max_avg_forward", "sfb_max_argmax_avg_forward",
     "sfb_max_argmax_avg_backward", "sfb_compression_forward", "sfb_compression_backward",
     "sfb_corr_volume", "sfb_device_status", "sfb_status_string", "sfb_last_error", "sfb_version",
+    "sfb_kernel_timing_enable", "sfb_kernel_timing_count", "sfb_kernel_timing_read",
 )
 
 
@@ -67,5 +68,29 @@ def load() -> ctypes.CDLL:
     lib.sfb_last_error.argtypes = []
     lib.sfb_version.restype = ctypes.c_int
     lib.sfb_version.argtypes = []
+    lib.sfb_kernel_timing_enable.restype = ctypes.c_int
+    lib.sfb_kernel_timing_enable.argtypes = [ctypes.c_int]
+    lib.sfb_kernel_timing_count.restype = ctypes.c_int
+    lib.sfb_kernel_timing_count.argtypes = []
+    lib.sfb_kernel_timing_read.restype = ctypes.c_int
+    lib.sfb_kernel_timing_read.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                           ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_int64)]
     _lib = lib
     return lib
+
+
+def kernel_timing(enable: bool) -> None:
+    """Start (True) or stop (False) a fresh per-kernel timing measurement."""
+    load().sfb_kernel_timing_enable(1 if enable else 0)
+
+
+def kernel_timing_report():
+    """[(kernel name, total device ms, launches)] for every kernel that ran since timing was enabled."""
+    lib = load()
+    rows = []
+    for i in range(lib.sfb_kernel_timing_count()):
+        name, ms, n = ctypes.c_char_p(), ctypes.c_double(), ctypes.c_int64()
+        lib.sfb_kernel_timing_read(i, ctypes.byref(name), ctypes.byref(ms), ctypes.byref(n))
+        if n.value:
+            rows.append((name.value.decode(), ms.value, n.value))
+    return rows

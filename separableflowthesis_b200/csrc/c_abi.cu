@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "../../include/sepflow_b200.h"
 #include "kernels.h"
@@ -65,6 +66,62 @@ int make_map(CUtensorMap* tm, const float* base, int rank, const uint64_t* dims,
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- optional per-kernel timing (off by default): CUDA events around each launch on its own stream ----
+enum KernelId : int {
+  KID_PREPARE = 0, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
+  KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_COUNT
+};
+const char* const kKernelNames[KID_COUNT] = {
+    "prepare(round_copy+f2_means)", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
+    "grad_gemm_kernel<maxavg,image1-major>", "grad_gemm_kernel<maxavg,image2-major>",
+    "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>"};
+struct TimingRec { cudaEvent_t e0, e1; int id; int launches; };
+std::mutex g_timing_mu;
+bool g_timing_on = false;
+std::vector<TimingRec> g_timing_pending;
+std::vector<cudaEvent_t> g_event_pool;
+double g_timing_ms[KID_COUNT] = {0};
+long long g_timing_launches[KID_COUNT] = {0};
+
+cudaEvent_t take_event() {
+  if (!g_event_pool.empty()) { cudaEvent_t e = g_event_pool.back(); g_event_pool.pop_back(); return e; }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+
+template <class Launch>
+cudaError_t timed(int id, int launches, cudaStream_t st, Launch&& launch) {
+  bool on;
+  TimingRec rec{nullptr, nullptr, id, launches};
+  {
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    on = g_timing_on;
+    if (on) { rec.e0 = take_event(); rec.e1 = take_event(); }
+  }
+  if (on) cudaEventRecord(rec.e0, st);
+  cudaError_t err = launch();
+  if (on) {
+    cudaEventRecord(rec.e1, st);
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    g_timing_pending.push_back(rec);
+  }
+  return err;
+}
+
+void drain_timing_locked() {
+  for (TimingRec& r : g_timing_pending) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(r.e1) == cudaSuccess && cudaEventElapsedTime(&ms, r.e0, r.e1) == cudaSuccess) {
+      g_timing_ms[r.id] += ms;
+      g_timing_launches[r.id] += r.launches;
+    }
+    g_event_pool.push_back(r.e0);
+    g_event_pool.push_back(r.e1);
+  }
+  g_timing_pending.clear();
+}
 
 struct Workspace {
   int* status;
@@ -174,14 +231,14 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
   SFB_TRY(map_aux(&tm_aux, d, w.aux));
-  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st));
+  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st); }));
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
   a.ma_u = MA_u; a.ma_v = MA_v; a.am_u = AM_u; a.am_v = AM_v;
   a.status = w.status;
-  SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_aux, st));
+  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
   return SFB_OK;
 }
 
@@ -197,7 +254,7 @@ int run_compress_sweeps(const Dims& d, const Workspace& w, const CUtensorMap& tm
     a.kc = (d.Kc - k0 < KC_MAX_PER_SWEEP) ? d.Kc - k0 : KC_MAX_PER_SWEEP;
     a.w_u = w_u; a.w_v = w_v; a.c_u = c_u; a.c_v = c_v;
     a.status = w.status;
-    SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st));
+    SFB_CUDA(timed(KID_SWEEP_COMPRESS, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));
   }
   return SFB_OK;
 }
@@ -210,12 +267,13 @@ int run_grad_pair(const Dims& d, const Workspace& w, GradArgs a, float* gF1, flo
   SFB_TRY(map_f2_tile(&tm_y, d, w.F2r, GG_UT, GG_VT, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
   a.image2_major = 0;
   a.out = gF1;
-  SFB_CUDA(launch_grad_gemm(a, tm_y, st));
+  const int kid = a.mode == GRAD_MAXAVG ? KID_GRAD_MAXAVG_IMG1 : KID_GRAD_COMPRESS_IMG1;
+  SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(a, tm_y, st); }));
   // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1.
   SFB_TRY(map_f1_rows(&tm_y, d, w.F1r, GG_KJ, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
   a.image2_major = 1;
   a.out = gF2;
-  SFB_CUDA(launch_grad_gemm(a, tm_y, st));
+  SFB_CUDA(timed(kid + 1, 1, st, [&] { return launch_grad_gemm(a, tm_y, st); }));
   return SFB_OK;
 }
 
@@ -253,7 +311,7 @@ int sfb_compression_forward(const float* F1, const float* F2, const float* A_u, 
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
   return run_compress_sweeps(d, w, tm_f1, tm_f2, A_u, A_v, C_u, C_v, st);
 }
 
@@ -267,7 +325,7 @@ int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t*
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
   GradArgs a;
   memset(&a, 0, sizeof(a));
   a.mode = GRAD_MAXAVG;
@@ -289,7 +347,7 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
   // gA_v[p,k,u] = sum_v S * gC_v[p,k,v]  and  gA_u[p,k,v] = sum_u S * gC_u[p,k,u]: the forward
   // compression sweep with the upstream gradients in the role of the weights.
   SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, gC_v, gC_u, gA_v, gA_u, st));
@@ -311,14 +369,14 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = SWEEP_DUMP;
   a.dump = S;
   a.status = w.status;
-  SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st));
+  SFB_CUDA(timed(KID_SWEEP_DUMP, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));
   return SFB_OK;
 }
 
@@ -347,6 +405,26 @@ const char* sfb_status_string(int code) {
 }
 
 const char* sfb_last_error(void) { return g_err; }
+
+int sfb_kernel_timing_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_timing_mu);
+  drain_timing_locked();
+  g_timing_on = on != 0;
+  for (int i = 0; i < KID_COUNT; ++i) { g_timing_ms[i] = 0; g_timing_launches[i] = 0; }
+  return SFB_OK;
+}
+
+int sfb_kernel_timing_count(void) { return KID_COUNT; }
+
+int sfb_kernel_timing_read(int kernel, const char** name, double* total_ms, int64_t* launches) {
+  if (kernel < 0 || kernel >= KID_COUNT) return fail(SFB_ERR_INVALID_ARGUMENT, "kernel index %d out of range", kernel);
+  std::lock_guard<std::mutex> lk(g_timing_mu);
+  drain_timing_locked();
+  if (name) *name = kKernelNames[kernel];
+  if (total_ms) *total_ms = g_timing_ms[kernel];
+  if (launches) *launches = g_timing_launches[kernel];
+  return SFB_OK;
+}
 
 int sfb_version(void) { return 100; }
 

@@ -1,0 +1,227 @@
+"""GPU parity tests: the CUDA ops (called through the ctypes binding of the C ABI) against the
+oracle on the same seeded inputs.
+
+Tolerances.  The device path multiplies TF32-rounded operands (round-to-nearest, 2^-11 relative)
+and accumulates in FP32; for S ~ N(0,1) that is ~4e-4 absolute per entry.  Values and gradients
+must agree with the float64 oracle to TOL = 1e-3 in the reference's own error measure
+max|x - ref| / max(|x|max, |ref|max) (scripts/test_model.py:251-256).  An argmax must be
+bit-identical wherever the float64 gap between the best and second-best entry exceeds
+MARGIN = 5e-3, and must always point at an entry within TOL of the maximum.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import separableflowthesis_b200 as sfb
+from separableflowthesis_b200 import ops
+from oracle import separation_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+MARGIN = 5e-3
+
+# (B, H1, W1, H2, W2, C, Kc): tiny, ragged/odd, pooled levels, C not a multiple of 32, Kc above one sweep
+SHAPES = [
+    (1, 1, 1, 1, 1, 4, 1),
+    (1, 3, 5, 3, 5, 8, 1),
+    (1, 8, 16, 8, 16, 32, 2),
+    (2, 11, 19, 9, 21, 100, 3),
+    (1, 17, 23, 8, 11, 64, 5),     # level-1 sized image 2, Kc > 4 -> two compression sweeps
+    (3, 16, 16, 2, 2, 256, 2),     # level-3 sized image 2
+    (1, 9, 130, 9, 130, 36, 4),    # more than one 128-pixel row tile per image row, W2 > 128
+    (2, 48, 64, 48, 64, 256, 2),   # BASELINE config 2 at full size
+]
+
+
+def relerr(x, ref):
+    x = x.detach().double().cpu()
+    ref = ref.detach().double().cpu()
+    den = max(x.abs().max().item(), ref.abs().max().item(), 1e-30)
+    return (x - ref).abs().max().item() / den
+
+
+def make_inputs(shape, seed):
+    B, H1, W1, H2, W2, C, Kc = shape
+    g = torch.Generator().manual_seed(seed)
+    F1 = torch.randn(B, H1, W1, C, generator=g) / C ** 0.5
+    F2 = torch.randn(B, H2, W2, C, generator=g)
+    A_u = torch.randn(B, H1, W1, Kc, W2, generator=g).softmax(-1)
+    A_v = torch.randn(B, H1, W1, Kc, H2, generator=g).softmax(-1)
+    return F1, F2, A_u, A_v, g
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_corr_volume(shape, cuda_device):
+    if shape[1] * shape[2] * shape[3] * shape[4] > 1 << 22:
+        pytest.skip("dense dump only for small cases")
+    F1, F2, *_ = make_inputs(shape, 0)
+    S = ops.corr_volume(F1.to(cuda_device), F2.to(cuda_device))
+    assert relerr(S, orc.corr_volume(F1.double(), F2.double())) < TOL
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_max_argmax_avg_forward(shape, cuda_device):
+    F1, F2, *_ = make_inputs(shape, 1)
+    MA_u, MA_v, AM_u, AM_v = ops.max_argmax_avg_forward(F1.to(cuda_device), F2.to(cuda_device))
+    r_u, r_v, ra_u, ra_v = orc.max_argmax_avg_forward(F1.double(), F2.double())
+    assert MA_u.shape == r_u.shape and MA_v.shape == r_v.shape
+    assert AM_u.shape == ra_u.shape and AM_v.shape == ra_v.shape and AM_u.dtype == torch.int32
+    for ch in (0, 1):
+        assert relerr(MA_u[..., ch, :], r_u[..., ch, :]) < TOL
+        assert relerr(MA_v[..., ch, :], r_v[..., ch, :]) < TOL
+    gap_u, gap_v = orc.top2_margins(F1, F2)
+    AM_u, AM_v = AM_u.cpu(), AM_v.cpu()
+    assert ((AM_u[..., 0, :] == ra_u[..., 0, :]) | (gap_u <= MARGIN)).all()
+    assert ((AM_v[..., 0, :] == ra_v[..., 0, :]) | (gap_v <= MARGIN)).all()
+    # whatever index was chosen holds a value within tolerance of the maximum, and is in range
+    S = orc.corr_volume(F1.double(), F2.double())
+    assert (AM_u >= 0).all() and (AM_u < shape[4]).all() and (AM_v >= 0).all() and (AM_v < shape[3]).all()
+    scale = max(S.abs().max().item(), 1e-30)
+    picked_u = S.gather(4, AM_u[..., 0, :].long().unsqueeze(-1)).squeeze(-1)
+    picked_v = S.gather(3, AM_v[..., 0, :].long().unsqueeze(-2)).squeeze(-2)
+    assert ((r_u[..., 0, :] - picked_u).abs().max() / scale) < TOL
+    assert ((r_v[..., 0, :] - picked_v).abs().max() / scale) < TOL
+    # the inference variant returns the same max/mean channels, bit for bit
+    MA_u2, MA_v2 = ops.max_avg_forward(F1.to(cuda_device), F2.to(cuda_device))
+    assert torch.equal(MA_u2, MA_u) and torch.equal(MA_v2, MA_v)
+
+
+def test_argmax_ties_lowest_index(cuda_device):
+    """Duplicated image-2 pixels give bit-identical S entries; the lower index must win
+    (MemorySaver_kernel_forward.cu:498-507)."""
+    g = torch.Generator().manual_seed(3)
+    B, H1, W1, H2, W2, C = 1, 6, 9, 20, 40, 64
+    F1 = torch.randn(B, H1, W1, C, generator=g) / 8
+    base = torch.randn(B, 1, 1, C, generator=g)
+    F2 = base.expand(B, H2, W2, C).contiguous()          # all pixels equal: every row/column is one big tie
+    _, _, AM_u, AM_v = ops.max_argmax_avg_forward(F1.to(cuda_device), F2.to(cuda_device))
+    assert (AM_u == 0).all() and (AM_v == 0).all()
+    F2 = torch.randn(B, H2, W2, C, generator=g)
+    F2[:, :, 17] = F2[:, :, 3]                            # column 17 duplicates column 3
+    F2[:, 12] = F2[:, 5]                                  # row 12 duplicates row 5 (after the column copy)
+    _, _, AM_u, AM_v = ops.max_argmax_avg_forward(F1.to(cuda_device), F2.to(cuda_device))
+    assert not (AM_u == 17).any() and not (AM_v == 12).any()
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_compression_forward(shape, cuda_device):
+    F1, F2, A_u, A_v, _ = make_inputs(shape, 2)
+    C_u, C_v = ops.compression_forward(*[t.to(cuda_device) for t in (F1, F2, A_u, A_v)])
+    r_u, r_v = orc.compression_forward(F1.double(), F2.double(), A_u.double(), A_v.double())
+    assert C_u.shape == r_u.shape and C_v.shape == r_v.shape
+    assert relerr(C_u, r_u) < TOL and relerr(C_v, r_v) < TOL
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_max_argmax_avg_backward(shape, cuda_device):
+    """The backward op takes the argmax as an input (MemorySaver_cuda.cpp:55-61), so it is tested in
+    isolation with the oracle's argmax."""
+    B, H1, W1, H2, W2, C, Kc = shape
+    F1, F2, _, _, g = make_inputs(shape, 4)
+    _, _, AM_u, AM_v = orc.max_argmax_avg_forward(F1.double(), F2.double())
+    gMA_u = torch.randn(B, H1, W1, 2, H2, generator=g)
+    gMA_v = torch.randn(B, H1, W1, 2, W2, generator=g)
+    gF1, gF2 = ops.max_argmax_avg_backward(*[t.to(cuda_device) for t in (F1, F2, AM_u, AM_v, gMA_u, gMA_v)])
+    r1, r2 = orc.max_argmax_avg_backward(F1.double(), F2.double(), AM_u, AM_v, gMA_u.double(), gMA_v.double())
+    assert relerr(gF1, r1) < TOL and relerr(gF2, r2) < TOL
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_compression_backward(shape, cuda_device):
+    B, H1, W1, H2, W2, C, Kc = shape
+    F1, F2, A_u, A_v, g = make_inputs(shape, 5)
+    gC_u = torch.randn(B, H1, W1, Kc, H2, generator=g)
+    gC_v = torch.randn(B, H1, W1, Kc, W2, generator=g)
+    args = (F1, F2, A_u, A_v, gC_u, gC_v)
+    out = ops.compression_backward(*[t.to(cuda_device) for t in args])
+    ref = orc.compression_backward(*[t.double() for t in args])
+    for name, x, r in zip(("gF1", "gF2", "gA_u", "gA_v"), out, ref):
+        assert x.shape == r.shape, name
+        assert relerr(x, r) < TOL, name
+
+
+def test_backward_is_deterministic(cuda_device):
+    """Gradients accumulate in TMEM, not with atomics: two runs are bit-identical."""
+    shape = (2, 24, 40, 24, 40, 128, 2)
+    B, H1, W1, H2, W2, C, Kc = shape
+    F1, F2, A_u, A_v, g = make_inputs(shape, 6)
+    gC_u = torch.randn(B, H1, W1, Kc, H2, generator=g)
+    gC_v = torch.randn(B, H1, W1, Kc, W2, generator=g)
+    args = [t.to(cuda_device) for t in (F1, F2, A_u, A_v, gC_u, gC_v)]
+    a = ops.compression_backward(*args)
+    b = ops.compression_backward(*args)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_golden_op_vectors(golden_dir, cuda_device):
+    """CUDA ops against the vectors produced by the reference's own test definitions."""
+    gold = np.load(os.path.join(golden_dir, "ops_b2_c12_8x12_k3.npz"))
+    F1 = torch.from_numpy(gold["F1"]).float().to(cuda_device)
+    F2 = torch.from_numpy(gold["F2"]).float().to(cuda_device)
+    for level in range(3):
+        x = F2.permute(0, 3, 1, 2)
+        for _ in range(level):
+            x = F.avg_pool2d(x, 2, stride=2)
+        F2l = x.permute(0, 2, 3, 1).contiguous()
+        MA_u, MA_v = ops.max_avg_forward(F1, F2l)
+        for name, ours in (("max_u", MA_u[..., 0, :]), ("avg_u", MA_u[..., 1, :]),
+                           ("max_v", MA_v[..., 0, :]), ("avg_v", MA_v[..., 1, :])):
+            ref = torch.from_numpy(gold[f"l{level}_{name}"]).permute(0, 2, 3, 1)
+            assert relerr(ours, ref) < TOL, (level, name)
+        A_u = torch.from_numpy(gold[f"l{level}_A_u"]).float().to(cuda_device)
+        A_v = torch.from_numpy(gold[f"l{level}_A_v"]).float().to(cuda_device)
+        C_u, C_v = ops.compression_forward(F1, F2l, A_u, A_v)
+        assert relerr(C_u, torch.from_numpy(gold[f"l{level}_C_u"]).permute(0, 3, 4, 1, 2)) < TOL
+        assert relerr(C_v, torch.from_numpy(gold[f"l{level}_C_v"]).permute(0, 3, 4, 1, 2)) < TOL
+
+
+def test_block_against_reference_dense_vectors(golden_dir, cuda_device):
+    """The whole call site (4 pyramid levels, Conv3d attention, autograd) on the GPU against the
+    vectors of the reference's dense CorrBlock.  Gradients flow through argmax choices; the seeded
+    case has no near-ties at the MARGIN level, so the same tolerance applies."""
+    gold = np.load(os.path.join(golden_dir, "block_dense_b2_c16_9x11_k2.npz"))
+    f1 = torch.from_numpy(gold["f1"]).float().to(cuda_device).requires_grad_(True)
+    f2 = torch.from_numpy(gold["f2"]).float().to(cuda_device).requires_grad_(True)
+    convs = []
+    for i in range(2):
+        conv = torch.nn.Conv3d(2, gold["w0"].shape[0], 3, padding=1).to(cuda_device)
+        with torch.no_grad():
+            conv.weight.copy_(torch.from_numpy(gold[f"w{i}"]).float())
+            conv.bias.copy_(torch.from_numpy(gold[f"b{i}"]).float())
+        convs.append(conv)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True)
+    sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(convs))
+    assert relerr(sep_u, torch.from_numpy(gold["sep_u"])) < TOL
+    assert relerr(sep_v, torch.from_numpy(gold["sep_v"])) < TOL
+    gen = torch.Generator().manual_seed(int(gold["loss_seed"]))
+    wu = torch.randn(sep_u.shape, generator=gen, dtype=torch.float64).float().to(cuda_device)
+    wv = torch.randn(sep_v.shape, generator=gen, dtype=torch.float64).float().to(cuda_device)
+    ((sep_u * wu).sum() + (sep_v * wv).sum()).backward()
+    assert relerr(f1.grad, torch.from_numpy(gold["g_f1"])) < 2 * TOL
+    assert relerr(f2.grad, torch.from_numpy(gold["g_f2"])) < 2 * TOL
+    for i, conv in enumerate(convs):
+        gw = torch.from_numpy(gold[f"g_w{i}"])
+        assert relerr(conv.weight.grad, gw) < 2 * TOL
+        # a bias shifts all logits of a softmax equally, so its gradient is ~0: compare on the weights' scale
+        gb_err = (conv.bias.grad.double().cpu() - torch.from_numpy(gold[f"g_b{i}"])).abs().max().item()
+        assert gb_err < 2 * TOL * gw.abs().max().item()
+
+
+def test_ops_reject_bad_inputs(cuda_device):
+    F1 = torch.randn(1, 4, 4, 8, device=cuda_device)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        ops.max_avg_forward(F1.permute(0, 2, 1, 3), F1)
+    with pytest.raises(RuntimeError, match="dtype"):
+        ops.max_avg_forward(F1.half(), F1.half())
+    with pytest.raises(RuntimeError, match="feature dimensions differ"):
+        ops.max_avg_forward(F1, torch.randn(1, 4, 4, 12, device=cuda_device))
+    with pytest.raises(RuntimeError, match="unsupported"):
+        ops.max_avg_forward(torch.randn(1, 4, 4, 6, device=cuda_device), torch.randn(1, 4, 4, 6, device=cuda_device))
+    with pytest.raises(RuntimeError, match="shape"):
+        ops.compression_forward(F1, F1, torch.randn(1, 4, 4, 2, 5, device=cuda_device),
+                                torch.randn(1, 4, 4, 2, 4, device=cuda_device))
