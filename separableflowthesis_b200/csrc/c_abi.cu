@@ -69,11 +69,11 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ---- optional per-kernel timing (off by default): CUDA events around each launch on its own stream ----
 enum KernelId : int {
-  KID_PREPARE = 0, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
+  KID_PREPARE = 0, KID_PACK, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
   KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_COUNT
 };
 const char* const kKernelNames[KID_COUNT] = {
-    "prepare(round_copy+f2_means)", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
+    "prepare(round_copy+f2_means)", "pack_transposed_kernel", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
     "grad_gemm_kernel<maxavg,image1-major>", "grad_gemm_kernel<maxavg,image2-major>",
     "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>"};
 struct TimingRec { cudaEvent_t e0, e1; int id; int launches; };
@@ -128,10 +128,16 @@ struct Workspace {
   float* F1r;
   float* F2r;
   float* aux;
+  float* xu;   // packed (pixel,u) operands of the gradient GEMMs, (B, H2, R, n1p)
+  float* xv;   // packed (pixel,v) operands, (B, W2, R, n1p)
+  int n1p;
   size_t bytes;
 };
 
-Workspace carve(const Dims& d, void* base, bool with_aux) {
+int padded_pixels(const Dims& d) { return (d.N1() + TILE_M - 1) / TILE_M * TILE_M; }
+
+// pack_R: slots of the packed gradient operands (0 for the forward ops).
+Workspace carve(const Dims& d, void* base, bool with_aux, int pack_R = 0) {
   Workspace w;
   size_t off = 0;
   char* p = static_cast<char*>(base);
@@ -145,6 +151,14 @@ Workspace carve(const Dims& d, void* base, bool with_aux) {
   if (with_aux) {
     w.aux = reinterpret_cast<float*>(p + off);
     off += align_up((size_t)d.B * d.aux_rows() * d.C * sizeof(float), 256);
+  }
+  w.xu = w.xv = nullptr;
+  w.n1p = padded_pixels(d);
+  if (pack_R > 0) {
+    w.xu = reinterpret_cast<float*>(p + off);
+    off += align_up((size_t)d.B * d.H2 * pack_R * w.n1p * sizeof(float), 256);
+    w.xv = reinterpret_cast<float*>(p + off);
+    off += align_up((size_t)d.B * d.W2 * pack_R * w.n1p * sizeof(float), 256);
   }
   w.bytes = off;
   return w;
@@ -187,11 +201,11 @@ int check_ptr(const void* p, const char* name) {
     if (e_ != cudaSuccess) return fail(SFB_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_));  \
   } while (0)
 
-int check_workspace(const Dims& d, void* ws, size_t ws_bytes, bool with_aux, Workspace* out) {
+int check_workspace(const Dims& d, void* ws, size_t ws_bytes, bool with_aux, Workspace* out, int pack_R = 0) {
   if (ws == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "workspace is NULL");
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0)
     return fail(SFB_ERR_INVALID_ARGUMENT, "workspace is not 256-byte aligned");
-  *out = carve(d, ws, with_aux);
+  *out = carve(d, ws, with_aux, pack_R);
   if (ws_bytes < out->bytes)
     return fail(SFB_ERR_WORKSPACE_TOO_SMALL, "workspace has %zu bytes, %zu needed", ws_bytes, out->bytes);
   return SFB_OK;
@@ -259,15 +273,27 @@ int run_compress_sweeps(const Dims& d, const Workspace& w, const CUtensorMap& tm
   return SFB_OK;
 }
 
-int run_grad_pair(const Dims& d, const Workspace& w, GradArgs a, float* gF1, float* gF2, cudaStream_t st) {
+constexpr int MAXAVG_PACK_R = 3;
+int compress_pack_R(const Dims& d) { return 2 * (d.Kc < KC_MAX_PER_SWEEP ? d.Kc : KC_MAX_PER_SWEEP); }
+
+int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R, int accumulate, float* gF1, float* gF2,
+                  cudaStream_t st) {
   CUtensorMap tm_y;
+  GradArgs a;
+  memset(&a, 0, sizeof(a));
   a.d = d;
+  a.mode = mode;
+  a.R = R;
+  a.n1p = w.n1p;
+  a.accumulate = accumulate;
+  a.xu = w.xu;
+  a.xv = w.xv;
   a.status = w.status;
   // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2.
   SFB_TRY(map_f2_tile(&tm_y, d, w.F2r, GG_UT, GG_VT, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
   a.image2_major = 0;
   a.out = gF1;
-  const int kid = a.mode == GRAD_MAXAVG ? KID_GRAD_MAXAVG_IMG1 : KID_GRAD_COMPRESS_IMG1;
+  const int kid = mode == GRAD_MAXAVG ? KID_GRAD_MAXAVG_IMG1 : KID_GRAD_COMPRESS_IMG1;
   SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(a, tm_y, st); }));
   // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1.
   SFB_TRY(map_f1_rows(&tm_y, d, w.F1r, GG_KJ, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
@@ -285,7 +311,14 @@ size_t sfb_workspace_bytes(int op, const sfb_shape* shape) {
   Dims d;
   if (check_shape(shape, false, &d) != SFB_OK) return 0;
   if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_CORR_VOLUME) return 0;
-  return carve(d, nullptr, op == SFB_OP_MAX_AVG_FORWARD).bytes;
+  int pack_R = 0;
+  if (op == SFB_OP_MAX_ARGMAX_AVG_BACKWARD) pack_R = MAXAVG_PACK_R;
+  if (op == SFB_OP_COMPRESSION_BACKWARD) {
+    if (shape->Kc < 1) return 0;
+    d.Kc = shape->Kc;
+    pack_R = compress_pack_R(d);
+  }
+  return carve(d, nullptr, op == SFB_OP_MAX_AVG_FORWARD, pack_R).bytes;
 }
 
 int sfb_max_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, const sfb_shape* shape,
@@ -323,14 +356,20 @@ int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t*
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v);
   SFB_CHECK_PTR(gMA_u); SFB_CHECK_PTR(gMA_v); SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2);
   Workspace w;
-  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w, MAXAVG_PACK_R));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
-  GradArgs a;
-  memset(&a, 0, sizeof(a));
-  a.mode = GRAD_MAXAVG;
-  a.am_u = AM_u; a.am_v = AM_v; a.gma_u = gMA_u; a.gma_v = gMA_v;
-  return run_grad_pair(d, w, a, gF1, gF2, st);
+  // packed operands: slot 0 = mean-gradient / row length, slot 1 = max-gradient, slot 2 = argmax (raw bits)
+  SFB_CUDA(timed(KID_PACK, 6, st, [&] {
+    const int N1 = d.N1(), R = MAXAVG_PACK_R;
+    launch_pack_transposed(gMA_u, w.xu, d.B, N1, w.n1p, 2, 1, d.H2, R, 0, 1.f / (float)d.W2, st);
+    launch_pack_transposed(gMA_u, w.xu, d.B, N1, w.n1p, 2, 0, d.H2, R, 1, 0.f, st);
+    launch_pack_transposed(AM_u, w.xu, d.B, N1, w.n1p, 1, 0, d.H2, R, 2, 0.f, st);
+    launch_pack_transposed(gMA_v, w.xv, d.B, N1, w.n1p, 2, 1, d.W2, R, 0, 1.f / (float)d.H2, st);
+    launch_pack_transposed(gMA_v, w.xv, d.B, N1, w.n1p, 2, 0, d.W2, R, 1, 0.f, st);
+    return launch_pack_transposed(AM_v, w.xv, d.B, N1, w.n1p, 1, 0, d.W2, R, 2, 0.f, st);
+  }));
+  return run_grad_pair(d, w, GRAD_MAXAVG, MAXAVG_PACK_R, 0, gF1, gF2, st);
 }
 
 int sfb_compression_backward(const float* F1, const float* F2, const float* A_u, const float* A_v,
@@ -342,7 +381,7 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(gC_u); SFB_CHECK_PTR(gC_v);
   SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2); SFB_CHECK_PTR(gA_u); SFB_CHECK_PTR(gA_v);
   Workspace w;
-  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w, compress_pack_R(d)));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
@@ -351,11 +390,24 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   // gA_v[p,k,u] = sum_v S * gC_v[p,k,v]  and  gA_u[p,k,v] = sum_u S * gC_u[p,k,u]: the forward
   // compression sweep with the upstream gradients in the role of the weights.
   SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, gC_v, gC_u, gA_v, gA_u, st));
-  GradArgs a;
-  memset(&a, 0, sizeof(a));
-  a.mode = GRAD_COMPRESS;
-  a.a_u = A_u; a.a_v = A_v; a.gc_u = gC_u; a.gc_v = gC_v;
-  return run_grad_pair(d, w, a, gF1, gF2, st);
+  // gradient GEMMs, at most KC_MAX_PER_SWEEP channels per pass; later passes add to gF1 / gF2.
+  // packed slots per channel k: XU (gC_u, A_v), XV (A_u, gC_v), so that G = sum_slots XU * XV.
+  for (int k0 = 0; k0 < d.Kc; k0 += KC_MAX_PER_SWEEP) {
+    const int kc = (d.Kc - k0 < KC_MAX_PER_SWEEP) ? d.Kc - k0 : KC_MAX_PER_SWEEP;
+    const int R = 2 * kc, N1 = d.N1();
+    SFB_CUDA(timed(KID_PACK, 4 * kc, st, [&] {
+      cudaError_t e = cudaSuccess;
+      for (int k = 0; k < kc; ++k) {
+        launch_pack_transposed(gC_u, w.xu, d.B, N1, w.n1p, d.Kc, k0 + k, d.H2, R, 2 * k, 0.f, st);
+        launch_pack_transposed(A_v, w.xu, d.B, N1, w.n1p, d.Kc, k0 + k, d.H2, R, 2 * k + 1, 0.f, st);
+        launch_pack_transposed(A_u, w.xv, d.B, N1, w.n1p, d.Kc, k0 + k, d.W2, R, 2 * k, 0.f, st);
+        e = launch_pack_transposed(gC_v, w.xv, d.B, N1, w.n1p, d.Kc, k0 + k, d.W2, R, 2 * k + 1, 0.f, st);
+      }
+      return e;
+    }));
+    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R, k0 > 0 ? 1 : 0, gF1, gF2, st));
+  }
+  return SFB_OK;
 }
 
 int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,

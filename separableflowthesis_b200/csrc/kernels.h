@@ -41,14 +41,22 @@ struct SweepArgs {
   int* status;           // device status word
 };
 
+// Gradient GEMM.  G = dLoss/dS is generated from two "packed" operand sets laid out with the image-1
+// pixel index fastest, so that one warp reads 32 consecutive pixels with one 128-byte request:
+//   XU (B, H2, R, N1p)  values that depend on (pixel, u);  XV (B, W2, R, N1p)  values that depend on (pixel, v)
+// N1p = N1 rounded up to a multiple of 128, padding is zero.
+//   GRAD_COMPRESS: G[p,u,v] = sum_r XU[u,r,p] * XV[v,r,p]            (R = 2 * channels of this launch)
+//   GRAD_MAXAVG  : R = 3, slots (mean-gradient already divided by the row length, max-gradient, argmax bits):
+//                  G[p,u,v] = XU[u,0,p] + XV[v,0,p] + (XU[u,2,p]==v ? XU[u,1,p] : 0) + (XV[v,2,p]==u ? XV[v,1,p] : 0)
 struct GradArgs {
   Dims d;
   int mode;
   int image2_major;      // 0: rows = image-1 pixels, output gF1; 1: rows = image-2 pixels, output gF2
-  // GRAD_MAXAVG inputs
-  const int32_t* am_u; const int32_t* am_v; const float* gma_u; const float* gma_v;
-  // GRAD_COMPRESS inputs
-  const float* a_u; const float* a_v; const float* gc_u; const float* gc_v;
+  int R;                 // slots per (u | v) in the packed operands
+  int n1p;               // padded pixel count of the packed operands
+  int accumulate;        // 0: out = result, 1: out += result (later channel chunks of the compression op)
+  const float* xu;
+  const float* xv;
   float* out;            // gF1 (B,N1,C) or gF2 (B,N2,C)
   int* status;
 };
@@ -57,6 +65,10 @@ struct GradArgs {
 // row/column mean rows of F2, and clears the status word.
 cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
                            int* status, cudaStream_t stream);
+// dst[b][d][r][p] = scale * src[b][p][ksrc][d]  (raw 32-bit copy when scale == 0), zero for N1 <= p < n1p.
+// src is (B, N1, Ksrc, D), dst is (B, D, R, n1p).
+cudaError_t launch_pack_transposed(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc, int D,
+                                   int R, int r, float scale, cudaStream_t stream);
 cudaError_t launch_sweep(const SweepArgs& a, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
                          const CUtensorMap& tm_aux, cudaStream_t stream);
 cudaError_t launch_grad_gemm(const GradArgs& a, const CUtensorMap& tm_y, cudaStream_t stream);

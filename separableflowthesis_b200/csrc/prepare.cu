@@ -41,6 +41,39 @@ __global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict_
   }
 }
 
+// Tiled transpose: reads 32 consecutive displacement indices of 32 pixels (coalesced along d), writes the
+// same 32 x 32 patch with the pixel index fastest (coalesced along p).
+__global__ void pack_transposed_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int N1, int n1p,
+                                       int Ksrc, int ksrc, int D, int R, int r, float scale) {
+  __shared__ uint32_t tile[32][33];
+  const int b = blockIdx.z, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  for (int j = ty; j < 32; j += 8) {
+    const int p = p0 + j, d = d0 + tx;
+    uint32_t v = 0;
+    if (p < N1 && d < D) v = __ldg(src + (((size_t)b * N1 + p) * Ksrc + ksrc) * D + d);
+    tile[j][tx] = v;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int d = d0 + j, p = p0 + tx;
+    if (d < D) {
+      uint32_t v = tile[tx][j];
+      if (scale != 0.f) v = __float_as_uint(__uint_as_float(v) * scale);
+      dst[(((size_t)b * D + d) * R + r) * n1p + p] = v;
+    }
+  }
+}
+
+cudaError_t launch_pack_transposed(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc, int D,
+                                   int R, int r, float scale, cudaStream_t stream) {
+  const dim3 grid(n1p / 32, (D + 31) / 32, B), block(32, 8);
+  pack_transposed_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src),
+                                                     reinterpret_cast<uint32_t*>(dst), N1, n1p, Ksrc, ksrc, D, R, r,
+                                                     scale);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
                            int* status, cudaStream_t stream) {
   cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), stream);
