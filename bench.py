@@ -306,8 +306,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-roofline", action="store_true", help="skip the per-kernel timing pass and the TF32 peak run")
+    ap.add_argument("--batch", type=int, default=0, help="override the batch size (small ncu captures)")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.batch > 0:
+        cfg["B"] = args.batch
+        cfg["name"] += f" [batch overridden to {args.batch}]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -376,12 +381,14 @@ def main():
     value = total_cells / (ms_per_step * 1e-3)
 
     # ---- per-kernel device time of the same steps (separate pass: events around every launch) ----
-    _lib.kernel_timing(True)
-    for _ in range(min(args.steps, 3)):
-        run_ops(ms, cfg, job)
-    torch.cuda.synchronize()
-    report = _lib.kernel_timing_report()
-    _lib.kernel_timing(False)
+    report = []
+    if not args.no_roofline:
+        _lib.kernel_timing(True)
+        for _ in range(min(args.steps, 3)):
+            run_ops(ms, cfg, job)
+        torch.cuda.synchronize()
+        report = _lib.kernel_timing_report()
+        _lib.kernel_timing(False)
     roofline, kernels = None, []
     if rank == 0 and report:
         tot = sum(r[1] for r in report)

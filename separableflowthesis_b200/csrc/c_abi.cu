@@ -73,7 +73,7 @@ enum KernelId : int {
   KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_COUNT
 };
 const char* const kKernelNames[KID_COUNT] = {
-    "prepare(round_copy+f2_means)", "pack_transposed_kernel", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
+    "prepare(round_copy+f2_means)", "pack_kernel/unpack_kernel", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
     "grad_gemm_kernel<maxavg,image1-major>", "grad_gemm_kernel<maxavg,image2-major>",
     "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>"};
 struct TimingRec { cudaEvent_t e0, e1; int id; int launches; };
@@ -128,38 +128,50 @@ struct Workspace {
   float* F1r;
   float* F2r;
   float* aux;
-  float* xu;   // packed (pixel,u) operands of the gradient GEMMs, (B, H2, R, n1p)
-  float* xv;   // packed (pixel,v) operands, (B, W2, R, n1p)
+  float* xu;   // packed inputs indexed by (u, slot, pixel): (B, H2, Rx, n1p)
+  float* xv;   // packed inputs indexed by (v, slot, pixel): (B, W2, Rx, n1p)
+  float* ou;   // packed outputs, (B, H2, Ro, n1p)
+  float* ov;   // packed outputs, (B, W2, Ro, n1p)
   int n1p;
   size_t bytes;
 };
 
 int padded_pixels(const Dims& d) { return (d.N1() + TILE_M - 1) / TILE_M * TILE_M; }
 
-// pack_R: slots of the packed gradient operands (0 for the forward ops).
-Workspace carve(const Dims& d, void* base, bool with_aux, int pack_R = 0) {
+// What an op keeps in the workspace: the mean rows of F2, Rx packed input slots, Ro packed output slots.
+struct WsPlan { bool aux; int Rx; int Ro; };
+constexpr int MAXAVG_SLOTS = 3;  // max, mean, argmax bits
+int chunk_channels(int Kc) { return Kc < KC_MAX_PER_SWEEP ? Kc : KC_MAX_PER_SWEEP; }
+
+WsPlan plan_for(int op, const Dims& d) {
+  switch (op) {
+    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS};
+    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc};
+    case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, MAXAVG_SLOTS, 0};
+    case SFB_OP_COMPRESSION_BACKWARD: return {false, 2 * d.Kc, d.Kc};
+    default: return {false, 0, 0};
+  }
+}
+
+Workspace carve(const Dims& d, void* base, const WsPlan& plan) {
   Workspace w;
   size_t off = 0;
   char* p = static_cast<char*>(base);
+  auto take = [&](size_t floats) {
+    float* r = reinterpret_cast<float*>(p + off);
+    off += align_up(floats * sizeof(float), 256);
+    return r;
+  };
   w.status = reinterpret_cast<int*>(p + off);
   off += 256;
-  w.F1r = reinterpret_cast<float*>(p + off);
-  off += align_up((size_t)d.B * d.N1() * d.C * sizeof(float), 256);
-  w.F2r = reinterpret_cast<float*>(p + off);
-  off += align_up((size_t)d.B * d.N2() * d.C * sizeof(float), 256);
-  w.aux = nullptr;
-  if (with_aux) {
-    w.aux = reinterpret_cast<float*>(p + off);
-    off += align_up((size_t)d.B * d.aux_rows() * d.C * sizeof(float), 256);
-  }
-  w.xu = w.xv = nullptr;
   w.n1p = padded_pixels(d);
-  if (pack_R > 0) {
-    w.xu = reinterpret_cast<float*>(p + off);
-    off += align_up((size_t)d.B * d.H2 * pack_R * w.n1p * sizeof(float), 256);
-    w.xv = reinterpret_cast<float*>(p + off);
-    off += align_up((size_t)d.B * d.W2 * pack_R * w.n1p * sizeof(float), 256);
-  }
+  w.F1r = take((size_t)d.B * d.N1() * d.C);
+  w.F2r = take((size_t)d.B * d.N2() * d.C);
+  w.aux = plan.aux ? take((size_t)d.B * d.aux_rows() * d.C) : nullptr;
+  w.xu = plan.Rx ? take((size_t)d.B * d.H2 * plan.Rx * w.n1p) : nullptr;
+  w.xv = plan.Rx ? take((size_t)d.B * d.W2 * plan.Rx * w.n1p) : nullptr;
+  w.ou = plan.Ro ? take((size_t)d.B * d.H2 * plan.Ro * w.n1p) : nullptr;
+  w.ov = plan.Ro ? take((size_t)d.B * d.W2 * plan.Ro * w.n1p) : nullptr;
   w.bytes = off;
   return w;
 }
@@ -175,6 +187,12 @@ int check_shape(const sfb_shape* s, bool need_kc, Dims* d) {
   if (need_kc && s->Kc < 1) return fail(SFB_ERR_INVALID_ARGUMENT, "Kc must be >= 1 (got %d)", s->Kc);
   if ((long long)s->H1 * s->W1 > (1ll << 30) || (long long)s->H2 * s->W2 > (1ll << 30))
     return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image has more than 2^30 pixels");
+  {  // element offsets inside one sample's packed array are 32-bit in the kernels
+    const long long n1p = ((long long)s->H1 * s->W1 + TILE_M - 1) / TILE_M * TILE_M;
+    const long long slots = need_kc ? 2ll * s->Kc : MAXAVG_SLOTS;
+    if (n1p * slots * (s->H2 > s->W2 ? s->H2 : s->W2) >= (1ll << 32))
+      return fail(SFB_ERR_UNSUPPORTED_SHAPE, "H1*W1*max(H2,W2)*slots exceeds 2^32 elements per sample");
+  }
   d->B = s->B; d->H1 = s->H1; d->W1 = s->W1; d->H2 = s->H2; d->W2 = s->W2; d->C = s->C;
   d->Kc = need_kc ? s->Kc : 0;
   return SFB_OK;
@@ -201,11 +219,11 @@ int check_ptr(const void* p, const char* name) {
     if (e_ != cudaSuccess) return fail(SFB_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_));  \
   } while (0)
 
-int check_workspace(const Dims& d, void* ws, size_t ws_bytes, bool with_aux, Workspace* out, int pack_R = 0) {
+int check_workspace(const Dims& d, void* ws, size_t ws_bytes, int op, Workspace* out) {
   if (ws == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "workspace is NULL");
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0)
     return fail(SFB_ERR_INVALID_ARGUMENT, "workspace is not 256-byte aligned");
-  *out = carve(d, ws, with_aux, pack_R);
+  *out = carve(d, ws, plan_for(op, d));
   if (ws_bytes < out->bytes)
     return fail(SFB_ERR_WORKSPACE_TOO_SMALL, "workspace has %zu bytes, %zu needed", ws_bytes, out->bytes);
   return SFB_OK;
@@ -239,7 +257,7 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(MA_u); SFB_CHECK_PTR(MA_v);
   if (with_argmax) { SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v); }
   Workspace w;
-  SFB_TRY(check_workspace(d, ws, ws_bytes, true, &w));
+  SFB_TRY(check_workspace(d, ws, ws_bytes, SFB_OP_MAX_AVG_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap tm_f1, tm_f2, tm_aux;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
@@ -250,40 +268,57 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
-  a.ma_u = MA_u; a.ma_v = MA_v; a.am_u = AM_u; a.am_v = AM_v;
+  a.n1p = w.n1p;
+  a.pu = w.ou;
+  a.pv = w.ov;
   a.status = w.status;
   SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
+  // packed (displacement, slot, pixel) -> the reference's (pixel, channel, displacement) tensors
+  const int N1 = d.N1(), R = MAXAVG_SLOTS;
+  SFB_CUDA(timed(KID_PACK, with_argmax ? 4 : 2, st, [&] {
+    launch_unpack(w.ou, MA_u, d.B, N1, w.n1p, 2, d.H2, R, 0, 1, 2, 0, st);
+    cudaError_t e = launch_unpack(w.ov, MA_v, d.B, N1, w.n1p, 2, d.W2, R, 0, 1, 2, 0, st);
+    if (with_argmax) {
+      launch_unpack(w.ou, AM_u, d.B, N1, w.n1p, 1, d.H2, R, 2, 1, 1, 0, st);
+      e = launch_unpack(w.ov, AM_v, d.B, N1, w.n1p, 1, d.W2, R, 2, 1, 1, 0, st);
+    }
+    return e;
+  }));
   return SFB_OK;
 }
 
-// C_u-like output = sum_v S * w_u, C_v-like output = sum_u S * w_v, at most KC_MAX_PER_SWEEP channels per sweep.
+// OU slot k = sum_v S * w_u[k], OV slot k = sum_u S * w_v[k] for all Kc channels, at most
+// KC_MAX_PER_SWEEP channels per sweep.  Weights are slots (slot0 + k*stride) of the packed inputs.
 int run_compress_sweeps(const Dims& d, const Workspace& w, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
-                        const float* w_u, const float* w_v, float* c_u, float* c_v, cudaStream_t st) {
+                        int Rw, int wu_slot0, int wv_slot0, int w_stride, cudaStream_t st) {
   for (int k0 = 0; k0 < d.Kc; k0 += KC_MAX_PER_SWEEP) {
     SweepArgs a;
     memset(&a, 0, sizeof(a));
     a.d = d;
     a.mode = SWEEP_COMPRESS;
+    a.n1p = w.n1p;
     a.k0 = k0;
-    a.kc = (d.Kc - k0 < KC_MAX_PER_SWEEP) ? d.Kc - k0 : KC_MAX_PER_SWEEP;
-    a.w_u = w_u; a.w_v = w_v; a.c_u = c_u; a.c_v = c_v;
+    a.kc = chunk_channels(d.Kc - k0);
+    a.xu = w.xu; a.xv = w.xv;
+    a.Rw = Rw; a.wu_slot0 = wu_slot0; a.wv_slot0 = wv_slot0; a.w_stride = w_stride;
+    a.ou = w.ou; a.ov = w.ov;
+    a.Ro = d.Kc;
     a.status = w.status;
     SFB_CUDA(timed(KID_SWEEP_COMPRESS, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));
   }
   return SFB_OK;
 }
 
-constexpr int MAXAVG_PACK_R = 3;
-int compress_pack_R(const Dims& d) { return 2 * (d.Kc < KC_MAX_PER_SWEEP ? d.Kc : KC_MAX_PER_SWEEP); }
-
-int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R, int accumulate, float* gF1, float* gF2,
-                  cudaStream_t st) {
+int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R, int Rtot, int r0, int accumulate, float* gF1,
+                  float* gF2, cudaStream_t st) {
   CUtensorMap tm_y;
   GradArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = mode;
   a.R = R;
+  a.Rtot = Rtot;
+  a.r0 = r0;
   a.n1p = w.n1p;
   a.accumulate = accumulate;
   a.xu = w.xu;
@@ -309,16 +344,10 @@ extern "C" {
 
 size_t sfb_workspace_bytes(int op, const sfb_shape* shape) {
   Dims d;
-  if (check_shape(shape, false, &d) != SFB_OK) return 0;
   if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_CORR_VOLUME) return 0;
-  int pack_R = 0;
-  if (op == SFB_OP_MAX_ARGMAX_AVG_BACKWARD) pack_R = MAXAVG_PACK_R;
-  if (op == SFB_OP_COMPRESSION_BACKWARD) {
-    if (shape->Kc < 1) return 0;
-    d.Kc = shape->Kc;
-    pack_R = compress_pack_R(d);
-  }
-  return carve(d, nullptr, op == SFB_OP_MAX_AVG_FORWARD, pack_R).bytes;
+  const bool need_kc = op == SFB_OP_COMPRESSION_FORWARD || op == SFB_OP_COMPRESSION_BACKWARD;
+  if (check_shape(shape, need_kc, &d) != SFB_OK) return 0;
+  return carve(d, nullptr, plan_for(op, d)).bytes;
 }
 
 int sfb_max_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, const sfb_shape* shape,
@@ -339,13 +368,23 @@ int sfb_compression_forward(const float* F1, const float* F2, const float* A_u, 
   SFB_TRY(check_shape(shape, true, &d));
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(C_u); SFB_CHECK_PTR(C_v);
   Workspace w;
-  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
-  return run_compress_sweeps(d, w, tm_f1, tm_f2, A_u, A_v, C_u, C_v, st);
+  const int N1 = d.N1(), K = d.Kc;
+  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+    launch_pack(A_u, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);         // w_u[k][v] = XV slot k
+    return launch_pack(A_v, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);  // w_v[k][u] = XU slot k
+  }));
+  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, K, 0, 0, 1, st));
+  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+    launch_unpack(w.ou, C_u, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
+    return launch_unpack(w.ov, C_v, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
+  }));
+  return SFB_OK;
 }
 
 int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
@@ -356,20 +395,20 @@ int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t*
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v);
   SFB_CHECK_PTR(gMA_u); SFB_CHECK_PTR(gMA_v); SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2);
   Workspace w;
-  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w, MAXAVG_PACK_R));
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_MAX_ARGMAX_AVG_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
   // packed operands: slot 0 = mean-gradient / row length, slot 1 = max-gradient, slot 2 = argmax (raw bits)
   SFB_CUDA(timed(KID_PACK, 6, st, [&] {
-    const int N1 = d.N1(), R = MAXAVG_PACK_R;
-    launch_pack_transposed(gMA_u, w.xu, d.B, N1, w.n1p, 2, 1, d.H2, R, 0, 1.f / (float)d.W2, st);
-    launch_pack_transposed(gMA_u, w.xu, d.B, N1, w.n1p, 2, 0, d.H2, R, 1, 0.f, st);
-    launch_pack_transposed(AM_u, w.xu, d.B, N1, w.n1p, 1, 0, d.H2, R, 2, 0.f, st);
-    launch_pack_transposed(gMA_v, w.xv, d.B, N1, w.n1p, 2, 1, d.W2, R, 0, 1.f / (float)d.H2, st);
-    launch_pack_transposed(gMA_v, w.xv, d.B, N1, w.n1p, 2, 0, d.W2, R, 1, 0.f, st);
-    return launch_pack_transposed(AM_v, w.xv, d.B, N1, w.n1p, 1, 0, d.W2, R, 2, 0.f, st);
+    const int N1 = d.N1(), R = MAXAVG_SLOTS;
+    launch_pack(gMA_u, w.xu, d.B, N1, w.n1p, 2, 1, 1, d.H2, R, 0, 1, 1.f / (float)d.W2, st);
+    launch_pack(gMA_u, w.xu, d.B, N1, w.n1p, 2, 0, 1, d.H2, R, 1, 1, 0.f, st);
+    launch_pack(AM_u, w.xu, d.B, N1, w.n1p, 1, 0, 1, d.H2, R, 2, 1, 0.f, st);
+    launch_pack(gMA_v, w.xv, d.B, N1, w.n1p, 2, 1, 1, d.W2, R, 0, 1, 1.f / (float)d.H2, st);
+    launch_pack(gMA_v, w.xv, d.B, N1, w.n1p, 2, 0, 1, d.W2, R, 1, 1, 0.f, st);
+    return launch_pack(AM_v, w.xv, d.B, N1, w.n1p, 1, 0, 1, d.W2, R, 2, 1, 0.f, st);
   }));
-  return run_grad_pair(d, w, GRAD_MAXAVG, MAXAVG_PACK_R, 0, gF1, gF2, st);
+  return run_grad_pair(d, w, GRAD_MAXAVG, MAXAVG_SLOTS, MAXAVG_SLOTS, 0, 0, gF1, gF2, st);
 }
 
 int sfb_compression_backward(const float* F1, const float* F2, const float* A_u, const float* A_v,
@@ -381,32 +420,32 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(gC_u); SFB_CHECK_PTR(gC_v);
   SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2); SFB_CHECK_PTR(gA_u); SFB_CHECK_PTR(gA_v);
   Workspace w;
-  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w, compress_pack_R(d)));
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  // packed slots of channel k:  XU 2k = gC_u, 2k+1 = A_v;  XV 2k = A_u, 2k+1 = gC_v,
+  // so that G[p,u,v] = sum_slots XU[u,slot,p] * XV[v,slot,p].
+  const int N1 = d.N1(), K = d.Kc, R2 = 2 * d.Kc;
+  SFB_CUDA(timed(KID_PACK, 4, st, [&] {
+    launch_pack(gC_u, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, R2, 0, 2, 0.f, st);
+    launch_pack(A_v, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, R2, 1, 2, 0.f, st);
+    launch_pack(A_u, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, R2, 0, 2, 0.f, st);
+    return launch_pack(gC_v, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, R2, 1, 2, 0.f, st);
+  }));
   // gA_v[p,k,u] = sum_v S * gC_v[p,k,v]  and  gA_u[p,k,v] = sum_u S * gC_u[p,k,u]: the forward
-  // compression sweep with the upstream gradients in the role of the weights.
-  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, gC_v, gC_u, gA_v, gA_u, st));
-  // gradient GEMMs, at most KC_MAX_PER_SWEEP channels per pass; later passes add to gF1 / gF2.
-  // packed slots per channel k: XU (gC_u, A_v), XV (A_u, gC_v), so that G = sum_slots XU * XV.
-  for (int k0 = 0; k0 < d.Kc; k0 += KC_MAX_PER_SWEEP) {
-    const int kc = (d.Kc - k0 < KC_MAX_PER_SWEEP) ? d.Kc - k0 : KC_MAX_PER_SWEEP;
-    const int R = 2 * kc, N1 = d.N1();
-    SFB_CUDA(timed(KID_PACK, 4 * kc, st, [&] {
-      cudaError_t e = cudaSuccess;
-      for (int k = 0; k < kc; ++k) {
-        launch_pack_transposed(gC_u, w.xu, d.B, N1, w.n1p, d.Kc, k0 + k, d.H2, R, 2 * k, 0.f, st);
-        launch_pack_transposed(A_v, w.xu, d.B, N1, w.n1p, d.Kc, k0 + k, d.H2, R, 2 * k + 1, 0.f, st);
-        launch_pack_transposed(A_u, w.xv, d.B, N1, w.n1p, d.Kc, k0 + k, d.W2, R, 2 * k, 0.f, st);
-        e = launch_pack_transposed(gC_v, w.xv, d.B, N1, w.n1p, d.Kc, k0 + k, d.W2, R, 2 * k + 1, 0.f, st);
-      }
-      return e;
-    }));
-    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R, k0 > 0 ? 1 : 0, gF1, gF2, st));
-  }
+  // compression sweep with the upstream gradients in the role of the weights
+  // (w_u = gC_v = XV slot 2k+1, w_v = gC_u = XU slot 2k).
+  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, R2, 1, 0, 2, st));
+  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+    launch_unpack(w.ou, gA_v, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
+    return launch_unpack(w.ov, gA_u, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
+  }));
+  // gradient GEMMs, at most KC_MAX_PER_SWEEP channels (2 slots each) per pass; later passes add to gF1 / gF2.
+  for (int k0 = 0; k0 < K; k0 += KC_MAX_PER_SWEEP)
+    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, 2 * chunk_channels(K - k0), R2, 2 * k0, k0 > 0 ? 1 : 0, gF1, gF2, st));
   return SFB_OK;
 }
 
@@ -416,7 +455,7 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
   SFB_TRY(check_shape(shape, false, &d));
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(S);
   Workspace w;
-  SFB_TRY(check_workspace(d, workspace, workspace_bytes, false, &w));
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_CORR_VOLUME, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
@@ -426,6 +465,7 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = SWEEP_DUMP;
+  a.n1p = w.n1p;
   a.dump = S;
   a.status = w.status;
   SFB_CUDA(timed(KID_SWEEP_DUMP, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));

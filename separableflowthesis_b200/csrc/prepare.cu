@@ -41,20 +41,22 @@ __global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict_
   }
 }
 
-// Tiled transpose: reads 32 consecutive displacement indices of 32 pixels (coalesced along d), writes the
-// same 32 x 32 patch with the pixel index fastest (coalesced along p).
-__global__ void pack_transposed_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int N1, int n1p,
-                                       int Ksrc, int ksrc, int D, int R, int r, float scale) {
+// Tiled transposes between the reference's per-pixel layout (B, N1, K, D) (displacement d fastest) and the
+// packed layout (B, D, R, n1p) (pixel fastest) the kernels use.  32 x 32 patches through shared memory so
+// that both the read and the write are coalesced.  grid (n1p/32, ceil(D/32), B*K), block (32, 8).
+__global__ void pack_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int N1, int n1p, int Ksrc,
+                            int ksrc0, int K, int D, int R, int r0, int rstride, float scale) {
   __shared__ uint32_t tile[32][33];
-  const int b = blockIdx.z, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int b = blockIdx.z / K, k = blockIdx.z - b * K, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
   const int tx = threadIdx.x, ty = threadIdx.y;
   for (int j = ty; j < 32; j += 8) {
     const int p = p0 + j, d = d0 + tx;
     uint32_t v = 0;
-    if (p < N1 && d < D) v = __ldg(src + (((size_t)b * N1 + p) * Ksrc + ksrc) * D + d);
+    if (p < N1 && d < D) v = __ldg(src + (((size_t)b * N1 + p) * Ksrc + ksrc0 + k) * D + d);
     tile[j][tx] = v;
   }
   __syncthreads();
+  const int r = r0 + k * rstride;
   for (int j = ty; j < 32; j += 8) {
     const int d = d0 + j, p = p0 + tx;
     if (d < D) {
@@ -65,12 +67,36 @@ __global__ void pack_transposed_kernel(const uint32_t* __restrict__ src, uint32_
   }
 }
 
-cudaError_t launch_pack_transposed(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc, int D,
-                                   int R, int r, float scale, cudaStream_t stream) {
-  const dim3 grid(n1p / 32, (D + 31) / 32, B), block(32, 8);
-  pack_transposed_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src),
-                                                     reinterpret_cast<uint32_t*>(dst), N1, n1p, Ksrc, ksrc, D, R, r,
-                                                     scale);
+__global__ void unpack_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int N1, int n1p, int K,
+                              int D, int R, int r0, int rstride, int Kdst, int kdst0) {
+  __shared__ uint32_t tile[32][33];
+  const int b = blockIdx.z / K, k = blockIdx.z - b * K, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int r = r0 + k * rstride;
+  for (int j = ty; j < 32; j += 8) {
+    const int d = d0 + j, p = p0 + tx;
+    tile[j][tx] = (d < D) ? __ldg(src + (((size_t)b * D + d) * R + r) * n1p + p) : 0u;
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const int p = p0 + j, d = d0 + tx;
+    if (p < N1 && d < D) dst[(((size_t)b * N1 + p) * Kdst + kdst0 + k) * D + d] = tile[tx][j];
+  }
+}
+
+cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,
+                        int R, int r0, int rstride, float scale, cudaStream_t stream) {
+  const dim3 grid(n1p / 32, (D + 31) / 32, B * K), block(32, 8);
+  pack_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src), reinterpret_cast<uint32_t*>(dst), N1,
+                                          n1p, Ksrc, ksrc0, K, D, R, r0, rstride, scale);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_unpack(const float* src, void* dst, int B, int N1, int n1p, int K, int D, int R, int r0,
+                          int rstride, int Kdst, int kdst0, cudaStream_t stream) {
+  const dim3 grid(n1p / 32, (D + 31) / 32, B * K), block(32, 8);
+  unpack_kernel<<<grid, block, 0, stream>>>(reinterpret_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), N1,
+                                            n1p, K, D, R, r0, rstride, Kdst, kdst0);
   return cudaGetLastError();
 }
 

@@ -6,14 +6,19 @@
 // columns = 128 accumulator columns), column-blocks outermost.  Warp roles:
 //   warp 0      TMA producer: F1 tile once (stays resident), F2 tiles through a ring of stages
 //   warp 1      allocates TMEM, issues tcgen05.mma (TF32 in, FP32 accumulate), 4 accumulators in flight
-//   warps 2..5  epilogue: one thread per image-1 pixel reads its accumulator lane with tcgen05.ld
+//   warps 2..9  two epilogue warpgroups; in each, one thread per image-1 pixel reads its accumulator
+//               lane with tcgen05.ld.  Both groups consume every tile and split its work.
+// Everything indexed by an image-1 pixel is read and written in the packed, pixel-fastest layout
+// (kernels.h), so a warp's 32 lanes touch one 128-byte line per access.
 // Epilogues
-//   max/avg      : running column-direction max(+argmax) in registers across the inner row-block
-//                  loop, row-direction max(+argmax) merged through global memory once per tile;
-//                  the two mean channels come from extra tiles whose "image-2 pixels" are the
-//                  row-mean and column-mean feature rows of F2 (mean_v S[u,v] = F1 . mean_v F2[u,v]).
-//   compression  : C_u[k,u] = sum_v S*W_u[k,v] (reduced per tile, accumulated with red.add),
-//                  C_v[k,v] = sum_u S*W_v[k,u] (register accumulators across the inner loop).
+//   max/avg      : group g takes tile rows 4g..4g+3.  Running column-direction max(+argmax) in
+//                  registers across the inner row-block loop (the two groups' partial results are merged
+//                  once per column block), row-direction max(+argmax) merged through the packed output
+//                  once per tile.  The two mean channels come from extra tiles whose "image-2 pixels"
+//                  are the row-mean and column-mean feature rows of F2 (mean_v S[u,v] = F1 . mean_v F2[u,v]).
+//   compression  : group g takes channels g, g+2.  OU[k,u] = sum_v S*w_u[k,v] (reduced per tile,
+//                  accumulated with red.add), OV[k,v] = sum_u S*w_v[k,u] (register accumulators across
+//                  the inner loop).
 // Replaces the reference kernels MemorySaver_kernel_forward.cu:128-313, :328-533, :550-753.
 #include <math_constants.h>
 
@@ -25,11 +30,14 @@ namespace sfb {
 constexpr int SW_NSTAGE = 5;
 constexpr int SW_NACC = 4;
 constexpr int SW_TILE_N = SWEEP_UT * SWEEP_VT;  // 128 accumulator columns
-constexpr int SW_THREADS = 192;
+constexpr int SW_EPI_WARPS = 8;
+constexpr int SW_THREADS = 64 + SW_EPI_WARPS * 32;
+constexpr int SW_NMERGE = 8;                    // ring of column-merge barriers (> SW_NACC tiles of run-ahead)
 constexpr uint32_t SW_STAGE_BYTES = SW_TILE_N * KBLK * 4;
 constexpr uint32_t SW_F1_BLOCK_BYTES = TILE_M * KBLK * 4;
 constexpr uint32_t SW_TMEM_COLS = 512;
 static_assert(SW_NACC * SW_TILE_N <= 512, "accumulators exceed TMEM");
+static_assert(SW_NMERGE > SW_NACC, "a warpgroup can run SW_NACC tiles ahead of the other");
 
 struct SweepSmem {
   float f1[MAX_KB][TILE_M * KBLK];        // resident image-1 tile, one 128B-swizzled block per 32 channels
@@ -39,6 +47,7 @@ struct SweepSmem {
   uint64_t empty[SW_NSTAGE];
   uint64_t acc_full[SW_NACC];
   uint64_t acc_empty[SW_NACC];
+  uint64_t merge[SW_NMERGE];              // group 1 -> group 0: partial column results are in memory
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -54,9 +63,9 @@ __device__ void sweep_producer(SweepSmem& sm, const SweepArgs& a, const SweepSch
   mbar_expect_tx(&sm.f1_full, sc.nkb * SW_F1_BLOCK_BYTES);
   for (int kb = 0; kb < sc.nkb; ++kb) tma_load_3d(sm.f1[kb], tm_f1, &sm.f1_full, kb * KBLK, sc.m0, sc.b);
   uint32_t it = 0;
+  int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_total; ++t) {
     const bool main_tile = t < sc.t_main;
-    const int vb = t / sc.n_ub, ub = t - vb * sc.n_ub;
     for (int kb = 0; kb < sc.nkb; ++kb, ++it) {
       const uint32_t s = it % SW_NSTAGE, ph = (it / SW_NSTAGE) & 1u;
       if (!mbar_wait(&sm.empty[s], ph ^ 1u, &sm.abort_flag, a.status, DEV_TIMEOUT_PRODUCER)) return;
@@ -66,6 +75,7 @@ __device__ void sweep_producer(SweepSmem& sm, const SweepArgs& a, const SweepSch
       else
         tma_load_3d(sm.f2[s], tm_aux, &sm.full[s], kb * KBLK, (t - sc.t_main) * SW_TILE_N, sc.b);
     }
+    if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
 }
 
@@ -97,9 +107,9 @@ __device__ void sweep_mma(SweepSmem& sm, const SweepArgs& a, const SweepSched& s
 
 // ---------------------------------------------------------------------------------- epilogues
 struct EpiCtx {
-  int q, lane, p;
-  bool valid;
-  size_t row;       // b*N1 + p (0 when the lane is past the image)
+  int wg;           // epilogue warpgroup 0 / 1
+  int lane;
+  int p;            // pixel index inside the padded sample: m0 + 32*quarter + lane  (< n1p)
   uint32_t tbase;   // TMEM address of this warp's lane quarter, column 0
 };
 
@@ -120,195 +130,228 @@ __device__ __forceinline__ void epi_release(SweepSmem& sm, int t, int lane) {
 
 template <bool ARG>
 __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const EpiCtx& e) {
+  constexpr int RW = SWEEP_UT / 2;  // tile rows of one warpgroup
   const int H2 = a.d.H2, W2 = a.d.W2;
-  float* mau = a.ma_u + e.row * 2 * H2;
-  float* mav = a.ma_v + e.row * 2 * W2;
-  int32_t* amu = ARG ? a.am_u + e.row * H2 : nullptr;
-  int32_t* amv = ARG ? a.am_v + e.row * W2 : nullptr;
+  const size_t n1p = a.n1p;
+  float* pu = a.pu + (size_t)sc.b * H2 * 3 * n1p + e.p;  // (u, slot) at pu[(u*3 + slot) * n1p]
+  float* pv = a.pv + (size_t)sc.b * W2 * 3 * n1p + e.p;
 
   float cm[SWEEP_VT];
   int ca[SWEEP_VT];
+  int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_main; ++t) {
-    const int vb = t / sc.n_ub, ub = t - vb * sc.n_ub;
-    const int v0 = vb * SWEEP_VT, u0 = ub * SWEEP_UT;
-    const int nu = min(SWEEP_UT, H2 - u0), nv = min(SWEEP_VT, W2 - v0);
+    const int v0 = vb * SWEEP_VT, ubase = ub * SWEEP_UT + e.wg * RW;
+    const int nu = min(RW, H2 - ubase), nv = min(SWEEP_VT, W2 - v0);  // nu may be <= 0
     if (ub == 0) {
 #pragma unroll
       for (int j = 0; j < SWEEP_VT; ++j) { cm[j] = -CUDART_INF_F; ca[j] = 0; }
     }
     // row-direction state of earlier column blocks (issued before the wait to hide the latency)
-    float rold[SWEEP_UT];
+    float rold[RW];
 #pragma unroll
-    for (int ul = 0; ul < SWEEP_UT; ++ul)
-      rold[ul] = (e.valid && vb > 0 && ul < nu) ? mau[u0 + ul] : -CUDART_INF_F;
+    for (int ul = 0; ul < RW; ++ul)
+      rold[ul] = (vb > 0 && ul < nu) ? pu[(size_t)((ubase + ul) * 3) * n1p] : -CUDART_INF_F;
 
     if (!epi_wait(sm, a, t)) return;
-    const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N;
-    float rm[SWEEP_UT];
-    int ra[SWEEP_UT];
+    float s[RW * SWEEP_VT];
+    tmem_ld64(e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * (RW * SWEEP_VT), s);
+    epi_release(sm, t, e.lane);  // the values are in registers: hand the accumulator back at once
+
 #pragma unroll
-    for (int ul = 0; ul < SWEEP_UT; ++ul) {
-      rm[ul] = -CUDART_INF_F;
-      ra[ul] = 0;
+    for (int ul = 0; ul < RW; ++ul) {
       if (ul < nu) {  // warp-uniform
-        float s[SWEEP_VT];
-        tmem_ld16(tacc + ul * SWEEP_VT, s);
+        float* r = &s[ul * SWEEP_VT];
         if (nv < SWEEP_VT) {
 #pragma unroll
           for (int j = 0; j < SWEEP_VT; ++j)
-            if (j >= nv) s[j] = -CUDART_INF_F;  // padded columns never win a max
+            if (j >= nv) r[j] = -CUDART_INF_F;  // padded columns never win a max
         }
-        float m = s[0];
+        float m = r[0];
         int arg = 0;
 #pragma unroll
         for (int j = 1; j < SWEEP_VT; ++j) {
-          if (s[j] > m) { m = s[j]; arg = j; }  // strict: lowest v wins ties
+          if (r[j] > m) { m = r[j]; arg = j; }  // strict: lowest v wins ties
         }
-        rm[ul] = m;
-        ra[ul] = v0 + arg;
+        const int u = ubase + ul;
 #pragma unroll
         for (int j = 0; j < SWEEP_VT; ++j) {
-          if (s[j] > cm[j]) { cm[j] = s[j]; ca[j] = u0 + ul; }  // strict: lowest u wins ties
+          if (r[j] > cm[j]) { cm[j] = r[j]; ca[j] = u; }  // strict: lowest u of this group wins ties
+        }
+        if (vb == 0 || m > rold[ul]) {
+          pu[(size_t)(u * 3) * n1p] = m;
+          if (ARG) pu[(size_t)(u * 3 + 2) * n1p] = __int_as_float(v0 + arg);
         }
       }
     }
-    epi_release(sm, t, e.lane);
-    if (e.valid) {
-#pragma unroll
-      for (int ul = 0; ul < SWEEP_UT; ++ul) {
-        if (ul < nu && (vb == 0 || rm[ul] > rold[ul])) {
-          mau[u0 + ul] = rm[ul];
-          if (ARG) amu[u0 + ul] = ra[ul];
-        }
-      }
-      if (ub == sc.n_ub - 1) {
+    if (ub == sc.n_ub - 1) {
+      // end of a column block: group 1 publishes its partial column maxima, group 0 merges and stores
+      uint64_t* bar = &sm.merge[vb % SW_NMERGE];
+      if (e.wg == 1) {
 #pragma unroll
         for (int j = 0; j < SWEEP_VT; ++j) {
           if (j < nv) {
-            mav[v0 + j] = cm[j];
-            if (ARG) amv[v0 + j] = ca[j];
+            pv[(size_t)((v0 + j) * 3) * n1p] = cm[j];
+            if (ARG) pv[(size_t)((v0 + j) * 3 + 2) * n1p] = __int_as_float(ca[j]);
+          }
+        }
+        __threadfence_block();
+        __syncwarp();
+        if (e.lane == 0) mbar_arrive(bar);
+      } else {
+        const bool ok = mbar_wait(bar, (vb / SW_NMERGE) & 1u, &sm.abort_flag, a.status, DEV_TIMEOUT_EPILOGUE);
+        if (!__all_sync(0xffffffffu, ok)) return;
+#pragma unroll
+        for (int j = 0; j < SWEEP_VT; ++j) {
+          if (j < nv) {
+            float* dst = pv + (size_t)((v0 + j) * 3) * n1p;
+            const float om = __ldcg(dst);
+            float best = cm[j];
+            int besta = ca[j];
+            if (ARG) {
+              const int oa = __float_as_int(__ldcg(dst + 2 * n1p));
+              if (om > best || (om == best && oa < besta)) { best = om; besta = oa; }  // lowest u on ties
+              dst[2 * n1p] = __int_as_float(besta);
+            } else {
+              best = fmaxf(best, om);
+            }
+            dst[0] = best;
           }
         }
       }
     }
+    if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
   // mean channels: accumulator column r of an aux tile is F1[p] . (row-mean u=r | column-mean v=r-H2)
   const int naux = H2 + W2;
   for (int t = sc.t_main; t < sc.t_total; ++t) {
     if (!epi_wait(sm, a, t)) return;
-    const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N;
-    const int rbase = (t - sc.t_main) * SW_TILE_N;
+    const int r0 = (t - sc.t_main) * SW_TILE_N + e.wg * 64;
+    if (r0 < naux) {  // warp-uniform
+      float s[64];
+      tmem_ld64(e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * 64, s);
+      epi_release(sm, t, e.lane);
 #pragma unroll
-    for (int c = 0; c < SW_TILE_N / 16; ++c) {
-      const int r0 = rbase + c * 16;
-      if (r0 < naux) {  // warp-uniform
-        float s[16];
-        tmem_ld16(tacc + c * 16, s);
-        if (e.valid) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int r = r0 + j;
-            if (r < H2) mau[H2 + r] = s[j];
-            else if (r < naux) mav[W2 + (r - H2)] = s[j];
-          }
-        }
+      for (int j = 0; j < 64; ++j) {
+        const int r = r0 + j;
+        if (r < H2) pu[(size_t)(r * 3 + 1) * n1p] = s[j];
+        else if (r < naux) pv[(size_t)((r - H2) * 3 + 1) * n1p] = s[j];
       }
+    } else {
+      epi_release(sm, t, e.lane);
     }
-    epi_release(sm, t, e.lane);
   }
 }
 
-template <int KC>
 __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const EpiCtx& e) {
-  const int H2 = a.d.H2, W2 = a.d.W2, Kc = a.d.Kc;
-  const float* wu = a.w_u + (e.row * Kc + a.k0) * W2;
-  const float* wv = a.w_v + (e.row * Kc + a.k0) * H2;
-  float* cu = a.c_u + (e.row * Kc + a.k0) * H2;
-  float* cvo = a.c_v + (e.row * Kc + a.k0) * W2;
+  constexpr int KW = KC_MAX_PER_SWEEP / 2;  // channels of one warpgroup: local channels wg, wg + 2
+  const int H2 = a.d.H2, W2 = a.d.W2;
+  const size_t n1p = a.n1p;
+  const float* xu = a.xu + (size_t)sc.b * H2 * a.Rw * n1p + e.p;
+  const float* xv = a.xv + (size_t)sc.b * W2 * a.Rw * n1p + e.p;
+  float* ou = a.ou + (size_t)sc.b * H2 * a.Ro * n1p + e.p;
+  float* ov = a.ov + (size_t)sc.b * W2 * a.Ro * n1p + e.p;
+  int nk = 0, wu_slot[KW], wv_slot[KW], o_slot[KW];
+#pragma unroll
+  for (int j = 0; j < KW; ++j) {
+    const int kl = e.wg + 2 * j;
+    if (kl < a.kc) nk = j + 1;
+    wu_slot[j] = a.wu_slot0 + (a.k0 + kl) * a.w_stride;
+    wv_slot[j] = a.wv_slot0 + (a.k0 + kl) * a.w_stride;
+    o_slot[j] = a.k0 + kl;
+  }
 
-  float au[KC][SWEEP_VT], cv[KC][SWEEP_VT];
+  float au[KW][SWEEP_VT], cv[KW][SWEEP_VT];
+  int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_main; ++t) {
-    const int vb = t / sc.n_ub, ub = t - vb * sc.n_ub;
     const int v0 = vb * SWEEP_VT, u0 = ub * SWEEP_UT;
     const int nu = min(SWEEP_UT, H2 - u0), nv = min(SWEEP_VT, W2 - v0);
     if (ub == 0) {
 #pragma unroll
-      for (int k = 0; k < KC; ++k)
+      for (int j = 0; j < KW; ++j)
 #pragma unroll
-        for (int j = 0; j < SWEEP_VT; ++j) {
-          au[k][j] = (e.valid && j < nv) ? __ldg(wu + (size_t)k * W2 + v0 + j) : 0.f;
-          cv[k][j] = 0.f;
+        for (int i = 0; i < SWEEP_VT; ++i) {
+          au[j][i] = (j < nk && i < nv) ? __ldg(xv + (size_t)((v0 + i) * a.Rw + wu_slot[j]) * n1p) : 0.f;
+          cv[j][i] = 0.f;
         }
     }
-    float av[KC][SWEEP_UT];
+    float av[KW][SWEEP_UT];
 #pragma unroll
-    for (int k = 0; k < KC; ++k)
+    for (int j = 0; j < KW; ++j)
 #pragma unroll
       for (int ul = 0; ul < SWEEP_UT; ++ul)
-        av[k][ul] = (e.valid && ul < nu) ? __ldg(wv + (size_t)k * H2 + u0 + ul) : 0.f;
+        av[j][ul] = (j < nk && ul < nu) ? __ldg(xu + (size_t)((u0 + ul) * a.Rw + wv_slot[j]) * n1p) : 0.f;
 
     if (!epi_wait(sm, a, t)) return;
     const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N;
+    if (nk > 0) {
 #pragma unroll
-    for (int ul = 0; ul < SWEEP_UT; ++ul) {
-      if (ul < nu) {  // warp-uniform; padded cells hold S = 0 (zero-filled F2 rows) and weight 0
-        float s[SWEEP_VT];
-        tmem_ld16(tacc + ul * SWEEP_VT, s);
+      for (int pr = 0; pr < SWEEP_UT / 2; ++pr) {
+        if (2 * pr < nu) {  // warp-uniform; padded cells hold S = 0 (zero-filled F2 rows) and weight 0
+          float s[2 * SWEEP_VT];
+          tmem_ld32(tacc + pr * 2 * SWEEP_VT, s);
+          if (pr == SWEEP_UT / 2 - 1 || 2 * pr + 2 >= nu) epi_release(sm, t, e.lane);  // last read of this tile
 #pragma unroll
-        for (int k = 0; k < KC; ++k) {
-          float r = 0.f;
+          for (int h = 0; h < 2; ++h) {
+            const int ul = 2 * pr + h;
+            if (ul < nu) {
 #pragma unroll
-          for (int j = 0; j < SWEEP_VT; ++j) {
-            r = fmaf(s[j], au[k][j], r);
-            cv[k][j] = fmaf(s[j], av[k][ul], cv[k][j]);
-          }
-          if (e.valid) {
-            float* dst = cu + (size_t)k * H2 + u0 + ul;
-            if (vb == 0) *dst = r;          // first column block initialises the output
-            else atomicAdd(dst, r);         // later blocks accumulate (same thread, same address: ordered)
+              for (int j = 0; j < KW; ++j) {
+                float r = 0.f;
+#pragma unroll
+                for (int i = 0; i < SWEEP_VT; ++i) {
+                  r = fmaf(s[h * SWEEP_VT + i], au[j][i], r);
+                  cv[j][i] = fmaf(s[h * SWEEP_VT + i], av[j][ul], cv[j][i]);
+                }
+                if (j < nk) {
+                  float* dst = ou + (size_t)((u0 + ul) * a.Ro + o_slot[j]) * n1p;
+                  if (vb == 0) *dst = r;     // first column block initialises the output
+                  else atomicAdd(dst, r);    // later blocks accumulate (same thread, same address: ordered)
+                }
+              }
+            }
           }
         }
       }
+    } else {
+      epi_release(sm, t, e.lane);
     }
-    epi_release(sm, t, e.lane);
-    if (e.valid && ub == sc.n_ub - 1) {
+    if (ub == sc.n_ub - 1) {
 #pragma unroll
-      for (int k = 0; k < KC; ++k)
+      for (int j = 0; j < KW; ++j)
 #pragma unroll
-        for (int j = 0; j < SWEEP_VT; ++j)
-          if (j < nv) cvo[(size_t)k * W2 + v0 + j] = cv[k][j];
+        for (int i = 0; i < SWEEP_VT; ++i)
+          if (j < nk && i < nv) ov[(size_t)((v0 + i) * a.Ro + o_slot[j]) * n1p] = cv[j][i];
     }
+    if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
 }
 
 // Test aid: writes the dense volume of a (small) problem so the tensor-core plumbing can be checked alone.
 __device__ void epilogue_dump(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const EpiCtx& e) {
-  const int H2 = a.d.H2, W2 = a.d.W2;
-  float* out = a.dump + e.row * H2 * W2;
+  const int H2 = a.d.H2, W2 = a.d.W2, N1 = a.d.N1();
+  const bool valid = e.p < N1;
+  float* out = a.dump + ((size_t)sc.b * N1 + (valid ? e.p : 0)) * H2 * W2;
+  int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_main; ++t) {
-    const int vb = t / sc.n_ub, ub = t - vb * sc.n_ub;
-    const int v0 = vb * SWEEP_VT, u0 = ub * SWEEP_UT;
-    const int nu = min(SWEEP_UT, H2 - u0), nv = min(SWEEP_VT, W2 - v0);
+    const int v0 = vb * SWEEP_VT, ubase = ub * SWEEP_UT + e.wg * (SWEEP_UT / 2);
+    const int nu = min(SWEEP_UT / 2, H2 - ubase), nv = min(SWEEP_VT, W2 - v0);
     if (!epi_wait(sm, a, t)) return;
-    const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N;
-#pragma unroll
-    for (int ul = 0; ul < SWEEP_UT; ++ul) {
-      if (ul < nu) {
-        float s[SWEEP_VT];
-        tmem_ld16(tacc + ul * SWEEP_VT, s);
-        if (e.valid) {
-#pragma unroll
-          for (int j = 0; j < SWEEP_VT; ++j)
-            if (j < nv) out[(size_t)(u0 + ul) * W2 + v0 + j] = s[j];
-        }
-      }
-    }
+    float s[64];
+    tmem_ld64(e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * 64, s);
     epi_release(sm, t, e.lane);
+    if (valid) {
+#pragma unroll
+      for (int ul = 0; ul < SWEEP_UT / 2; ++ul)
+#pragma unroll
+        for (int j = 0; j < SWEEP_VT; ++j)
+          if (ul < nu && j < nv) out[(size_t)(ubase + ul) * W2 + v0 + j] = s[ul * SWEEP_VT + j];
+    }
+    if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
 }
 
 // ---------------------------------------------------------------------------------- kernel
-template <int MODE, int KC>
+template <int MODE>
 __global__ void __launch_bounds__(SW_THREADS, 1)
 sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ CUtensorMap tm_f2,
              const __grid_constant__ CUtensorMap tm_aux, const SweepArgs a) {
@@ -319,8 +362,7 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
   SweepSmem& sm = *reinterpret_cast<SweepSmem*>(smem_raw + pad);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int N1 = a.d.N1();
-  const int tiles_per_sample = (N1 + TILE_M - 1) / TILE_M;
+  const int tiles_per_sample = (a.d.N1() + TILE_M - 1) / TILE_M;
 
   SweepSched sc;
   sc.b = blockIdx.x / tiles_per_sample;
@@ -335,7 +377,8 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
   if (threadIdx.x == 0) {
     mbar_init(&sm.f1_full, 1);
     for (int s = 0; s < SW_NSTAGE; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    for (int i = 0; i < SW_NACC; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 4); }
+    for (int i = 0; i < SW_NACC; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], SW_EPI_WARPS); }
+    for (int i = 0; i < SW_NMERGE; ++i) mbar_init(&sm.merge[i], SW_EPI_WARPS / 2);
     sm.abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tm_f1);
@@ -358,15 +401,14 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
     __syncwarp();
   } else {
     EpiCtx e;
-    e.q = warp & 3;  // tcgen05.ld lets a warp read TMEM lanes 32*(warp%4) .. +31 only
+    const int q = warp & 3;  // tcgen05.ld lets a warp read TMEM lanes 32*(warp%4) .. +31 only
+    e.wg = (warp - 2) >> 2;
     e.lane = lane;
-    e.p = sc.m0 + e.q * 32 + lane;
-    e.valid = e.p < N1;
-    e.row = (size_t)sc.b * N1 + (e.valid ? e.p : 0);
-    e.tbase = sm.tmem_base + (static_cast<uint32_t>(e.q * 32) << 16);
+    e.p = sc.m0 + q * 32 + lane;
+    e.tbase = sm.tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     if (MODE == SWEEP_MAXAVG) epilogue_maxavg<false>(sm, a, sc, e);
     else if (MODE == SWEEP_MAXARGAVG) epilogue_maxavg<true>(sm, a, sc, e);
-    else if (MODE == SWEEP_COMPRESS) epilogue_compress<KC>(sm, a, sc, e);
+    else if (MODE == SWEEP_COMPRESS) epilogue_compress(sm, a, sc, e);
     else epilogue_dump(sm, a, sc, e);
   }
 
@@ -384,10 +426,10 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
   }
 }
 
-template <int MODE, int KC>
+template <int MODE>
 static cudaError_t launch_one(const SweepArgs& a, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
                               const CUtensorMap& tm_aux, cudaStream_t stream) {
-  auto kern = sweep_kernel<MODE, KC>;
+  auto kern = sweep_kernel<MODE>;
   cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SW_SMEM_BYTES);
   if (err != cudaSuccess) return err;
   const int tiles_per_sample = (a.d.N1() + TILE_M - 1) / TILE_M;
@@ -399,17 +441,12 @@ static cudaError_t launch_one(const SweepArgs& a, const CUtensorMap& tm_f1, cons
 cudaError_t launch_sweep(const SweepArgs& a, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
                          const CUtensorMap& tm_aux, cudaStream_t stream) {
   switch (a.mode) {
-    case SWEEP_MAXAVG: return launch_one<SWEEP_MAXAVG, 1>(a, tm_f1, tm_f2, tm_aux, stream);
-    case SWEEP_MAXARGAVG: return launch_one<SWEEP_MAXARGAVG, 1>(a, tm_f1, tm_f2, tm_aux, stream);
-    case SWEEP_DUMP: return launch_one<SWEEP_DUMP, 1>(a, tm_f1, tm_f2, tm_aux, stream);
+    case SWEEP_MAXAVG: return launch_one<SWEEP_MAXAVG>(a, tm_f1, tm_f2, tm_aux, stream);
+    case SWEEP_MAXARGAVG: return launch_one<SWEEP_MAXARGAVG>(a, tm_f1, tm_f2, tm_aux, stream);
+    case SWEEP_DUMP: return launch_one<SWEEP_DUMP>(a, tm_f1, tm_f2, tm_aux, stream);
     case SWEEP_COMPRESS:
-      switch (a.kc) {
-        case 1: return launch_one<SWEEP_COMPRESS, 1>(a, tm_f1, tm_f2, tm_aux, stream);
-        case 2: return launch_one<SWEEP_COMPRESS, 2>(a, tm_f1, tm_f2, tm_aux, stream);
-        case 3: return launch_one<SWEEP_COMPRESS, 3>(a, tm_f1, tm_f2, tm_aux, stream);
-        case 4: return launch_one<SWEEP_COMPRESS, 4>(a, tm_f1, tm_f2, tm_aux, stream);
-        default: return cudaErrorInvalidValue;
-      }
+      if (a.kc < 1 || a.kc > KC_MAX_PER_SWEEP) return cudaErrorInvalidValue;
+      return launch_one<SWEEP_COMPRESS>(a, tm_f1, tm_f2, tm_aux, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -30,8 +30,10 @@ def test_workspace_query(lib):
     s = _lib.SfbShape(2, 48, 64, 48, 64, 256, 2)
     fwd = lib.sfb_workspace_bytes(_lib.OP_MAX_AVG_FORWARD, ctypes.byref(s))
     bwd = lib.sfb_workspace_bytes(_lib.OP_COMPRESSION_BACKWARD, ctypes.byref(s))
-    feat = 2 * 48 * 64 * 256 * 4
-    assert bwd >= 2 * feat and fwd >= bwd + 2 * (48 + 64) * 256 * 4
+    feat = 2 * 48 * 64 * 256 * 4                      # one rounded feature copy
+    packed = 2 * 48 * 64 * (48 + 64) * 4              # one packed slot of every (pixel, displacement) pair
+    assert fwd >= 2 * feat + 2 * (48 + 64) * 256 * 4 + 3 * packed   # + mean rows of F2 + max/mean/argmax slots
+    assert bwd >= 2 * feat + (4 + 2) * packed                      # + 2*Kc input slots + Kc output slots
     bad = _lib.SfbShape(2, 48, 64, 48, 64, 258, 2)
     assert lib.sfb_workspace_bytes(_lib.OP_MAX_AVG_FORWARD, ctypes.byref(bad)) == 0
     assert lib.sfb_workspace_bytes(99, ctypes.byref(s)) == 0
