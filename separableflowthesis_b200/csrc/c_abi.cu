@@ -132,6 +132,8 @@ struct Workspace {
   float* xv;   // packed inputs indexed by (v, slot, pixel): (B, W2, Rx, n1p)
   float* ou;   // packed outputs, (B, H2, Ro, n1p)
   float* ov;   // packed outputs, (B, W2, Ro, n1p)
+  float* gxu;  // interleaved gradient-GEMM operands, (B, H2, n1p, Rg)
+  float* gxv;  // interleaved gradient-GEMM operands, (B, W2, n1p, Rg)
   int n1p;
   size_t bytes;
 };
@@ -139,17 +141,18 @@ struct Workspace {
 int padded_pixels(const Dims& d) { return (d.N1() + TILE_M - 1) / TILE_M * TILE_M; }
 
 // What an op keeps in the workspace: the mean rows of F2, Rx packed input slots, Ro packed output slots.
-struct WsPlan { bool aux; int Rx; int Ro; };
+struct WsPlan { bool aux; int Rx; int Ro; int Rg; };
 constexpr int MAXAVG_SLOTS = 3;  // max, mean, argmax bits
 int chunk_channels(int Kc) { return Kc < KC_MAX_PER_SWEEP ? Kc : KC_MAX_PER_SWEEP; }
+int grad_slots(int kc) { return 2 * kc <= 4 ? 4 : 8; }  // two slots per channel, rounded up to a multiple of 4
 
 WsPlan plan_for(int op, const Dims& d) {
   switch (op) {
-    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS};
-    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc};
-    case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, MAXAVG_SLOTS, 0};
-    case SFB_OP_COMPRESSION_BACKWARD: return {false, 2 * d.Kc, d.Kc};
-    default: return {false, 0, 0};
+    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS, 0};
+    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc, 0};
+    case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, 0, 0, 4};
+    case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc))};
+    default: return {false, 0, 0, 0};
   }
 }
 
@@ -172,6 +175,8 @@ Workspace carve(const Dims& d, void* base, const WsPlan& plan) {
   w.xv = plan.Rx ? take((size_t)d.B * d.W2 * plan.Rx * w.n1p) : nullptr;
   w.ou = plan.Ro ? take((size_t)d.B * d.H2 * plan.Ro * w.n1p) : nullptr;
   w.ov = plan.Ro ? take((size_t)d.B * d.W2 * plan.Ro * w.n1p) : nullptr;
+  w.gxu = plan.Rg ? take((size_t)d.B * d.H2 * plan.Rg * w.n1p) : nullptr;
+  w.gxv = plan.Rg ? take((size_t)d.B * d.W2 * plan.Rg * w.n1p) : nullptr;
   w.bytes = off;
   return w;
 }
@@ -189,7 +194,7 @@ int check_shape(const sfb_shape* s, bool need_kc, Dims* d) {
     return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image has more than 2^30 pixels");
   {  // element offsets inside one sample's packed array are 32-bit in the kernels
     const long long n1p = ((long long)s->H1 * s->W1 + TILE_M - 1) / TILE_M * TILE_M;
-    const long long slots = need_kc ? 2ll * s->Kc : MAXAVG_SLOTS;
+    const long long slots = 8;
     if (n1p * slots * (s->H2 > s->W2 ? s->H2 : s->W2) >= (1ll << 32))
       return fail(SFB_ERR_UNSUPPORTED_SHAPE, "H1*W1*max(H2,W2)*slots exceeds 2^32 elements per sample");
   }
@@ -309,20 +314,18 @@ int run_compress_sweeps(const Dims& d, const Workspace& w, const CUtensorMap& tm
   return SFB_OK;
 }
 
-int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R, int Rtot, int r0, int accumulate, float* gF1,
-                  float* gF2, cudaStream_t st) {
+int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accumulate, float* gF1, float* gF2,
+                  cudaStream_t st) {
   CUtensorMap tm_y;
   GradArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = mode;
-  a.R = R;
-  a.Rtot = Rtot;
-  a.r0 = r0;
+  a.R4 = R4;
   a.n1p = w.n1p;
   a.accumulate = accumulate;
-  a.xu = w.xu;
-  a.xv = w.xv;
+  a.xu = w.gxu;
+  a.xv = w.gxv;
   a.status = w.status;
   // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2.
   SFB_TRY(map_f2_tile(&tm_y, d, w.F2r, GG_UT, GG_VT, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
@@ -398,17 +401,22 @@ int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t*
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_MAX_ARGMAX_AVG_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
-  // packed operands: slot 0 = mean-gradient / row length, slot 1 = max-gradient, slot 2 = argmax (raw bits)
-  SFB_CUDA(timed(KID_PACK, 6, st, [&] {
-    const int N1 = d.N1(), R = MAXAVG_SLOTS;
-    launch_pack(gMA_u, w.xu, d.B, N1, w.n1p, 2, 1, 1, d.H2, R, 0, 1, 1.f / (float)d.W2, st);
-    launch_pack(gMA_u, w.xu, d.B, N1, w.n1p, 2, 0, 1, d.H2, R, 1, 1, 0.f, st);
-    launch_pack(AM_u, w.xu, d.B, N1, w.n1p, 1, 0, 1, d.H2, R, 2, 1, 0.f, st);
-    launch_pack(gMA_v, w.xv, d.B, N1, w.n1p, 2, 1, 1, d.W2, R, 0, 1, 1.f / (float)d.H2, st);
-    launch_pack(gMA_v, w.xv, d.B, N1, w.n1p, 2, 0, 1, d.W2, R, 1, 1, 0.f, st);
-    return launch_pack(AM_v, w.xv, d.B, N1, w.n1p, 1, 0, 1, d.W2, R, 2, 1, 0.f, st);
+  // interleaved slots: 0 = mean-gradient / row length, 1 = max-gradient, 2 = argmax (raw bits), 3 = 0
+  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+    const int N1 = d.N1();
+    SlotSources su, sv;
+    memset(&su, 0, sizeof(su));
+    memset(&sv, 0, sizeof(sv));
+    su.s[0] = {gMA_u, 2, 1, 1.f / (float)d.W2};
+    su.s[1] = {gMA_u, 2, 0, 0.f};
+    su.s[2] = {AM_u, 1, 0, 0.f};
+    sv.s[0] = {gMA_v, 2, 1, 1.f / (float)d.H2};
+    sv.s[1] = {gMA_v, 2, 0, 0.f};
+    sv.s[2] = {AM_v, 1, 0, 0.f};
+    launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, 4, st);
+    return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4, st);
   }));
-  return run_grad_pair(d, w, GRAD_MAXAVG, MAXAVG_SLOTS, MAXAVG_SLOTS, 0, 0, gF1, gF2, st);
+  return run_grad_pair(d, w, GRAD_MAXAVG, 4, 0, gF1, gF2, st);
 }
 
 int sfb_compression_backward(const float* F1, const float* F2, const float* A_u, const float* A_v,
@@ -426,26 +434,38 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
-  // packed slots of channel k:  XU 2k = gC_u, 2k+1 = A_v;  XV 2k = A_u, 2k+1 = gC_v,
-  // so that G[p,u,v] = sum_slots XU[u,slot,p] * XV[v,slot,p].
-  const int N1 = d.N1(), K = d.Kc, R2 = 2 * d.Kc;
-  SFB_CUDA(timed(KID_PACK, 4, st, [&] {
-    launch_pack(gC_u, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, R2, 0, 2, 0.f, st);
-    launch_pack(A_v, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, R2, 1, 2, 0.f, st);
-    launch_pack(A_u, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, R2, 0, 2, 0.f, st);
-    return launch_pack(gC_v, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, R2, 1, 2, 0.f, st);
-  }));
+  const int N1 = d.N1(), K = d.Kc;
   // gA_v[p,k,u] = sum_v S * gC_v[p,k,v]  and  gA_u[p,k,v] = sum_u S * gC_u[p,k,u]: the forward
-  // compression sweep with the upstream gradients in the role of the weights
-  // (w_u = gC_v = XV slot 2k+1, w_v = gC_u = XU slot 2k).
-  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, R2, 1, 0, 2, st));
+  // compression sweep with the upstream gradients in the role of the weights (w_u = gC_v, w_v = gC_u).
+  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+    launch_pack(gC_v, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);
+    return launch_pack(gC_u, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);
+  }));
+  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, K, 0, 0, 1, st));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_unpack(w.ou, gA_v, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
     return launch_unpack(w.ov, gA_u, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
   }));
-  // gradient GEMMs, at most KC_MAX_PER_SWEEP channels (2 slots each) per pass; later passes add to gF1 / gF2.
-  for (int k0 = 0; k0 < K; k0 += KC_MAX_PER_SWEEP)
-    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, 2 * chunk_channels(K - k0), R2, 2 * k0, k0 > 0 ? 1 : 0, gF1, gF2, st));
+  // gradient GEMMs, at most KC_MAX_PER_SWEEP channels per pass; later passes add to gF1 / gF2.
+  // interleaved slots of local channel j:  XU 2j = gC_u, 2j+1 = A_v;  XV 2j = A_u, 2j+1 = gC_v,
+  // so that G[p,u,v] = sum_slots XU[u,p,slot] * XV[v,p,slot].
+  for (int k0 = 0; k0 < K; k0 += KC_MAX_PER_SWEEP) {
+    const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
+    SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+      SlotSources su, sv;
+      memset(&su, 0, sizeof(su));
+      memset(&sv, 0, sizeof(sv));
+      for (int j = 0; j < kc; ++j) {
+        su.s[2 * j] = {gC_u, K, k0 + j, 0.f};
+        su.s[2 * j + 1] = {A_v, K, k0 + j, 0.f};
+        sv.s[2 * j] = {A_u, K, k0 + j, 0.f};
+        sv.s[2 * j + 1] = {gC_v, K, k0 + j, 0.f};
+      }
+      launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, st);
+      return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, st);
+    }));
+    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R4, k0 > 0 ? 1 : 0, gF1, gF2, st));
+  }
   return SFB_OK;
 }
 

@@ -17,10 +17,15 @@ struct Dims {
 // Tile constants shared by host and device code.
 constexpr int TILE_M = 128;   // TMEM lanes = rows of one accumulator tile
 constexpr int KBLK = 32;      // fp32 elements in one 128-byte swizzled row
-constexpr int MAX_KB = 8;     // feature dimension C <= MAX_KB * KBLK
+#ifndef SFB_MAX_KB
+#define SFB_MAX_KB 8
+#endif
+constexpr int MAX_KB = SFB_MAX_KB;  // feature dimension C <= MAX_KB * KBLK
 constexpr int MAX_C = MAX_KB * KBLK;
-constexpr int SWEEP_UT = 8;   // image-2 rows per correlation tile
+constexpr int SWEEP_UT = 16;  // image-2 rows per correlation tile (16 x 16 = 256 accumulator columns)
 constexpr int SWEEP_VT = 16;  // image-2 columns per correlation tile
+constexpr int GG_ROW_UT = 8;  // row tile of the image-2-major gradient GEMM: 8 x 16 image-2 pixels = 128 TMEM lanes
+constexpr int GG_ROW_VT = 16;
 constexpr int GG_UT = 2;      // image-2 rows per K-block of the gradient GEMM (image-1-major form)
 constexpr int GG_VT = 16;
 constexpr int GG_KJ = 32;     // K extent (pixels of the other image) of one gradient-GEMM block
@@ -50,26 +55,41 @@ struct SweepArgs {
   int* status;           // device status word
 };
 
-// Gradient GEMM.  G = dLoss/dS is generated from two "packed" operand sets laid out with the image-1
-// pixel index fastest, so that one warp reads 32 consecutive pixels with one 128-byte request:
-//   XU (B, H2, R, N1p)  values that depend on (pixel, u);  XV (B, W2, R, N1p)  values that depend on (pixel, v)
-// N1p = N1 rounded up to a multiple of 128, padding is zero.
-//   GRAD_COMPRESS: G[p,u,v] = sum_r XU[u,r,p] * XV[v,r,p]            (R = 2 * channels of this launch)
-//   GRAD_MAXAVG  : R = 3, slots (mean-gradient already divided by the row length, max-gradient, argmax bits):
-//                  G[p,u,v] = XU[u,0,p] + XV[v,0,p] + (XU[u,2,p]==v ? XU[u,1,p] : 0) + (XV[v,2,p]==u ? XV[v,1,p] : 0)
+// Gradient GEMM.  G = dLoss/dS is generated from two "interleaved" operand sets: for every displacement
+// and image-1 pixel, the R4 values (slots) that pixel contributes, contiguous:
+//   XU (B, H2, n1p, R4)  values that depend on (pixel, u);  XV (B, W2, n1p, R4)  values that depend on (pixel, v)
+// n1p = N1 rounded up to a multiple of 128 (padding is zero), R4 = slots rounded up to a multiple of 4, so a
+// thread fetches all slots of its pixel with 16-byte loads and a warp reads consecutive memory.
+//   GRAD_COMPRESS: G[p,u,v] = sum_r XU[u,p,r] * XV[v,p,r]            (2 slots per channel, zero padded)
+//   GRAD_MAXAVG  : slots (mean-gradient already divided by the row length, max-gradient, argmax bits, 0):
+//                  G[p,u,v] = XU[u,p,0] + XV[v,p,0] + (XU[u,p,2]==v ? XU[u,p,1] : 0) + (XV[v,p,2]==u ? XV[v,p,1] : 0)
 struct GradArgs {
   Dims d;
   int mode;
   int image2_major;      // 0: rows = image-1 pixels, output gF1; 1: rows = image-2 pixels, output gF2
-  int R;                 // slots of this launch (compile-time variants 2,4,6,8 / 3)
-  int Rtot, r0;          // slots per (u | v) in the packed arrays and first slot of this launch
-  int n1p;               // padded pixel count of the packed operands
+  int R4;                // slots per pixel in the interleaved operands: 4 or 8
+  int n1p;               // padded pixel count of the interleaved operands
   int accumulate;        // 0: out = result, 1: out += result (later channel chunks of the compression op)
   const float* xu;
   const float* xv;
   float* out;            // gF1 (B,N1,C) or gF2 (B,N2,C)
   int* status;
 };
+
+// One source of an interleaved slot: dst[b][d][p][slot] = scale * src[b][p][k][d] (raw copy when scale == 0);
+// src is (B, N1, Ksrc, D).  A null src leaves the slot zero.
+struct SlotSource {
+  const void* src;
+  int Ksrc, k;
+  float scale;
+};
+constexpr int MAX_SLOTS = 8;
+struct SlotSources {
+  SlotSource s[MAX_SLOTS];
+};
+// dst (B, D, n1p, R4) from up to R4 <= MAX_SLOTS sources; pixels N1 <= p < n1p and unused slots are zero.
+cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
+                                    cudaStream_t stream);
 
 // Rounds F1/F2 to TF32 (round-to-nearest) into the workspace copies, optionally builds the
 // row/column mean rows of F2, and clears the status word.

@@ -84,6 +84,50 @@ __global__ void unpack_kernel(const uint32_t* __restrict__ src, uint32_t* __rest
   }
 }
 
+// Interleaved pack: every block transposes a 32-pixel x 32-displacement patch of each source through
+// shared memory, then writes, per displacement, the R4 slots of its 32 pixels as one contiguous run.
+template <int R4>
+__global__ void pack_interleaved_kernel(const SlotSources src, uint32_t* __restrict__ dst, int N1, int n1p, int D) {
+  constexpr int RS = 32 * 33 + 32 / R4;  // slot stride chosen so that the interleaved read below is conflict-free
+  __shared__ uint32_t tile[R4 * RS];
+  const int b = blockIdx.z, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+#pragma unroll
+  for (int r = 0; r < R4; ++r) {
+    const uint32_t* s = static_cast<const uint32_t*>(src.s[r].src);
+    for (int j = ty; j < 32; j += 8) {
+      const int p = p0 + j, d = d0 + tx;
+      uint32_t v = 0;
+      if (s != nullptr && p < N1 && d < D) {
+        v = __ldg(s + (((size_t)b * N1 + p) * src.s[r].Ksrc + src.s[r].k) * D + d);
+        if (src.s[r].scale != 0.f) v = __float_as_uint(__uint_as_float(v) * src.s[r].scale);
+      }
+      tile[r * RS + j * 33 + tx] = v;
+    }
+  }
+  __syncthreads();
+  // 32 pixels x R4 slots = 32*R4 consecutive words per displacement
+  const int t = ty * 32 + tx;
+  for (int j = 0; j < 32; ++j) {
+    const int d = d0 + j;
+    if (d >= D) break;
+    uint32_t* row = dst + (((size_t)b * D + d) * n1p + p0) * R4;
+    for (int i = t; i < 32 * R4; i += 256) row[i] = tile[(i % R4) * RS + (i / R4) * 33 + j];
+  }
+}
+
+cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
+                                    cudaStream_t stream) {
+  const dim3 grid(n1p / 32, (D + 31) / 32, B), block(32, 8);
+  if (R4 == 4)
+    pack_interleaved_kernel<4><<<grid, block, 0, stream>>>(src, reinterpret_cast<uint32_t*>(dst), N1, n1p, D);
+  else if (R4 == 8)
+    pack_interleaved_kernel<8><<<grid, block, 0, stream>>>(src, reinterpret_cast<uint32_t*>(dst), N1, n1p, D);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
 cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,
                         int R, int r0, int rstride, float scale, cudaStream_t stream) {
   const dim3 grid(n1p / 32, (D + 31) / 32, B * K), block(32, 8);

@@ -2,16 +2,16 @@
 // accumulator in TMEM, reduced in the epilogue so that S never reaches HBM.
 //
 // One CTA owns 128 consecutive image-1 pixels of one sample (the rows / TMEM lanes of every
-// accumulator tile) and sweeps all image-2 pixels in tiles of SWEEP_UT x SWEEP_VT (8 rows x 16
-// columns = 128 accumulator columns), column-blocks outermost.  Warp roles:
+// accumulator tile) and sweeps all image-2 pixels in tiles of SWEEP_UT x SWEEP_VT (16 rows x 16
+// columns = 256 accumulator columns), column-blocks outermost.  Warp roles:
 //   warp 0      TMA producer: F1 tile once (stays resident), F2 tiles through a ring of stages
-//   warp 1      allocates TMEM, issues tcgen05.mma (TF32 in, FP32 accumulate), 4 accumulators in flight
+//   warp 1      allocates TMEM, issues tcgen05.mma (TF32 in, FP32 accumulate), 2 accumulators in flight
 //   warps 2..9  two epilogue warpgroups; in each, one thread per image-1 pixel reads its accumulator
 //               lane with tcgen05.ld.  Both groups consume every tile and split its work.
 // Everything indexed by an image-1 pixel is read and written in the packed, pixel-fastest layout
 // (kernels.h), so a warp's 32 lanes touch one 128-byte line per access.
 // Epilogues
-//   max/avg      : group g takes tile rows 4g..4g+3.  Running column-direction max(+argmax) in
+//   max/avg      : group g takes tile rows 8g..8g+7.  Running column-direction max(+argmax) in
 //                  registers across the inner row-block loop (the two groups' partial results are merged
 //                  once per column block), row-direction max(+argmax) merged through the packed output
 //                  once per tile.  The two mean channels come from extra tiles whose "image-2 pixels"
@@ -27,17 +27,20 @@
 
 namespace sfb {
 
-constexpr int SW_NSTAGE = 5;
-constexpr int SW_NACC = 4;
-constexpr int SW_TILE_N = SWEEP_UT * SWEEP_VT;  // 128 accumulator columns
+constexpr int SW_NSTAGE = 3;                    // 3 x 32 KB of F2 blocks next to the 128 KB resident F1 tile
+constexpr int SW_NACC = 2;                      // 2 x 256 TMEM columns
+constexpr int SW_TILE_N = SWEEP_UT * SWEEP_VT;  // 256 accumulator columns: tcgen05.mma issues at a fixed
+                                                // rate per instruction, so the widest N does the most work
 constexpr int SW_EPI_WARPS = 8;
 constexpr int SW_THREADS = 64 + SW_EPI_WARPS * 32;
-constexpr int SW_NMERGE = 8;                    // ring of column-merge barriers (> SW_NACC tiles of run-ahead)
+constexpr int SW_RW = SWEEP_UT / 2;             // tile rows of one epilogue warpgroup
+constexpr int SW_NMERGE = 4;                    // ring of column-merge barriers (> SW_NACC tiles of run-ahead)
 constexpr uint32_t SW_STAGE_BYTES = SW_TILE_N * KBLK * 4;
 constexpr uint32_t SW_F1_BLOCK_BYTES = TILE_M * KBLK * 4;
 constexpr uint32_t SW_TMEM_COLS = 512;
 static_assert(SW_NACC * SW_TILE_N <= 512, "accumulators exceed TMEM");
 static_assert(SW_NMERGE > SW_NACC, "a warpgroup can run SW_NACC tiles ahead of the other");
+static_assert(SW_TILE_N == 256 && SW_RW * SWEEP_VT == 128, "epilogues read two 64-column halves per warpgroup");
 
 struct SweepSmem {
   float f1[MAX_KB][TILE_M * KBLK];        // resident image-1 tile, one 128B-swizzled block per 32 channels
@@ -128,9 +131,24 @@ __device__ __forceinline__ void epi_release(SweepSmem& sm, int t, int lane) {
   if (lane == 0) mbar_arrive(&sm.acc_empty[t % SW_NACC]);
 }
 
+// Maximum of 16 values and the LOWEST index holding it: pairwise tournament, the left (lower-index)
+// entry survives ties.  Same comparison count as a linear scan but only four dependent steps.
+__device__ __forceinline__ void max16_first(const float* r, float& m, int& arg) {
+  float v8[8], v4[4], v2[2];
+  int i8[8], i4[4], i2[2];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { const bool g = r[2 * i + 1] > r[2 * i]; v8[i] = g ? r[2 * i + 1] : r[2 * i]; i8[i] = g ? 2 * i + 1 : 2 * i; }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const bool g = v8[2 * i + 1] > v8[2 * i]; v4[i] = g ? v8[2 * i + 1] : v8[2 * i]; i4[i] = g ? i8[2 * i + 1] : i8[2 * i]; }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) { const bool g = v4[2 * i + 1] > v4[2 * i]; v2[i] = g ? v4[2 * i + 1] : v4[2 * i]; i2[i] = g ? i4[2 * i + 1] : i4[2 * i]; }
+  const bool g = v2[1] > v2[0];
+  m = g ? v2[1] : v2[0];
+  arg = g ? i2[1] : i2[0];
+}
+
 template <bool ARG>
 __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const EpiCtx& e) {
-  constexpr int RW = SWEEP_UT / 2;  // tile rows of one warpgroup
   const int H2 = a.d.H2, W2 = a.d.W2;
   const size_t n1p = a.n1p;
   float* pu = a.pu + (size_t)sc.b * H2 * 3 * n1p + e.p;  // (u, slot) at pu[(u*3 + slot) * n1p]
@@ -140,46 +158,56 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
   int ca[SWEEP_VT];
   int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_main; ++t) {
-    const int v0 = vb * SWEEP_VT, ubase = ub * SWEEP_UT + e.wg * RW;
-    const int nu = min(RW, H2 - ubase), nv = min(SWEEP_VT, W2 - v0);  // nu may be <= 0
+    const int v0 = vb * SWEEP_VT, ubase = ub * SWEEP_UT + e.wg * SW_RW;
+    const int nu = min(SW_RW, H2 - ubase), nv = min(SWEEP_VT, W2 - v0);  // nu may be <= 0
     if (ub == 0) {
 #pragma unroll
       for (int j = 0; j < SWEEP_VT; ++j) { cm[j] = -CUDART_INF_F; ca[j] = 0; }
     }
     // row-direction state of earlier column blocks (issued before the wait to hide the latency)
-    float rold[RW];
+    float rold[SW_RW];
 #pragma unroll
-    for (int ul = 0; ul < RW; ++ul)
+    for (int ul = 0; ul < SW_RW; ++ul)
       rold[ul] = (vb > 0 && ul < nu) ? pu[(size_t)((ubase + ul) * 3) * n1p] : -CUDART_INF_F;
 
     if (!epi_wait(sm, a, t)) return;
-    float s[RW * SWEEP_VT];
-    tmem_ld64(e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * (RW * SWEEP_VT), s);
-    epi_release(sm, t, e.lane);  // the values are in registers: hand the accumulator back at once
-
+    const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * (SW_RW * SWEEP_VT);
 #pragma unroll
-    for (int ul = 0; ul < RW; ++ul) {
-      if (ul < nu) {  // warp-uniform
-        float* r = &s[ul * SWEEP_VT];
-        if (nv < SWEEP_VT) {
+    for (int half = 0; half < 2; ++half) {
+      float s[64];
+      tmem_ld64(tacc + half * 64, s);
+      if (half == 1) epi_release(sm, t, e.lane);  // all values are in registers: hand the accumulator back
 #pragma unroll
-          for (int j = 0; j < SWEEP_VT; ++j)
-            if (j >= nv) r[j] = -CUDART_INF_F;  // padded columns never win a max
-        }
-        float m = r[0];
-        int arg = 0;
+      for (int hl = 0; hl < SW_RW / 2; ++hl) {
+        const int ul = half * (SW_RW / 2) + hl;
+        if (ul < nu) {  // warp-uniform
+          float* r = &s[hl * SWEEP_VT];
+          if (nv < SWEEP_VT) {
 #pragma unroll
-        for (int j = 1; j < SWEEP_VT; ++j) {
-          if (r[j] > m) { m = r[j]; arg = j; }  // strict: lowest v wins ties
-        }
-        const int u = ubase + ul;
+            for (int j = 0; j < SWEEP_VT; ++j)
+              if (j >= nv) r[j] = -CUDART_INF_F;  // padded columns never win a max
+          }
+          const int u = ubase + ul;
+          float m;
+          int arg;
+          if (ARG) {
+            max16_first(r, m, arg);
 #pragma unroll
-        for (int j = 0; j < SWEEP_VT; ++j) {
-          if (r[j] > cm[j]) { cm[j] = r[j]; ca[j] = u; }  // strict: lowest u of this group wins ties
-        }
-        if (vb == 0 || m > rold[ul]) {
-          pu[(size_t)(u * 3) * n1p] = m;
-          if (ARG) pu[(size_t)(u * 3 + 2) * n1p] = __int_as_float(v0 + arg);
+            for (int j = 0; j < SWEEP_VT; ++j) {
+              if (r[j] > cm[j]) { cm[j] = r[j]; ca[j] = u; }  // strict: lowest u of this group wins ties
+            }
+          } else {
+            m = r[0];
+            arg = 0;
+#pragma unroll
+            for (int j = 1; j < SWEEP_VT; ++j) m = fmaxf(m, r[j]);
+#pragma unroll
+            for (int j = 0; j < SWEEP_VT; ++j) cm[j] = fmaxf(cm[j], r[j]);
+          }
+          if (vb == 0 || m > rold[ul]) {  // strict: the lowest column block wins ties
+            pu[(size_t)(u * 3) * n1p] = m;
+            if (ARG) pu[(size_t)(u * 3 + 2) * n1p] = __int_as_float(v0 + arg);
+          }
         }
       }
     }
@@ -225,20 +253,22 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
   const int naux = H2 + W2;
   for (int t = sc.t_main; t < sc.t_total; ++t) {
     if (!epi_wait(sm, a, t)) return;
-    const int r0 = (t - sc.t_main) * SW_TILE_N + e.wg * 64;
-    if (r0 < naux) {  // warp-uniform
-      float s[64];
-      tmem_ld64(e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * 64, s);
-      epi_release(sm, t, e.lane);
+    const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * 128;
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        const int r = r0 + j;
-        if (r < H2) pu[(size_t)(r * 3 + 1) * n1p] = s[j];
-        else if (r < naux) pv[(size_t)((r - H2) * 3 + 1) * n1p] = s[j];
+    for (int half = 0; half < 2; ++half) {
+      const int r0 = (t - sc.t_main) * SW_TILE_N + e.wg * 128 + half * 64;
+      if (r0 < naux) {  // warp-uniform
+        float s[64];
+        tmem_ld64(tacc + half * 64, s);
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int r = r0 + j;
+          if (r < H2) pu[(size_t)(r * 3 + 1) * n1p] = s[j];
+          else if (r < naux) pv[(size_t)((r - H2) * 3 + 1) * n1p] = s[j];
+        }
       }
-    } else {
-      epi_release(sm, t, e.lane);
     }
+    epi_release(sm, t, e.lane);
   }
 }
 
@@ -333,18 +363,24 @@ __device__ void epilogue_dump(SweepSmem& sm, const SweepArgs& a, const SweepSche
   float* out = a.dump + ((size_t)sc.b * N1 + (valid ? e.p : 0)) * H2 * W2;
   int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_main; ++t) {
-    const int v0 = vb * SWEEP_VT, ubase = ub * SWEEP_UT + e.wg * (SWEEP_UT / 2);
-    const int nu = min(SWEEP_UT / 2, H2 - ubase), nv = min(SWEEP_VT, W2 - v0);
+    const int v0 = vb * SWEEP_VT, ubase = ub * SWEEP_UT + e.wg * SW_RW;
+    const int nu = min(SW_RW, H2 - ubase), nv = min(SWEEP_VT, W2 - v0);
     if (!epi_wait(sm, a, t)) return;
-    float s[64];
-    tmem_ld64(e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * 64, s);
-    epi_release(sm, t, e.lane);
-    if (valid) {
+    const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * 128;
 #pragma unroll
-      for (int ul = 0; ul < SWEEP_UT / 2; ++ul)
+    for (int half = 0; half < 2; ++half) {
+      float s[64];
+      tmem_ld64(tacc + half * 64, s);
+      if (half == 1) epi_release(sm, t, e.lane);
+      if (valid) {
 #pragma unroll
-        for (int j = 0; j < SWEEP_VT; ++j)
-          if (ul < nu && j < nv) out[(size_t)(ubase + ul) * W2 + v0 + j] = s[ul * SWEEP_VT + j];
+        for (int hl = 0; hl < SW_RW / 2; ++hl)
+#pragma unroll
+          for (int j = 0; j < SWEEP_VT; ++j) {
+            const int ul = half * (SW_RW / 2) + hl;
+            if (ul < nu && j < nv) out[(size_t)(ubase + ul) * W2 + v0 + j] = s[hl * SWEEP_VT + j];
+          }
+      }
     }
     if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
