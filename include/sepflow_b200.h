@@ -66,6 +66,22 @@ size_t sfb_workspace_bytes(int op, const sfb_shape* shape);
 int sfb_max_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, const sfb_shape* shape,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  The same computation as sfb_max_avg_forward for callers that cannot
+ * allocate device memory at all -- code running inside a stream capture, under a memory pool that another
+ * component owns, in a real-time loop that must not enter the allocator, or in a host that only hands out
+ * input and output buffers.  Its scratch is a fixed array of sfb_static_scratch_bytes() bytes (32 MiB)
+ * that is part of the library image: every GPU that loads the library holds it until the process exits.
+ *   - Shapes whose scratch need (sfb_workspace_bytes(SFB_OP_MAX_AVG_FORWARD, shape)) exceeds that size are
+ *     rejected with SFB_ERR_UNSUPPORTED_SHAPE; BASELINE-style 48x64 feature maps with C=256 fit.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call outside any stream capture.  No call allocates or frees memory.
+ *   - All calls on a device share the one array, so two calls that overlap on the GPU (different streams,
+ *     or different threads) race; order them on one stream.  Contents left by an earlier call are never
+ *     read: the status word is cleared and everything else is rewritten before use. */
+int sfb_max_avg_forward_static(const float* F1, const float* F2, float* MA_u, float* MA_v, const sfb_shape* shape,
+                               void* stream);
+size_t sfb_static_scratch_bytes(void);
+
 /* Replaces MemorySaver.max_argmax_avg_forward (MemorySaver_cuda.cpp:23-34 -> MemorySaver_kernel_forward.cu:962-1016). */
 int sfb_max_argmax_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u,
                                int32_t* AM_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,

@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "sfb_max_argmax_avg_backward", "sfb_compression_forward", "sfb_compression_backward",
     "sfb_corr_volume", "sfb_device_status", "sfb_status_string", "sfb_last_error", "sfb_version",
     "sfb_kernel_timing_enable", "sfb_kernel_timing_count", "sfb_kernel_timing_read",
+    "sfb_max_avg_forward_static", "sfb_static_scratch_bytes",
 )
 
 
@@ -60,6 +61,10 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [P] * nptr + tail
+    lib.sfb_max_avg_forward_static.restype = ctypes.c_int
+    lib.sfb_max_avg_forward_static.argtypes = [P, P, P, P, SH, P]
+    lib.sfb_static_scratch_bytes.restype = SZ
+    lib.sfb_static_scratch_bytes.argtypes = []
     lib.sfb_device_status.restype = ctypes.c_int
     lib.sfb_device_status.argtypes = [P, P, ctypes.POINTER(ctypes.c_int32)]
     lib.sfb_status_string.restype = ctypes.c_char_p

@@ -341,6 +341,31 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   return SFB_OK;
 }
 
+// ---- scratch that lives in the library image, for callers that must not allocate ----
+constexpr size_t STATIC_SCRATCH_BYTES = 32u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mu;
+void* g_static_scratch_ptr[MAX_DEVICES] = {nullptr};
+
+// Device address of g_static_scratch on the current device.  In host code the symbol's name is only a
+// handle, not an address a kernel could use, so the address is looked up once per device (with that
+// device current) and cached.
+int static_scratch(void** out) {
+  int dev = -1;
+  SFB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return fail(SFB_ERR_CUDA, "device ordinal %d outside [0, %d)", dev, MAX_DEVICES);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    SFB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return SFB_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -357,6 +382,43 @@ int sfb_max_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA
                         void* workspace, size_t workspace_bytes, void* stream) {
   return run_maxavg_forward(F1, F2, MA_u, MA_v, nullptr, nullptr, false, shape, workspace, workspace_bytes, stream);
 }
+
+int sfb_max_avg_forward_static(const float* F1, const float* F2, float* MA_u, float* MA_v, const sfb_shape* shape,
+                               void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, false, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(MA_u); SFB_CHECK_PTR(MA_v);
+  const size_t need = carve(d, nullptr, plan_for(SFB_OP_MAX_AVG_FORWARD, d)).bytes;
+  if (need > STATIC_SCRATCH_BYTES)
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE,
+                "this shape needs %zu bytes of scratch but the built-in scratch holds %zu; use sfb_max_avg_forward "
+                "with a caller-provided workspace", need, (size_t)STATIC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  SFB_TRY(static_scratch(&scratch));
+  const Workspace w = carve(d, scratch, plan_for(SFB_OP_MAX_AVG_FORWARD, d));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2, tm_aux;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_TRY(map_aux(&tm_aux, d, w.aux));
+  // launch_prepare clears the status word; every other byte of the scratch that is read below is
+  // written first by these launches, so nothing depends on what an earlier call left behind
+  SFB_CUDA(launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st));
+  SweepArgs a;
+  memset(&a, 0, sizeof(a));
+  a.d = d;
+  a.mode = SWEEP_MAXAVG;
+  a.n1p = w.n1p;
+  a.pu = w.ou;
+  a.pv = w.ov;
+  a.status = w.status;
+  SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_aux, st));
+  SFB_CUDA(launch_unpack(w.ou, MA_u, d.B, d.N1(), w.n1p, 2, d.H2, MAXAVG_SLOTS, 0, 1, 2, 0, st));
+  SFB_CUDA(launch_unpack(w.ov, MA_v, d.B, d.N1(), w.n1p, 2, d.W2, MAXAVG_SLOTS, 0, 1, 2, 0, st));
+  return SFB_OK;
+}
+
+size_t sfb_static_scratch_bytes(void) { return STATIC_SCRATCH_BYTES; }
 
 int sfb_max_argmax_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u,
                                int32_t* AM_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
