@@ -131,8 +131,9 @@ def make_job(cfg, shard, device):
     return job
 
 
-def run_ops(ms, cfg, job):
-    """The hot path on device-resident inputs; returns something small that depends on the results."""
+def run_ops(ms, cfg, job, fused=True):
+    """The hot path on device-resident inputs.  With `fused` the two backward ops run as the library's
+    one-call backward (same outputs; the feature gradients of the two ops arrive already summed)."""
     F1, F2 = job["F1"], job["F2"]
     if cfg["bwd"]:
         MA_u, MA_v, AM_u, AM_v = ms.max_argmax_avg_forward(F1, F2)
@@ -142,6 +143,10 @@ def run_ops(ms, cfg, job):
     if cfg["Kc"] > 0:
         out += ms.compression_forward(F1, F2, job["A_u"], job["A_v"])
     if cfg["bwd"]:
+        if cfg["Kc"] > 0 and fused:
+            out += ms.separation_backward(F1, F2, AM_u, AM_v, job["gMA_u"], job["gMA_v"], job["A_u"], job["A_v"],
+                                          job["gC_u"], job["gC_v"])
+            return out
         if cfg["Kc"] > 0:
             out += ms.compression_backward(F1, F2, job["A_u"], job["A_v"], job["gC_u"], job["gC_v"])
         out += ms.max_argmax_avg_backward(F1, F2, AM_u, AM_v, job["gMA_u"], job["gMA_v"])
@@ -307,6 +312,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-roofline", action="store_true", help="skip the per-kernel timing pass and the TF32 peak run")
+    ap.add_argument("--unfused", action="store_true",
+                    help="run the two backward ops as the reference's two separate calls instead of the one-call backward")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small ncu captures)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
@@ -365,14 +372,14 @@ def main():
 
     # ---- device-resident throughput ("value") ----
     for _ in range(args.warmup):
-        run_ops(ms, cfg, job)
+        run_ops(ms, cfg, job, not args.unfused)
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     for _ in range(args.steps):
-        run_ops(ms, cfg, job)
+        run_ops(ms, cfg, job, not args.unfused)
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
@@ -385,7 +392,7 @@ def main():
     if not args.no_roofline:
         _lib.kernel_timing(True)
         for _ in range(min(args.steps, 3)):
-            run_ops(ms, cfg, job)
+            run_ops(ms, cfg, job, not args.unfused)
         torch.cuda.synchronize()
         report = _lib.kernel_timing_report()
         _lib.kernel_timing(False)

@@ -56,7 +56,8 @@ enum {
   SFB_OP_COMPRESSION_FORWARD = 1,
   SFB_OP_MAX_ARGMAX_AVG_BACKWARD = 2,
   SFB_OP_COMPRESSION_BACKWARD = 3,
-  SFB_OP_CORR_VOLUME = 4
+  SFB_OP_CORR_VOLUME = 4,
+  SFB_OP_SEPARATION_BACKWARD = 5
 };
 
 /* Scratch bytes an op needs for `shape` (0 if the shape is invalid). */
@@ -105,6 +106,27 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
                              const float* gC_u, const float* gC_v, float* gF1, float* gF2, float* gA_u,
                              float* gA_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
                              void* stream);
+
+/* Both backward ops in one call: gA_u, gA_v as sfb_compression_backward, and gF1 / gF2 = the SUM of the two
+ * ops' feature gradients, which is what autograd forms from MemorySaver.compression_backward and
+ * MemorySaver.max_argmax_avg_backward (functions/MemorySaver.py:71-105,140-177) when both act on the same
+ * F1, F2.  One pair of gradient GEMMs instead of two. */
+int sfb_separation_backward(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
+                            const float* gMA_u, const float* gMA_v, const float* A_u, const float* A_v,
+                            const float* gC_u, const float* gC_v, float* gF1, float* gF2, float* gA_u,
+                            float* gA_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* The two halves of sfb_separation_backward, for autograd: the attention gradients are needed as soon as the
+ * compression node runs its backward, the feature gradients can wait until the max/avg node's upstream
+ * gradients exist.  Same definitions as above (functions/MemorySaver.py:140-177 and :71-105). */
+int sfb_compression_attention_backward(const float* F1, const float* F2, const float* gC_u, const float* gC_v,
+                                       float* gA_u, float* gA_v, const sfb_shape* shape, void* workspace,
+                                       size_t workspace_bytes, void* stream);
+int sfb_separation_feature_backward(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
+                                    const float* gMA_u, const float* gMA_v, const float* A_u, const float* A_v,
+                                    const float* gC_u, const float* gC_v, float* gF1, float* gF2,
+                                    const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Test aid with no counterpart in the reference ops: writes the dense volume S (B,H1,W1,H2,W2) of a
  * SMALL problem through the same tensor-core pipeline (the reference builds it with torch.matmul,

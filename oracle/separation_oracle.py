@@ -43,6 +43,9 @@ __all__ = [
     "max_argmax_avg_backward",
     "compression_forward",
     "compression_backward",
+    "compression_attention_backward",
+    "separation_feature_backward",
+    "separation_backward",
     "top2_margins",
 ]
 
@@ -171,6 +174,35 @@ def compression_backward(F1, F2, A_u, A_v, gC_u, gC_v):
         gF1[:, r0:r1] = torch.matmul(Gf, F2f).reshape(B, r1 - r0, W1, C)
         gF2 += torch.matmul(Gf.transpose(1, 2), F1[:, r0:r1].reshape(B, -1, C)).reshape(B, H2, W2, C)
     return [gF1, gF2, gA_u, gA_v]
+
+
+def compression_attention_backward(F1, F2, gC_u, gC_v):
+    """[gA_u, gA_v] of compression_backward alone (they do not depend on the attention weights)."""
+    B, H1, W1, C = F1.shape
+    _, H2, W2, _ = F2.shape
+    Kc = gC_u.shape[3]
+    gA_u = F1.new_empty(B, H1, W1, Kc, W2)
+    gA_v = F1.new_empty(B, H1, W1, Kc, H2)
+    for r0, r1 in _row_chunks(H1, W1, H2, W2):
+        S = corr_volume(F1[:, r0:r1], F2)
+        gA_u[:, r0:r1] = torch.einsum("bijuv,bijku->bijkv", S, gC_u[:, r0:r1])
+        gA_v[:, r0:r1] = torch.einsum("bijuv,bijkv->bijku", S, gC_v[:, r0:r1])
+    return [gA_u, gA_v]
+
+
+def separation_feature_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v):
+    """[gF1, gF2] summed over the two backward ops, i.e. what autograd accumulates for the reference's
+    ComputeMaxArgmaxAvgFunction and ComputeSelfCompressionFunction
+    (libs/MemorySaver/functions/MemorySaver.py:71-105, 140-177) applied to the same F1, F2."""
+    a = max_argmax_avg_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v)
+    b = compression_backward(F1, F2, A_u, A_v, gC_u, gC_v)
+    return [a[0] + b[0], a[1] + b[1]]
+
+
+def separation_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v):
+    """[gF1, gF2, gA_u, gA_v]: both backward ops, feature gradients summed."""
+    return (separation_feature_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v)
+            + compression_attention_backward(F1, F2, gC_u, gC_v))
 
 
 def top2_margins(F1: torch.Tensor, F2: torch.Tensor):

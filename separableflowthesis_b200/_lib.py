@@ -23,6 +23,7 @@ OP_COMPRESSION_FORWARD = 1
 OP_MAX_ARGMAX_AVG_BACKWARD = 2
 OP_COMPRESSION_BACKWARD = 3
 OP_CORR_VOLUME = 4
+OP_SEPARATION_BACKWARD = 5
 
 # Every symbol include/sepflow_b200.h declares.
 EXPORTED_SYMBOLS = (
@@ -30,7 +31,8 @@ EXPORTED_SYMBOLS = (
     "sfb_max_argmax_avg_backward", "sfb_compression_forward", "sfb_compression_backward",
     "sfb_corr_volume", "sfb_device_status", "sfb_status_string", "sfb_last_error", "sfb_version",
     "sfb_kernel_timing_enable", "sfb_kernel_timing_count", "sfb_kernel_timing_read",
-    "sfb_max_avg_forward_static", "sfb_static_scratch_bytes",
+    "sfb_max_avg_forward_static", "sfb_static_scratch_bytes", "sfb_separation_backward",
+    "sfb_compression_attention_backward", "sfb_separation_feature_backward",
 )
 
 
@@ -57,7 +59,9 @@ def load() -> ctypes.CDLL:
     lib.sfb_workspace_bytes.argtypes = [ctypes.c_int, SH]
     for name, nptr in (("sfb_max_avg_forward", 4), ("sfb_max_argmax_avg_forward", 6),
                        ("sfb_max_argmax_avg_backward", 8), ("sfb_compression_forward", 6),
-                       ("sfb_compression_backward", 10), ("sfb_corr_volume", 3)):
+                       ("sfb_compression_backward", 10), ("sfb_corr_volume", 3),
+                       ("sfb_separation_backward", 14), ("sfb_compression_attention_backward", 6),
+                       ("sfb_separation_feature_backward", 12)):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [P] * nptr + tail

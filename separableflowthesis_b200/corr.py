@@ -3,7 +3,9 @@
 ever holding the 4D correlation volume.
 
 Differences from the reference that do not change results: the scaled channels-last copy of
-``fmap1`` is made once instead of once per level (core/corr.py:419 recomputes it inside the loop).
+``fmap1`` is made once instead of once per level (core/corr.py:419 recomputes it inside the loop); with
+``fuse_backward`` (default) the feature gradients of the max/avg node and the compression node of a level,
+which autograd would add, come out of one pair of gradient GEMMs instead of two.
 """
 from __future__ import annotations
 
@@ -12,7 +14,8 @@ import math
 import torch
 import torch.nn.functional as F
 
-from .functions import ComputeMaxArgmaxAvgFunction, ComputeMaxAvgFunction, ComputeSelfCompressionFunction
+from .functions import (ComputeMaxArgmaxAvgFunction, ComputeMaxAvgFunction, ComputeSelfCompressionFunction,
+                        FusedMaxArgmaxAvgFunction, FusedSelfCompressionFunction, SeparationState)
 
 
 class AlternateCorrBlockSepflow:
@@ -20,10 +23,12 @@ class AlternateCorrBlockSepflow:
     of ``fmap2``; ``guid`` must be None because non-local 4D filtering needs the stored volume
     (core/corr.py:356-358)."""
 
-    def __init__(self, fmap1, fmap2, guid, num_levels=4, radius=4, support_backward=False):
+    def __init__(self, fmap1, fmap2, guid, num_levels=4, radius=4, support_backward=False, fuse_backward=True):
         if guid is not None:
             raise Exception("Cannot use NLF while not storing the 4d correlation volume")
         self.max_avg_function = ComputeMaxArgmaxAvgFunction if support_backward else ComputeMaxAvgFunction
+        self.support_backward = support_backward
+        self.fuse_backward = fuse_backward
         self.num_levels = num_levels
         self.radius = radius
         self.fmap1_l0 = fmap1
@@ -35,7 +40,12 @@ class AlternateCorrBlockSepflow:
     def separate_level(self, F1, level, attention_weights):
         """One pyramid level: returns (sep_u (B,K,W2,H1,W1), sep_v (B,K,H2,H1,W1)) before upsampling."""
         F2 = self.pyramid[level].permute(0, 2, 3, 1).contiguous()
-        maxavg_u, maxavg_v = self.max_avg_function.apply(F1, F2)
+        fused = self.support_backward and self.fuse_backward and attention_weights is not None
+        state = SeparationState() if fused else None
+        if fused:
+            maxavg_u, maxavg_v = FusedMaxArgmaxAvgFunction.apply(F1, F2, state)
+        else:
+            maxavg_u, maxavg_v = self.max_avg_function.apply(F1, F2)
         # naming follows the reference: sep_v holds the per-u channels, sep_u the per-v channels
         sep_v = maxavg_u.permute(0, 3, 4, 1, 2).contiguous()
         sep_u = maxavg_v.permute(0, 3, 4, 1, 2).contiguous()
@@ -43,7 +53,10 @@ class AlternateCorrBlockSepflow:
             attention1, attention2 = attention_weights
             a_u = attention1(sep_u).softmax(dim=2).permute(0, 3, 4, 1, 2).contiguous()
             a_v = attention2(sep_v).softmax(dim=2).permute(0, 3, 4, 1, 2).contiguous()
-            c_u, c_v = ComputeSelfCompressionFunction.apply(F1, F2, a_u, a_v)
+            if fused:
+                c_u, c_v = FusedSelfCompressionFunction.apply(F1, F2, a_u, a_v, state)
+            else:
+                c_u, c_v = ComputeSelfCompressionFunction.apply(F1, F2, a_u, a_v)
             sep_v = torch.cat((sep_v, c_u.permute(0, 3, 4, 1, 2)), dim=1)
             sep_u = torch.cat((sep_u, c_v.permute(0, 3, 4, 1, 2)), dim=1)
         return sep_u, sep_v

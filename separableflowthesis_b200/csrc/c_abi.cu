@@ -48,7 +48,7 @@ int make_map(CUtensorMap* tm, const float* base, int rank, const uint64_t* dims,
              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
-  cuuint64_t gdim[5], gstride[4];
+  cuuint64_t gdim[5], gstride[5];
   cuuint32_t bdim[5], estride[5];
   uint64_t stride = sizeof(float);
   for (int i = 0; i < rank; ++i) {
@@ -70,12 +70,13 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // ---- optional per-kernel timing (off by default): CUDA events around each launch on its own stream ----
 enum KernelId : int {
   KID_PREPARE = 0, KID_PACK, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
-  KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_COUNT
+  KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_GRAD_FUSED_IMG1, KID_GRAD_FUSED_IMG2, KID_COUNT
 };
 const char* const kKernelNames[KID_COUNT] = {
     "prepare(round_copy+f2_means)", "pack_kernel/unpack_kernel", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
     "grad_gemm_kernel<maxavg,image1-major>", "grad_gemm_kernel<maxavg,image2-major>",
-    "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>"};
+    "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>",
+    "grad_gemm_kernel<fused,image1-major>", "grad_gemm_kernel<fused,image2-major>"};
 struct TimingRec { cudaEvent_t e0, e1; int id; int launches; };
 std::mutex g_timing_mu;
 bool g_timing_on = false;
@@ -152,6 +153,7 @@ WsPlan plan_for(int op, const Dims& d) {
     case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc, 0};
     case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, 0, 0, 4};
     case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc))};
+    case SFB_OP_SEPARATION_BACKWARD: return {false, d.Kc, d.Kc, 4 + grad_slots(chunk_channels(d.Kc))};
     default: return {false, 0, 0, 0};
   }
 }
@@ -249,6 +251,13 @@ int map_f2_tile(CUtensorMap* tm, const Dims& d, const float* F2r, uint32_t ut, u
   const uint32_t box[4] = {KBLK, vt, ut, 1};
   return make_map(tm, F2r, 4, dims, box, swizzle);
 }
+// Interleaved gradient operands (B, D, Q, n1p, 4), seen by TMA as (4*n1p, Q, D, B) so that the innermost box
+// dimension is a long contiguous run (`pixels` * 16 bytes): box = (4*pixels, Q groups, `disps` displacements, 1).
+int map_operands(CUtensorMap* tm, const float* x, int B, int D, int Q, int n1p, uint32_t pixels, uint32_t disps) {
+  const uint64_t dims[4] = {4ull * (uint64_t)n1p, (uint64_t)Q, (uint64_t)D, (uint64_t)B};
+  const uint32_t box[4] = {4 * pixels, (uint32_t)Q, disps, 1};
+  return make_map(tm, x, 4, dims, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
 int map_aux(CUtensorMap* tm, const Dims& d, const float* aux) {  // (C, H2+W2, B)
   const uint64_t dims[3] = {(uint64_t)d.C, (uint64_t)d.aux_rows(), (uint64_t)d.B};
   const uint32_t box[3] = {KBLK, (uint32_t)(SWEEP_UT * SWEEP_VT), 1};
@@ -316,7 +325,7 @@ int run_compress_sweeps(const Dims& d, const Workspace& w, const CUtensorMap& tm
 
 int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accumulate, float* gF1, float* gF2,
                   cudaStream_t st) {
-  CUtensorMap tm_y;
+  CUtensorMap tm_y, tm_xu, tm_xv;
   GradArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
@@ -327,17 +336,68 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   a.xu = w.gxu;
   a.xv = w.gxv;
   a.status = w.status;
-  // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2.
+  const int Q = R4 / 4;
+  const int kid = mode == GRAD_MAXAVG ? KID_GRAD_MAXAVG_IMG1 : (mode == GRAD_COMPRESS ? KID_GRAD_COMPRESS_IMG1 : KID_GRAD_FUSED_IMG1);
+  // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2 and 2-row blocks of XU.
   SFB_TRY(map_f2_tile(&tm_y, d, w.F2r, GG_UT, GG_VT, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, TILE_M / 2, GG_UT));  // two 64-pixel boxes per block
   a.image2_major = 0;
   a.out = gF1;
-  const int kid = mode == GRAD_MAXAVG ? KID_GRAD_MAXAVG_IMG1 : KID_GRAD_COMPRESS_IMG1;
-  SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(a, tm_y, st); }));
-  // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1.
+  SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(a, tm_y, tm_xu, tm_xu /* unused */, st); }));
+  // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1, XU and XV.
   SFB_TRY(map_f1_rows(&tm_y, d, w.F1r, GG_KJ, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, GG_KJ, GG_ROW_UT));
+  SFB_TRY(map_operands(&tm_xv, w.gxv, d.B, d.W2, Q, w.n1p, GG_KJ, GG_ROW_VT));
   a.image2_major = 1;
   a.out = gF2;
-  SFB_CUDA(timed(kid + 1, 1, st, [&] { return launch_grad_gemm(a, tm_y, st); }));
+  SFB_CUDA(timed(kid + 1, 1, st, [&] { return launch_grad_gemm(a, tm_y, tm_xu, tm_xv, st); }));
+  return SFB_OK;
+}
+
+// Interleaved slots of the max/avg backward: 0 = mean-gradient / row length, 1 = max-gradient, 2 = argmax bits.
+void maxavg_slot_sources(const Dims& d, const int32_t* AM_u, const int32_t* AM_v, const float* gMA_u,
+                         const float* gMA_v, SlotSources* su, SlotSources* sv) {
+  memset(su, 0, sizeof(*su));
+  memset(sv, 0, sizeof(*sv));
+  su->s[0] = {gMA_u, 2, 1, 1.f / (float)d.W2};
+  su->s[1] = {gMA_u, 2, 0, 0.f};
+  su->s[2] = {AM_u, 1, 0, 0.f};
+  sv->s[0] = {gMA_v, 2, 1, 1.f / (float)d.H2};
+  sv->s[1] = {gMA_v, 2, 0, 0.f};
+  sv->s[2] = {AM_v, 1, 0, 0.f};
+}
+// Interleaved slots of the compression backward for channels k0 .. k0+kc-1, local channel j:
+// XU 2j = gC_u, 2j+1 = A_v;  XV 2j = A_u, 2j+1 = gC_v, so that G[p,u,v] = sum_slots XU[u,p,slot] * XV[v,p,slot].
+void compress_slot_sources(int K, int k0, int kc, const float* A_u, const float* A_v, const float* gC_u,
+                           const float* gC_v, SlotSources* su, SlotSources* sv) {
+  memset(su, 0, sizeof(*su));
+  memset(sv, 0, sizeof(*sv));
+  for (int j = 0; j < kc; ++j) {
+    su->s[2 * j] = {gC_u, K, k0 + j, 0.f};
+    su->s[2 * j + 1] = {A_v, K, k0 + j, 0.f};
+    sv->s[2 * j] = {A_u, K, k0 + j, 0.f};
+    sv->s[2 * j + 1] = {gC_v, K, k0 + j, 0.f};
+  }
+}
+
+// Attention gradients of the compression backward: gA_v[p,k,u] = sum_v S * gC_v[p,k,v] and
+// gA_u[p,k,v] = sum_u S * gC_u[p,k,u] -- the forward compression sweep with the upstream gradients in the
+// role of the weights (w_u = gC_v, w_v = gC_u).
+int run_attention_grads(const Dims& d, const Workspace& w, const float* gC_u, const float* gC_v, float* gA_u,
+                        float* gA_v, cudaStream_t st) {
+  CUtensorMap tm_f1, tm_f2;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  const int N1 = d.N1(), K = d.Kc;
+  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+    launch_pack(gC_v, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);
+    return launch_pack(gC_u, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);
+  }));
+  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, K, 0, 0, 1, st));
+  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+    launch_unpack(w.ou, gA_v, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
+    return launch_unpack(w.ov, gA_u, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
+  }));
   return SFB_OK;
 }
 
@@ -372,8 +432,9 @@ extern "C" {
 
 size_t sfb_workspace_bytes(int op, const sfb_shape* shape) {
   Dims d;
-  if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_CORR_VOLUME) return 0;
-  const bool need_kc = op == SFB_OP_COMPRESSION_FORWARD || op == SFB_OP_COMPRESSION_BACKWARD;
+  if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_SEPARATION_BACKWARD) return 0;
+  const bool need_kc = op == SFB_OP_COMPRESSION_FORWARD || op == SFB_OP_COMPRESSION_BACKWARD ||
+                       op == SFB_OP_SEPARATION_BACKWARD;
   if (check_shape(shape, need_kc, &d) != SFB_OK) return 0;
   return carve(d, nullptr, plan_for(op, d)).bytes;
 }
@@ -463,20 +524,11 @@ int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t*
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_MAX_ARGMAX_AVG_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
-  // interleaved slots: 0 = mean-gradient / row length, 1 = max-gradient, 2 = argmax (raw bits), 3 = 0
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
-    const int N1 = d.N1();
     SlotSources su, sv;
-    memset(&su, 0, sizeof(su));
-    memset(&sv, 0, sizeof(sv));
-    su.s[0] = {gMA_u, 2, 1, 1.f / (float)d.W2};
-    su.s[1] = {gMA_u, 2, 0, 0.f};
-    su.s[2] = {AM_u, 1, 0, 0.f};
-    sv.s[0] = {gMA_v, 2, 1, 1.f / (float)d.H2};
-    sv.s[1] = {gMA_v, 2, 0, 0.f};
-    sv.s[2] = {AM_v, 1, 0, 0.f};
-    launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, 4, st);
-    return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4, st);
+    maxavg_slot_sources(d, AM_u, AM_v, gMA_u, gMA_v, &su, &sv);
+    launch_pack_interleaved(su, w.gxu, d.B, d.N1(), w.n1p, d.H2, 4, 1, 0, st);
+    return launch_pack_interleaved(sv, w.gxv, d.B, d.N1(), w.n1p, d.W2, 4, 1, 0, st);
   }));
   return run_grad_pair(d, w, GRAD_MAXAVG, 4, 0, gF1, gF2, st);
 }
@@ -492,43 +544,99 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
   const int N1 = d.N1(), K = d.Kc;
-  // gA_v[p,k,u] = sum_v S * gC_v[p,k,v]  and  gA_u[p,k,v] = sum_u S * gC_u[p,k,u]: the forward
-  // compression sweep with the upstream gradients in the role of the weights (w_u = gC_v, w_v = gC_u).
-  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
-    launch_pack(gC_v, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);
-    return launch_pack(gC_u, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);
-  }));
-  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, K, 0, 0, 1, st));
-  SFB_CUDA(timed(KID_PACK, 2, st, [&] {
-    launch_unpack(w.ou, gA_v, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
-    return launch_unpack(w.ov, gA_u, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
-  }));
+  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st));
   // gradient GEMMs, at most KC_MAX_PER_SWEEP channels per pass; later passes add to gF1 / gF2.
-  // interleaved slots of local channel j:  XU 2j = gC_u, 2j+1 = A_v;  XV 2j = A_u, 2j+1 = gC_v,
-  // so that G[p,u,v] = sum_slots XU[u,p,slot] * XV[v,p,slot].
   for (int k0 = 0; k0 < K; k0 += KC_MAX_PER_SWEEP) {
     const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
     SFB_CUDA(timed(KID_PACK, 2, st, [&] {
       SlotSources su, sv;
-      memset(&su, 0, sizeof(su));
-      memset(&sv, 0, sizeof(sv));
-      for (int j = 0; j < kc; ++j) {
-        su.s[2 * j] = {gC_u, K, k0 + j, 0.f};
-        su.s[2 * j + 1] = {A_v, K, k0 + j, 0.f};
-        sv.s[2 * j] = {A_u, K, k0 + j, 0.f};
-        sv.s[2 * j + 1] = {gC_v, K, k0 + j, 0.f};
-      }
-      launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, st);
-      return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, st);
+      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
+      launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
+      return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
     }));
     SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R4, k0 > 0 ? 1 : 0, gF1, gF2, st));
   }
   return SFB_OK;
+}
+
+int sfb_compression_attention_backward(const float* F1, const float* F2, const float* gC_u, const float* gC_v,
+                                       float* gA_u, float* gA_v, const sfb_shape* shape, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(gC_u); SFB_CHECK_PTR(gC_v); SFB_CHECK_PTR(gA_u); SFB_CHECK_PTR(gA_v);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_FORWARD, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  return run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st);
+}
+
+// Feature gradients of both backward ops from one GEMM pair (plus accumulated passes for channels beyond
+// KC_MAX_PER_SWEEP).  F1r / F2r must already hold the rounded features.
+static int run_fused_feature_grads(const Dims& d, const Workspace& w, const int32_t* AM_u, const int32_t* AM_v,
+                                   const float* gMA_u, const float* gMA_v, const float* A_u, const float* A_v,
+                                   const float* gC_u, const float* gC_v, float* gF1, float* gF2, cudaStream_t st) {
+  const int N1 = d.N1(), K = d.Kc;
+  {  // group 0 = max/avg slots, groups 1.. = the first (up to 4) compression channels; G is their sum
+    const int kc = chunk_channels(K), Qc = grad_slots(kc) / 4, Q = 1 + Qc;
+    SFB_CUDA(timed(KID_PACK, 4, st, [&] {
+      SlotSources su, sv;
+      maxavg_slot_sources(d, AM_u, AM_v, gMA_u, gMA_v, &su, &sv);
+      launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, 4, Q, 0, st);
+      launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4, Q, 0, st);
+      compress_slot_sources(K, 0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
+      launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, 4 * Qc, Q, 1, st);
+      return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4 * Qc, Q, 1, st);
+    }));
+    SFB_TRY(run_grad_pair(d, w, GRAD_FUSED, 4 * Q, 0, gF1, gF2, st));
+  }
+  for (int k0 = KC_MAX_PER_SWEEP; k0 < K; k0 += KC_MAX_PER_SWEEP) {  // remaining channels: compression form, accumulated
+    const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
+    SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+      SlotSources su, sv;
+      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
+      launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
+      return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
+    }));
+    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R4, 1, gF1, gF2, st));
+  }
+  return SFB_OK;
+}
+
+int sfb_separation_feature_backward(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
+                                    const float* gMA_u, const float* gMA_v, const float* A_u, const float* A_v,
+                                    const float* gC_u, const float* gC_v, float* gF1, float* gF2,
+                                    const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v); SFB_CHECK_PTR(gMA_u); SFB_CHECK_PTR(gMA_v);
+  SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(gC_u); SFB_CHECK_PTR(gC_v); SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_BACKWARD, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
+}
+
+int sfb_separation_backward(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
+                            const float* gMA_u, const float* gMA_v, const float* A_u, const float* A_v,
+                            const float* gC_u, const float* gC_v, float* gF1, float* gF2, float* gA_u,
+                            float* gA_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v); SFB_CHECK_PTR(gMA_u); SFB_CHECK_PTR(gMA_v);
+  SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(gC_u); SFB_CHECK_PTR(gC_v);
+  SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2); SFB_CHECK_PTR(gA_u); SFB_CHECK_PTR(gA_v);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_BACKWARD, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st));
+  return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
 }
 
 int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,

@@ -32,7 +32,7 @@ constexpr int GG_KJ = 32;     // K extent (pixels of the other image) of one gra
 constexpr int KC_MAX_PER_SWEEP = 4;  // attention channels handled by one compression sweep
 
 enum SweepMode : int { SWEEP_MAXAVG = 0, SWEEP_MAXARGAVG = 1, SWEEP_COMPRESS = 2, SWEEP_DUMP = 3 };
-enum GradMode : int { GRAD_MAXAVG = 0, GRAD_COMPRESS = 1 };
+enum GradMode : int { GRAD_MAXAVG = 0, GRAD_COMPRESS = 1, GRAD_FUSED = 2 };
 
 // Correlation sweep.  Everything indexed by an image-1 pixel is read and written in "packed" layout
 // (displacement, slot, pixel) with the pixel fastest and the pixel count padded to n1p (multiple of
@@ -56,13 +56,15 @@ struct SweepArgs {
 };
 
 // Gradient GEMM.  G = dLoss/dS is generated from two "interleaved" operand sets: for every displacement
-// and image-1 pixel, the R4 values (slots) that pixel contributes, contiguous:
-//   XU (B, H2, n1p, R4)  values that depend on (pixel, u);  XV (B, W2, n1p, R4)  values that depend on (pixel, v)
-// n1p = N1 rounded up to a multiple of 128 (padding is zero), R4 = slots rounded up to a multiple of 4, so a
-// thread fetches all slots of its pixel with 16-byte loads and a warp reads consecutive memory.
+// and image-1 pixel the R4 values (slots) that pixel contributes, in groups of four:
+//   XU (B, H2, R4/4, n1p, 4)  values that depend on (pixel, u);  XV (B, W2, R4/4, n1p, 4)  (pixel, v)
+// n1p = N1 rounded up to a multiple of 128 (padding is zero), R4 = slots rounded up to a multiple of 4.
+// One group of four slots of 32 consecutive pixels is 512 contiguous bytes: a 16-byte load per lane, or one
+// TMA box row, and conflict-free 16-byte shared-memory reads after a TMA copy.
 //   GRAD_COMPRESS: G[p,u,v] = sum_r XU[u,p,r] * XV[v,p,r]            (2 slots per channel, zero padded)
 //   GRAD_MAXAVG  : slots (mean-gradient already divided by the row length, max-gradient, argmax bits, 0):
 //                  G[p,u,v] = XU[u,p,0] + XV[v,p,0] + (XU[u,p,2]==v ? XU[u,p,1] : 0) + (XV[v,p,2]==u ? XV[v,p,1] : 0)
+//   GRAD_FUSED   : group 0 as GRAD_MAXAVG, groups 1.. as GRAD_COMPRESS; G is the sum of both
 struct GradArgs {
   Dims d;
   int mode;
@@ -76,7 +78,7 @@ struct GradArgs {
   int* status;
 };
 
-// One source of an interleaved slot: dst[b][d][p][slot] = scale * src[b][p][k][d] (raw copy when scale == 0);
+// One source of an interleaved slot: dst[b][d][slot/4][p][slot%4] = scale * src[b][p][k][d] (raw copy when scale == 0);
 // src is (B, N1, Ksrc, D).  A null src leaves the slot zero.
 struct SlotSource {
   const void* src;
@@ -87,9 +89,10 @@ constexpr int MAX_SLOTS = 8;
 struct SlotSources {
   SlotSource s[MAX_SLOTS];
 };
-// dst (B, D, n1p, R4) from up to R4 <= MAX_SLOTS sources; pixels N1 <= p < n1p and unused slots are zero.
+// Writes R4 (4 or 8) slots = R4/4 groups starting at group q0 of dst (B, D, Qtot, n1p, 4); pixels N1 <= p < n1p
+// and slots without a source are zero.
 cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
-                                    cudaStream_t stream);
+                                    int Qtot, int q0, cudaStream_t stream);
 
 // Rounds F1/F2 to TF32 (round-to-nearest) into the workspace copies, optionally builds the
 // row/column mean rows of F2, and clears the status word.
@@ -104,6 +107,9 @@ cudaError_t launch_unpack(const float* src, void* dst, int B, int N1, int n1p, i
                           int rstride, int Kdst, int kdst0, cudaStream_t stream);
 cudaError_t launch_sweep(const SweepArgs& a, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
                          const CUtensorMap& tm_aux, cudaStream_t stream);
-cudaError_t launch_grad_gemm(const GradArgs& a, const CUtensorMap& tm_y, cudaStream_t stream);
+// tm_y: features of the other image (B operand); tm_xu / tm_xv: interleaved operands (tm_xv is only read by the
+// image-2-major form; the image-1-major form keeps its (pixel, v) slots in registers).
+cudaError_t launch_grad_gemm(const GradArgs& a, const CUtensorMap& tm_y, const CUtensorMap& tm_xu,
+                             const CUtensorMap& tm_xv, cudaStream_t stream);
 
 }  // namespace sfb

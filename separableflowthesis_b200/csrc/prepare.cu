@@ -87,7 +87,8 @@ __global__ void unpack_kernel(const uint32_t* __restrict__ src, uint32_t* __rest
 // Interleaved pack: every block transposes a 32-pixel x 32-displacement patch of each source through
 // shared memory, then writes, per displacement, the R4 slots of its 32 pixels as one contiguous run.
 template <int R4>
-__global__ void pack_interleaved_kernel(const SlotSources src, uint32_t* __restrict__ dst, int N1, int n1p, int D) {
+__global__ void pack_interleaved_kernel(const SlotSources src, uint32_t* __restrict__ dst, int N1, int n1p, int D,
+                                        int Qtot, int q0) {
   constexpr int RS = 32 * 33 + 32 / R4;  // slot stride chosen so that the interleaved read below is conflict-free
   __shared__ uint32_t tile[R4 * RS];
   const int b = blockIdx.z, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
@@ -106,25 +107,25 @@ __global__ void pack_interleaved_kernel(const SlotSources src, uint32_t* __restr
     }
   }
   __syncthreads();
-  // 32 pixels x R4 slots = 32*R4 consecutive words per displacement
+  // per displacement and group of four slots: 32 pixels x 4 slots = 128 consecutive words
   const int t = ty * 32 + tx;
   for (int j = 0; j < 32; ++j) {
     const int d = d0 + j;
     if (d >= D) break;
-    uint32_t* row = dst + (((size_t)b * D + d) * n1p + p0) * R4;
-    for (int i = t; i < 32 * R4; i += 256) row[i] = tile[(i % R4) * RS + (i / R4) * 33 + j];
+    for (int i = t; i < 32 * R4; i += 256) {
+      const int q = i / 128, w = i % 128;  // group, word inside the group's 32-pixel run
+      dst[((((size_t)b * D + d) * Qtot + q0 + q) * n1p + p0) * 4 + w] = tile[(q * 4 + (w & 3)) * RS + (w >> 2) * 33 + j];
+    }
   }
 }
 
 cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
-                                    cudaStream_t stream) {
+                                    int Qtot, int q0, cudaStream_t stream) {
   const dim3 grid(n1p / 32, (D + 31) / 32, B), block(32, 8);
-  if (R4 == 4)
-    pack_interleaved_kernel<4><<<grid, block, 0, stream>>>(src, reinterpret_cast<uint32_t*>(dst), N1, n1p, D);
-  else if (R4 == 8)
-    pack_interleaved_kernel<8><<<grid, block, 0, stream>>>(src, reinterpret_cast<uint32_t*>(dst), N1, n1p, D);
-  else
-    return cudaErrorInvalidValue;
+  uint32_t* out = reinterpret_cast<uint32_t*>(dst);
+  if (R4 == 4) pack_interleaved_kernel<4><<<grid, block, 0, stream>>>(src, out, N1, n1p, D, Qtot, q0);
+  else if (R4 == 8) pack_interleaved_kernel<8><<<grid, block, 0, stream>>>(src, out, N1, n1p, D, Qtot, q0);
+  else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 

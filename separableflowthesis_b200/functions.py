@@ -67,3 +67,91 @@ class ComputeSelfCompressionFunction(Function):
             g1, g2, ga_u, ga_v = MemorySaver.compression_backward(f1, f2, a_u, a_v, grad_compressed_output_u,
                                                                   grad_compressed_output_v)
         return g1, g2, ga_u, ga_v
+
+
+# --------------------------------------------------------------------------------------------------
+# Fused backward for the call site.  Not part of the reference's surface.
+#
+# When the max/avg node and the compression node act on the same (F1, F2) -- which is how
+# AlternateCorrBlockSepflow.separate uses them (core/corr.py:425,448) -- their two feature gradients are
+# summed by autograd.  The pair of Functions below produces that sum with ONE pair of gradient GEMMs:
+# the compression node's backward returns only the attention gradients (they are needed at once, the
+# Conv3d/softmax backward sits between the two nodes) and parks its inputs in a shared state object; the
+# max/avg node's backward, which autograd always runs later because its outputs feed the attention
+# weights, then computes the summed feature gradients.
+class SeparationState:
+    """Shared between the two fused Functions of one pyramid level."""
+
+    def __init__(self):
+        self.pending = None          # (A_u, A_v, gC_u, gC_v) parked by the compression node's backward
+        self.collected = True
+
+
+def _guard_pending(state):
+    # runs when the backward pass that parked the tensors ends: they must have been consumed by then
+    def check():
+        if state.pending is not None:
+            state.pending = None
+            raise RuntimeError(
+                "fused separation backward: the compression node deferred its feature gradients but the "
+                "max/avg node's backward never ran (its outputs do not reach the loss); use "
+                "AlternateCorrBlockSepflow(..., fuse_backward=False)")
+    return check
+
+
+class FusedMaxArgmaxAvgFunction(Function):
+    @staticmethod
+    def forward(ctx, img1_features_l0, img2_features_lk, state):
+        assert img1_features_l0.is_contiguous() and img2_features_lk.is_contiguous()
+        with torch.cuda.device_of(img1_features_l0):
+            ma_u, ma_v, am_u, am_v = MemorySaver.max_argmax_avg_forward(img1_features_l0, img2_features_lk)
+        ctx.save_for_backward(img1_features_l0, img2_features_lk, am_u, am_v)
+        ctx.state = state
+        return ma_u, ma_v
+
+    @staticmethod
+    def backward(ctx, grad_MaxAvg_u, grad_MaxAvg_v):
+        f1, f2, am_u, am_v = ctx.saved_tensors
+        grad_MaxAvg_u = grad_MaxAvg_u.contiguous()
+        grad_MaxAvg_v = grad_MaxAvg_v.contiguous()
+        pending, ctx.state.pending = ctx.state.pending, None
+        with torch.cuda.device_of(grad_MaxAvg_u):
+            if pending is None:
+                g1, g2 = MemorySaver.max_argmax_avg_backward(f1, f2, am_u, am_v, grad_MaxAvg_u, grad_MaxAvg_v)
+            else:
+                a_u, a_v, gc_u, gc_v = pending
+                g1, g2 = MemorySaver.separation_feature_backward(f1, f2, am_u, am_v, grad_MaxAvg_u, grad_MaxAvg_v,
+                                                                 a_u, a_v, gc_u, gc_v)
+        return g1, g2, None
+
+
+class FusedSelfCompressionFunction(Function):
+    @staticmethod
+    def forward(ctx, img1_features_l0, img2_features_lk, attention_weights_u, attention_weights_v, state):
+        assert img1_features_l0.is_contiguous() and img2_features_lk.is_contiguous()
+        assert attention_weights_u.is_contiguous() and attention_weights_v.is_contiguous()
+        with torch.cuda.device_of(img1_features_l0):
+            c_u, c_v = MemorySaver.compression_forward(img1_features_l0, img2_features_lk,
+                                                       attention_weights_u, attention_weights_v)
+        ctx.save_for_backward(img1_features_l0, img2_features_lk, attention_weights_u, attention_weights_v)
+        ctx.state = state
+        return c_u, c_v
+
+    @staticmethod
+    def backward(ctx, grad_compressed_output_u, grad_compressed_output_v):
+        f1, f2, a_u, a_v = ctx.saved_tensors
+        gc_u = grad_compressed_output_u.contiguous()
+        gc_v = grad_compressed_output_v.contiguous()
+        with torch.cuda.device_of(gc_u):
+            if not (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]):
+                ga_u, ga_v = MemorySaver.compression_attention_backward(f1, f2, gc_u, gc_v)
+                return None, None, ga_u, ga_v, None
+            if not (ctx.needs_input_grad[2] or ctx.needs_input_grad[3]):
+                # the attention weights do not depend on the max/avg node: nothing guarantees that node's
+                # backward runs after this one, so do not defer
+                g1, g2, ga_u, ga_v = MemorySaver.compression_backward(f1, f2, a_u, a_v, gc_u, gc_v)
+                return g1, g2, ga_u, ga_v, None
+            ga_u, ga_v = MemorySaver.compression_attention_backward(f1, f2, gc_u, gc_v)
+            ctx.state.pending = (a_u, a_v, gc_u, gc_v)
+            torch.autograd.Variable._execution_engine.queue_callback(_guard_pending(ctx.state))
+        return None, None, ga_u, ga_v, None

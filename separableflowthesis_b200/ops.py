@@ -161,6 +161,71 @@ def compression_backward(img1_features_l0, img2_features_lk, attention_weights_u
     return [gF1, gF2, gA_u, gA_v]
 
 
+def separation_backward(img1_features_l0, img2_features_lk, argmax_output_u, argmax_output_v, grad_MaxAvg_u,
+                        grad_MaxAvg_v, attention_weights_u, attention_weights_v, grad_compressed_output_u,
+                        grad_compressed_output_v) -> List[torch.Tensor]:
+    """Both backward ops in one call (no counterpart in the reference's module): returns
+    [gF1, gF2, gA_u, gA_v] with gF1/gF2 the sum of what max_argmax_avg_backward and compression_backward
+    return, computed with one pair of gradient GEMMs."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_attention(s, attention_weights_u, attention_weights_v, dev)
+    _check_like(argmax_output_u, "argmax_output_u", (s.B, s.H1, s.W1, 1, s.H2), torch.int32, dev)
+    _check_like(argmax_output_v, "argmax_output_v", (s.B, s.H1, s.W1, 1, s.W2), torch.int32, dev)
+    _check_like(grad_MaxAvg_u, "grad_MaxAvg_u", (s.B, s.H1, s.W1, 2, s.H2), torch.float32, dev)
+    _check_like(grad_MaxAvg_v, "grad_MaxAvg_v", (s.B, s.H1, s.W1, 2, s.W2), torch.float32, dev)
+    _check_like(grad_compressed_output_u, "grad_compressed_output_u", (s.B, s.H1, s.W1, s.Kc, s.H2), torch.float32, dev)
+    _check_like(grad_compressed_output_v, "grad_compressed_output_v", (s.B, s.H1, s.W1, s.Kc, s.W2), torch.float32, dev)
+    gF1 = torch.empty_like(F1)
+    gF2 = torch.empty_like(F2)
+    gA_u = torch.empty_like(attention_weights_u)
+    gA_v = torch.empty_like(attention_weights_v)
+    _call("sfb_separation_backward", _lib.OP_SEPARATION_BACKWARD, s, dev,
+          (F1, F2, argmax_output_u, argmax_output_v, grad_MaxAvg_u, grad_MaxAvg_v, attention_weights_u,
+           attention_weights_v, grad_compressed_output_u, grad_compressed_output_v, gF1, gF2, gA_u, gA_v))
+    return [gF1, gF2, gA_u, gA_v]
+
+
+def compression_attention_backward(img1_features_l0, img2_features_lk, grad_compressed_output_u,
+                                   grad_compressed_output_v) -> List[torch.Tensor]:
+    """First half of separation_backward: [gA_u, gA_v] only."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check(grad_compressed_output_u, "grad_compressed_output_u", torch.float32, 5)
+    s.Kc = grad_compressed_output_u.shape[3]
+    _check_like(grad_compressed_output_u, "grad_compressed_output_u", (s.B, s.H1, s.W1, s.Kc, s.H2), torch.float32, dev)
+    _check_like(grad_compressed_output_v, "grad_compressed_output_v", (s.B, s.H1, s.W1, s.Kc, s.W2), torch.float32, dev)
+    gA_u = torch.empty(s.B, s.H1, s.W1, s.Kc, s.W2, dtype=torch.float32, device=dev)
+    gA_v = torch.empty(s.B, s.H1, s.W1, s.Kc, s.H2, dtype=torch.float32, device=dev)
+    _call("sfb_compression_attention_backward", _lib.OP_COMPRESSION_FORWARD, s, dev,
+          (F1, F2, grad_compressed_output_u, grad_compressed_output_v, gA_u, gA_v))
+    return [gA_u, gA_v]
+
+
+def separation_feature_backward(img1_features_l0, img2_features_lk, argmax_output_u, argmax_output_v,
+                                grad_MaxAvg_u, grad_MaxAvg_v, attention_weights_u, attention_weights_v,
+                                grad_compressed_output_u, grad_compressed_output_v) -> List[torch.Tensor]:
+    """Second half of separation_backward: [gF1, gF2], the summed feature gradients of both backward ops."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_attention(s, attention_weights_u, attention_weights_v, dev)
+    _check_like(argmax_output_u, "argmax_output_u", (s.B, s.H1, s.W1, 1, s.H2), torch.int32, dev)
+    _check_like(argmax_output_v, "argmax_output_v", (s.B, s.H1, s.W1, 1, s.W2), torch.int32, dev)
+    _check_like(grad_MaxAvg_u, "grad_MaxAvg_u", (s.B, s.H1, s.W1, 2, s.H2), torch.float32, dev)
+    _check_like(grad_MaxAvg_v, "grad_MaxAvg_v", (s.B, s.H1, s.W1, 2, s.W2), torch.float32, dev)
+    _check_like(grad_compressed_output_u, "grad_compressed_output_u", (s.B, s.H1, s.W1, s.Kc, s.H2), torch.float32, dev)
+    _check_like(grad_compressed_output_v, "grad_compressed_output_v", (s.B, s.H1, s.W1, s.Kc, s.W2), torch.float32, dev)
+    gF1 = torch.empty_like(F1)
+    gF2 = torch.empty_like(F2)
+    _call("sfb_separation_feature_backward", _lib.OP_SEPARATION_BACKWARD, s, dev,
+          (F1, F2, argmax_output_u, argmax_output_v, grad_MaxAvg_u, grad_MaxAvg_v, attention_weights_u,
+           attention_weights_v, grad_compressed_output_u, grad_compressed_output_v, gF1, gF2))
+    return [gF1, gF2]
+
+
 def corr_volume(img1_features_l0, img2_features_lk) -> torch.Tensor:
     """Test aid: the dense volume S (B,H1,W1,H2,W2) of a small problem, through the tensor-core pipeline."""
     F1, F2 = img1_features_l0, img2_features_lk

@@ -22,7 +22,8 @@ def oracle_backend(monkeypatch):
     monkeypatch.setattr(functions, "MemorySaver", orc)
 
 
-def test_block_matches_reference_dense_path(golden_dir, oracle_backend):
+@pytest.mark.parametrize("fuse_backward", [True, False])
+def test_block_matches_reference_dense_path(golden_dir, oracle_backend, fuse_backward):
     g = np.load(os.path.join(golden_dir, "block_dense_b2_c16_9x11_k2.npz"))
     f1 = _t(g["f1"]).requires_grad_(True)
     f2 = _t(g["f2"]).requires_grad_(True)
@@ -33,7 +34,7 @@ def test_block_matches_reference_dense_path(golden_dir, oracle_backend):
             conv.weight.copy_(_t(g[f"w{i}"]))
             conv.bias.copy_(_t(g[f"b{i}"]))
         convs.append(conv)
-    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True, fuse_backward=fuse_backward)
     sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(convs))
     assert (sep_u - _t(g["sep_u"])).abs().max().item() < 1e-11
     assert (sep_v - _t(g["sep_v"])).abs().max().item() < 1e-11
@@ -73,3 +74,20 @@ def test_ops_reject_cpu_and_malformed_tensors():
         sfb.MemorySaver.max_avg_forward(F1, F1)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         sfb.MemorySaver.compression_forward(F1, F1, F1, F1)
+
+
+def test_fused_backward_without_feature_gradients(oracle_backend):
+    """Only the attention parameters need gradients: nothing is deferred and nothing is lost."""
+    f1 = torch.randn(1, 8, 5, 6, dtype=torch.float64)
+    f2 = torch.randn(1, 8, 5, 6, dtype=torch.float64)
+    convs = [torch.nn.Conv3d(2, 2, 3, padding=1).double() for _ in range(2)]
+    outs = []
+    for fuse in (True, False):
+        for c in convs:
+            c.zero_grad()
+        blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=1, support_backward=True, fuse_backward=fuse)
+        su, sv = blk(None, sep=True, attention_weights=tuple(convs))
+        (su.sum() + (sv * sv).sum()).backward()
+        outs.append([c.weight.grad.clone() for c in convs])
+    for a, b in zip(*outs):
+        assert torch.allclose(a, b, atol=1e-12)

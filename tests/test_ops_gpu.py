@@ -144,6 +144,24 @@ def test_compression_backward(shape, cuda_device):
         assert relerr(x, r) < TOL, name
 
 
+@pytest.mark.parametrize("shape", SHAPES)
+def test_separation_backward_is_the_sum_of_both_backward_ops(shape, cuda_device):
+    """The one-call backward returns gA_u, gA_v of the compression op and gF1, gF2 = the sum of the two
+    ops' feature gradients (what autograd accumulates for the reference's two Functions)."""
+    B, H1, W1, H2, W2, C, Kc = shape
+    F1, F2, A_u, A_v, g = make_inputs(shape, 8)
+    _, _, AM_u, AM_v = orc.max_argmax_avg_forward(F1.double(), F2.double())
+    gMA_u = torch.randn(B, H1, W1, 2, H2, generator=g)
+    gMA_v = torch.randn(B, H1, W1, 2, W2, generator=g)
+    gC_u = torch.randn(B, H1, W1, Kc, H2, generator=g)
+    gC_v = torch.randn(B, H1, W1, Kc, W2, generator=g)
+    out = ops.separation_backward(*[t.to(cuda_device) for t in (F1, F2, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v)])
+    r_m = orc.max_argmax_avg_backward(F1.double(), F2.double(), AM_u, AM_v, gMA_u.double(), gMA_v.double())
+    r_c = orc.compression_backward(*[t.double() for t in (F1, F2, A_u, A_v, gC_u, gC_v)])
+    assert relerr(out[0], r_m[0] + r_c[0]) < TOL and relerr(out[1], r_m[1] + r_c[1]) < TOL
+    assert relerr(out[2], r_c[2]) < TOL and relerr(out[3], r_c[3]) < TOL
+
+
 def test_backward_is_deterministic(cuda_device):
     """Gradients accumulate in TMEM, not with atomics: two runs are bit-identical."""
     shape = (2, 24, 40, 24, 40, 128, 2)
