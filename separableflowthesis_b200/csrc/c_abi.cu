@@ -192,8 +192,8 @@ int check_shape(const sfb_shape* s, bool need_kc, Dims* d) {
     return fail(SFB_ERR_UNSUPPORTED_SHAPE, "feature dimension C=%d unsupported: need a multiple of 4 in [4, %d]", s->C,
                 MAX_C);
   if (need_kc && s->Kc < 1) return fail(SFB_ERR_INVALID_ARGUMENT, "Kc must be >= 1 (got %d)", s->Kc);
-  if ((long long)s->H1 * s->W1 > (1ll << 30) || (long long)s->H2 * s->W2 > (1ll << 30))
-    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image has more than 2^30 pixels");
+  if ((long long)s->H1 * s->W1 > (1ll << 21) || (long long)s->H2 * s->W2 > (1ll << 30))
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image 1 has more than 2^21 pixels or image 2 more than 2^30");
   {  // element offsets inside one sample's packed array are 32-bit in the kernels
     const long long n1p = ((long long)s->H1 * s->W1 + TILE_M - 1) / TILE_M * TILE_M;
     const long long slots = 8;

@@ -42,14 +42,19 @@ __global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict_
 }
 
 // Tiled transposes between the reference's per-pixel layout (B, N1, K, D) (displacement d fastest) and the
-// packed layout (B, D, R, n1p) (pixel fastest) the kernels use.  32 x 32 patches through shared memory so
-// that both the read and the write are coalesced.  grid (n1p/32, ceil(D/32), B*K), block (32, 8).
+// packed layout (B, D, R, n1p) (pixel fastest) the kernels use.  A block moves a patch of 128 pixels x 32
+// displacements through shared memory so that both sides are coalesced; every thread keeps 16 loads in flight,
+// and the displacement tiles are the fastest grid dimension so that blocks running together read neighbouring
+// 128-byte pieces of the same rows.  grid (ceil(D/32), n1p/128, B*K), block (32, 8).
+constexpr int PACK_PX = 128;
+
 __global__ void pack_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int N1, int n1p, int Ksrc,
                             int ksrc0, int K, int D, int R, int r0, int rstride, float scale) {
-  __shared__ uint32_t tile[32][33];
-  const int b = blockIdx.z / K, k = blockIdx.z - b * K, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  __shared__ uint32_t tile[PACK_PX][33];
+  const int b = blockIdx.z / K, k = blockIdx.z - b * K, d0 = blockIdx.x * 32, p0 = blockIdx.y * PACK_PX;
   const int tx = threadIdx.x, ty = threadIdx.y;
-  for (int j = ty; j < 32; j += 8) {
+#pragma unroll
+  for (int j = ty; j < PACK_PX; j += 8) {
     const int p = p0 + j, d = d0 + tx;
     uint32_t v = 0;
     if (p < N1 && d < D) v = __ldg(src + (((size_t)b * N1 + p) * Ksrc + ksrc0 + k) * D + d);
@@ -57,30 +62,33 @@ __global__ void pack_kernel(const uint32_t* __restrict__ src, uint32_t* __restri
   }
   __syncthreads();
   const int r = r0 + k * rstride;
-  for (int j = ty; j < 32; j += 8) {
-    const int d = d0 + j, p = p0 + tx;
+#pragma unroll
+  for (int i = ty; i < 32 * (PACK_PX / 32); i += 8) {
+    const int d = d0 + i / (PACK_PX / 32), p = (i % (PACK_PX / 32)) * 32 + tx;
     if (d < D) {
-      uint32_t v = tile[tx][j];
+      uint32_t v = tile[p][i / (PACK_PX / 32)];
       if (scale != 0.f) v = __float_as_uint(__uint_as_float(v) * scale);
-      dst[(((size_t)b * D + d) * R + r) * n1p + p] = v;
+      dst[(((size_t)b * D + d) * R + r) * n1p + p0 + p] = v;
     }
   }
 }
 
 __global__ void unpack_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int N1, int n1p, int K,
                               int D, int R, int r0, int rstride, int Kdst, int kdst0) {
-  __shared__ uint32_t tile[32][33];
-  const int b = blockIdx.z / K, k = blockIdx.z - b * K, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  __shared__ uint32_t tile[PACK_PX][33];
+  const int b = blockIdx.z / K, k = blockIdx.z - b * K, d0 = blockIdx.x * 32, p0 = blockIdx.y * PACK_PX;
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int r = r0 + k * rstride;
-  for (int j = ty; j < 32; j += 8) {
-    const int d = d0 + j, p = p0 + tx;
-    tile[j][tx] = (d < D) ? __ldg(src + (((size_t)b * D + d) * R + r) * n1p + p) : 0u;
+#pragma unroll
+  for (int i = ty; i < 32 * (PACK_PX / 32); i += 8) {
+    const int dl = i / (PACK_PX / 32), p = (i % (PACK_PX / 32)) * 32 + tx;
+    tile[p][dl] = (d0 + dl < D) ? __ldg(src + (((size_t)b * D + d0 + dl) * R + r) * n1p + p0 + p) : 0u;
   }
   __syncthreads();
-  for (int j = ty; j < 32; j += 8) {
+#pragma unroll
+  for (int j = ty; j < PACK_PX; j += 8) {
     const int p = p0 + j, d = d0 + tx;
-    if (p < N1 && d < D) dst[(((size_t)b * N1 + p) * Kdst + kdst0 + k) * D + d] = tile[tx][j];
+    if (p < N1 && d < D) dst[(((size_t)b * N1 + p) * Kdst + kdst0 + k) * D + d] = tile[j][tx];
   }
 }
 
@@ -91,7 +99,7 @@ __global__ void pack_interleaved_kernel(const SlotSources src, uint32_t* __restr
                                         int Qtot, int q0) {
   constexpr int RS = 32 * 33 + 32 / R4;  // slot stride chosen so that the interleaved read below is conflict-free
   __shared__ uint32_t tile[R4 * RS];
-  const int b = blockIdx.z, p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int b = blockIdx.z, d0 = blockIdx.x * 32, p0 = blockIdx.y * 32;  // displacement tiles fastest
   const int tx = threadIdx.x, ty = threadIdx.y;
 #pragma unroll
   for (int r = 0; r < R4; ++r) {
@@ -121,7 +129,7 @@ __global__ void pack_interleaved_kernel(const SlotSources src, uint32_t* __restr
 
 cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
                                     int Qtot, int q0, cudaStream_t stream) {
-  const dim3 grid(n1p / 32, (D + 31) / 32, B), block(32, 8);
+  const dim3 grid((D + 31) / 32, n1p / 32, B), block(32, 8);
   uint32_t* out = reinterpret_cast<uint32_t*>(dst);
   if (R4 == 4) pack_interleaved_kernel<4><<<grid, block, 0, stream>>>(src, out, N1, n1p, D, Qtot, q0);
   else if (R4 == 8) pack_interleaved_kernel<8><<<grid, block, 0, stream>>>(src, out, N1, n1p, D, Qtot, q0);
@@ -131,7 +139,7 @@ cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, i
 
 cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,
                         int R, int r0, int rstride, float scale, cudaStream_t stream) {
-  const dim3 grid(n1p / 32, (D + 31) / 32, B * K), block(32, 8);
+  const dim3 grid((D + 31) / 32, n1p / PACK_PX, B * K), block(32, 8);
   pack_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src), reinterpret_cast<uint32_t*>(dst), N1,
                                           n1p, Ksrc, ksrc0, K, D, R, r0, rstride, scale);
   return cudaGetLastError();
@@ -139,7 +147,7 @@ cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int
 
 cudaError_t launch_unpack(const float* src, void* dst, int B, int N1, int n1p, int K, int D, int R, int r0,
                           int rstride, int Kdst, int kdst0, cudaStream_t stream) {
-  const dim3 grid(n1p / 32, (D + 31) / 32, B * K), block(32, 8);
+  const dim3 grid((D + 31) / 32, n1p / PACK_PX, B * K), block(32, 8);
   unpack_kernel<<<grid, block, 0, stream>>>(reinterpret_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), N1,
                                             n1p, K, D, R, r0, rstride, Kdst, kdst0);
   return cudaGetLastError();
