@@ -303,6 +303,14 @@ def measure_tf32_peak(device):
 
 
 def main():
+    # Libraries (NCCL among them) print banners on stdout; keep stdout for the one JSON line by sending
+    # everything else to stderr.
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line: dict):
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -339,7 +347,7 @@ def main():
                 "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
-        print(json.dumps(line))
+        emit(line)
         return
 
     import torch.distributed as dist
@@ -458,7 +466,7 @@ def main():
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(cfg) * args.steps,
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 if __name__ == "__main__":

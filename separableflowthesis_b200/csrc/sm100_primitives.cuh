@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) features the separation kernels use:
-// mbarriers with BOUNDED waits, TMA tiled loads (no cluster multicast anywhere), tcgen05 MMA
+// mbarriers with BOUNDED waits, TMA tiled loads (each CTA fetches its own tiles), tcgen05 MMA
 // with TMEM accumulators, and the shared-memory / instruction descriptors tcgen05.mma reads.
 #pragma once
 #include <cuda.h>
