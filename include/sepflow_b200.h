@@ -57,7 +57,10 @@ enum {
   SFB_OP_MAX_ARGMAX_AVG_BACKWARD = 2,
   SFB_OP_COMPRESSION_BACKWARD = 3,
   SFB_OP_CORR_VOLUME = 4,
-  SFB_OP_SEPARATION_BACKWARD = 5
+  SFB_OP_SEPARATION_BACKWARD = 5,
+  SFB_OP_MAX_AVG_FORWARD_CF = 6,
+  SFB_OP_COMPRESSION_CF = 7,               /* compression forward and attention backward, channels-first */
+  SFB_OP_SEPARATION_FEATURE_BACKWARD_CF = 8
 };
 
 /* Scratch bytes an op needs for `shape` (0 if the shape is invalid). */
@@ -127,6 +130,28 @@ int sfb_separation_feature_backward(const float* F1, const float* F2, const int3
                                     const float* gMA_u, const float* gMA_v, const float* A_u, const float* A_v,
                                     const float* gC_u, const float* gC_v, float* gF1, float* gF2,
                                     const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Channels-first variants for the call site.  core/corr.py:428-457 permutes every op output from
+ * (B,H1,W1,K,D) to (B,K,D,H1,W1) for the Conv3d attention and permutes the attention weights back; these
+ * entry points read and write the (B,K,D,H1,W1) tensors directly (displacement-major, pixel fastest), so the
+ * call site needs no permute copies.  Same mathematics as the entry points above:
+ *   SEP_v (B,2,H2,H1,W1) = MA_u permuted, SEP_u (B,2,W2,H1,W1) = MA_v permuted, AM_u (B,H2,H1,W1), AM_v (B,W2,H1,W1),
+ *   A_u (B,Kc,W2,H1,W1), A_v (B,Kc,H2,H1,W1), C_u (B,Kc,H2,H1,W1), C_v (B,Kc,W2,H1,W1); gradients alike.
+ * AM_u / AM_v may both be NULL (inference). */
+int sfb_max_argmax_avg_forward_cf(const float* F1, const float* F2, float* SEP_v, float* SEP_u, int32_t* AM_u,
+                                  int32_t* AM_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                                  void* stream);
+int sfb_compression_forward_cf(const float* F1, const float* F2, const float* A_u, const float* A_v, float* C_u,
+                               float* C_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                               void* stream);
+int sfb_compression_attention_backward_cf(const float* F1, const float* F2, const float* gC_u, const float* gC_v,
+                                          float* gA_u, float* gA_v, const sfb_shape* shape, void* workspace,
+                                          size_t workspace_bytes, void* stream);
+int sfb_separation_feature_backward_cf(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
+                                       const float* gSEP_v, const float* gSEP_u, const float* A_u, const float* A_v,
+                                       const float* gC_u, const float* gC_v, float* gF1, float* gF2,
+                                       const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                                       void* stream);
 
 /* Test aid with no counterpart in the reference ops: writes the dense volume S (B,H1,W1,H2,W2) of a
  * SMALL problem through the same tensor-core pipeline (the reference builds it with torch.matmul,

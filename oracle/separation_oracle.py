@@ -46,6 +46,10 @@ __all__ = [
     "compression_attention_backward",
     "separation_feature_backward",
     "separation_backward",
+    "max_argmax_avg_forward_cf",
+    "compression_forward_cf",
+    "compression_attention_backward_cf",
+    "separation_feature_backward_cf",
     "top2_margins",
 ]
 
@@ -203,6 +207,39 @@ def separation_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v):
     """[gF1, gF2, gA_u, gA_v]: both backward ops, feature gradients summed."""
     return (separation_feature_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v)
             + compression_attention_backward(F1, F2, gC_u, gC_v))
+
+
+# Channels-first variants: the same results with every per-pixel tensor permuted the way the call site
+# permutes it for its Conv3d modules, (B,H1,W1,K,D) -> (B,K,D,H1,W1) (core/corr.py:428-429, 445-446).
+def _to_cf(x):
+    return x.permute(0, 3, 4, 1, 2).contiguous()
+
+
+def _from_cf(x):
+    return x.permute(0, 3, 4, 1, 2).contiguous()
+
+
+def max_argmax_avg_forward_cf(F1, F2, with_argmax=True):
+    MA_u, MA_v, AM_u, AM_v = max_argmax_avg_forward(F1, F2)
+    am_u = _to_cf(AM_u)[:, 0].contiguous() if with_argmax else None
+    am_v = _to_cf(AM_v)[:, 0].contiguous() if with_argmax else None
+    return [_to_cf(MA_u), _to_cf(MA_v), am_u, am_v]
+
+
+def compression_forward_cf(F1, F2, a_u, a_v):
+    C_u, C_v = compression_forward(F1, F2, _from_cf(a_u), _from_cf(a_v))
+    return [_to_cf(C_u), _to_cf(C_v)]
+
+
+def compression_attention_backward_cf(F1, F2, gc_u, gc_v):
+    gA_u, gA_v = compression_attention_backward(F1, F2, _from_cf(gc_u), _from_cf(gc_v))
+    return [_to_cf(gA_u), _to_cf(gA_v)]
+
+
+def separation_feature_backward_cf(F1, F2, am_u, am_v, g_sep_v, g_sep_u, a_u, a_v, gc_u, gc_v):
+    return separation_feature_backward(F1, F2, _from_cf(am_u.unsqueeze(1)), _from_cf(am_v.unsqueeze(1)),
+                                       _from_cf(g_sep_v), _from_cf(g_sep_u), _from_cf(a_u), _from_cf(a_v),
+                                       _from_cf(gc_u), _from_cf(gc_v))
 
 
 def top2_margins(F1: torch.Tensor, F2: torch.Tensor):

@@ -24,6 +24,9 @@ OP_MAX_ARGMAX_AVG_BACKWARD = 2
 OP_COMPRESSION_BACKWARD = 3
 OP_CORR_VOLUME = 4
 OP_SEPARATION_BACKWARD = 5
+OP_MAX_AVG_FORWARD_CF = 6
+OP_COMPRESSION_CF = 7
+OP_SEPARATION_FEATURE_BACKWARD_CF = 8
 
 # Every symbol include/sepflow_b200.h declares.
 EXPORTED_SYMBOLS = (
@@ -33,6 +36,8 @@ EXPORTED_SYMBOLS = (
     "sfb_kernel_timing_enable", "sfb_kernel_timing_count", "sfb_kernel_timing_read",
     "sfb_max_avg_forward_static", "sfb_static_scratch_bytes", "sfb_separation_backward",
     "sfb_compression_attention_backward", "sfb_separation_feature_backward",
+    "sfb_max_argmax_avg_forward_cf", "sfb_compression_forward_cf", "sfb_compression_attention_backward_cf",
+    "sfb_separation_feature_backward_cf",
 )
 
 
@@ -61,7 +66,9 @@ def load() -> ctypes.CDLL:
                        ("sfb_max_argmax_avg_backward", 8), ("sfb_compression_forward", 6),
                        ("sfb_compression_backward", 10), ("sfb_corr_volume", 3),
                        ("sfb_separation_backward", 14), ("sfb_compression_attention_backward", 6),
-                       ("sfb_separation_feature_backward", 12)):
+                       ("sfb_separation_feature_backward", 12), ("sfb_max_argmax_avg_forward_cf", 6),
+                       ("sfb_compression_forward_cf", 6), ("sfb_compression_attention_backward_cf", 6),
+                       ("sfb_separation_feature_backward_cf", 12)):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [P] * nptr + tail

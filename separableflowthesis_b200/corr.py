@@ -5,7 +5,9 @@ ever holding the 4D correlation volume.
 Differences from the reference that do not change results: the scaled channels-last copy of
 ``fmap1`` is made once instead of once per level (core/corr.py:419 recomputes it inside the loop); with
 ``fuse_backward`` (default) the feature gradients of the max/avg node and the compression node of a level,
-which autograd would add, come out of one pair of gradient GEMMs instead of two.
+which autograd would add, come out of one pair of gradient GEMMs instead of two; with ``channels_first``
+(default, used whenever attention weights are given) the ops read and write the (B,K,D,H1,W1) tensors of the
+Conv3d attention directly, which removes the permute copies of core/corr.py:428-429,445-446,451-452.
 """
 from __future__ import annotations
 
@@ -15,7 +17,8 @@ import torch
 import torch.nn.functional as F
 
 from .functions import (ComputeMaxArgmaxAvgFunction, ComputeMaxAvgFunction, ComputeSelfCompressionFunction,
-                        FusedMaxArgmaxAvgFunction, FusedSelfCompressionFunction, SeparationState)
+                        FusedMaxArgmaxAvgFunction, FusedSelfCompressionFunction, SeparationCompressionCF,
+                        SeparationMaxAvgCF, SeparationState)
 
 
 class AlternateCorrBlockSepflow:
@@ -23,12 +26,14 @@ class AlternateCorrBlockSepflow:
     of ``fmap2``; ``guid`` must be None because non-local 4D filtering needs the stored volume
     (core/corr.py:356-358)."""
 
-    def __init__(self, fmap1, fmap2, guid, num_levels=4, radius=4, support_backward=False, fuse_backward=True):
+    def __init__(self, fmap1, fmap2, guid, num_levels=4, radius=4, support_backward=False, fuse_backward=True,
+                 channels_first=True):
         if guid is not None:
             raise Exception("Cannot use NLF while not storing the 4d correlation volume")
         self.max_avg_function = ComputeMaxArgmaxAvgFunction if support_backward else ComputeMaxAvgFunction
         self.support_backward = support_backward
         self.fuse_backward = fuse_backward
+        self.channels_first = channels_first
         self.num_levels = num_levels
         self.radius = radius
         self.fmap1_l0 = fmap1
@@ -40,6 +45,14 @@ class AlternateCorrBlockSepflow:
     def separate_level(self, F1, level, attention_weights):
         """One pyramid level: returns (sep_u (B,K,W2,H1,W1), sep_v (B,K,H2,H1,W1)) before upsampling."""
         F2 = self.pyramid[level].permute(0, 2, 3, 1).contiguous()
+        if self.channels_first and self.fuse_backward and attention_weights is not None:
+            state = SeparationState()
+            sep_v, sep_u = SeparationMaxAvgCF.apply(F1, F2, state, self.support_backward)
+            attention1, attention2 = attention_weights
+            a_u = attention1(sep_u).softmax(dim=2)
+            a_v = attention2(sep_v).softmax(dim=2)
+            c_u, c_v = SeparationCompressionCF.apply(F1, F2, a_u.contiguous(), a_v.contiguous(), state)
+            return torch.cat((sep_u, c_v), dim=1), torch.cat((sep_v, c_u), dim=1)
         fused = self.support_backward and self.fuse_backward and attention_weights is not None
         state = SeparationState() if fused else None
         if fused:

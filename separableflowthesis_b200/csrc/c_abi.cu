@@ -141,6 +141,15 @@ struct Workspace {
 
 int padded_pixels(const Dims& d) { return (d.N1() + TILE_M - 1) / TILE_M * TILE_M; }
 
+// (B, D, slots, n1p) workspace array, optionally starting at slot `slot0`
+PixView packed_view(float* base, int D, int slots, int n1p, int slot0 = 0) {
+  return PixView{base + (size_t)slot0 * n1p, (long long)D * slots * n1p, (uint32_t)(slots * n1p), (uint32_t)n1p};
+}
+// (B, slots, D, N1) user tensor
+PixView cf_view(const void* base, int slots, int D, int N1) {
+  return PixView{static_cast<float*>(const_cast<void*>(base)), (long long)slots * D * N1, (uint32_t)N1, (uint32_t)(D * N1)};
+}
+
 // What an op keeps in the workspace: the mean rows of F2, Rx packed input slots, Ro packed output slots.
 struct WsPlan { bool aux; int Rx; int Ro; int Rg; };
 constexpr int MAXAVG_SLOTS = 3;  // max, mean, argmax bits
@@ -154,6 +163,9 @@ WsPlan plan_for(int op, const Dims& d) {
     case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, 0, 0, 4};
     case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc))};
     case SFB_OP_SEPARATION_BACKWARD: return {false, d.Kc, d.Kc, 4 + grad_slots(chunk_channels(d.Kc))};
+    case SFB_OP_MAX_AVG_FORWARD_CF: return {true, 0, 0, 0};
+    case SFB_OP_COMPRESSION_CF: return {false, 0, 0, 0};
+    case SFB_OP_SEPARATION_FEATURE_BACKWARD_CF: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc))};
     default: return {false, 0, 0, 0};
   }
 }
@@ -282,9 +294,11 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
-  a.n1p = w.n1p;
-  a.pu = w.ou;
-  a.pv = w.ov;
+  a.n_valid = w.n1p;
+  a.pu = packed_view(w.ou, d.H2, MAXAVG_SLOTS, w.n1p);
+  a.pv = packed_view(w.ov, d.W2, MAXAVG_SLOTS, w.n1p);
+  a.pu_arg = packed_view(w.ou, d.H2, MAXAVG_SLOTS, w.n1p, 2);
+  a.pv_arg = packed_view(w.ov, d.W2, MAXAVG_SLOTS, w.n1p, 2);
   a.status = w.status;
   SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
   // packed (displacement, slot, pixel) -> the reference's (pixel, channel, displacement) tensors
@@ -301,23 +315,23 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   return SFB_OK;
 }
 
-// OU slot k = sum_v S * w_u[k], OV slot k = sum_u S * w_v[k] for all Kc channels, at most
-// KC_MAX_PER_SWEEP channels per sweep.  Weights are slots (slot0 + k*stride) of the packed inputs.
-int run_compress_sweeps(const Dims& d, const Workspace& w, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
-                        int Rw, int wu_slot0, int wv_slot0, int w_stride, cudaStream_t st) {
+// ou(b,u,k,p) = sum_v S * w_u[k], ov(b,v,k,p) = sum_u S * w_v[k] for all Kc channels, at most KC_MAX_PER_SWEEP
+// channels per sweep.  Weight k is slot (slot0 + k*stride) of the views xu (per u: w_v) / xv (per v: w_u).
+int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2, PixView xu,
+                        PixView xv, int wu_slot0, int wv_slot0, int w_stride, PixView ou, PixView ov, int n_valid,
+                        cudaStream_t st) {
   for (int k0 = 0; k0 < d.Kc; k0 += KC_MAX_PER_SWEEP) {
     SweepArgs a;
     memset(&a, 0, sizeof(a));
     a.d = d;
     a.mode = SWEEP_COMPRESS;
-    a.n1p = w.n1p;
+    a.n_valid = n_valid;
     a.k0 = k0;
     a.kc = chunk_channels(d.Kc - k0);
-    a.xu = w.xu; a.xv = w.xv;
-    a.Rw = Rw; a.wu_slot0 = wu_slot0; a.wv_slot0 = wv_slot0; a.w_stride = w_stride;
-    a.ou = w.ou; a.ov = w.ov;
-    a.Ro = d.Kc;
-    a.status = w.status;
+    a.xu = xu; a.xv = xv;
+    a.wu_slot0 = wu_slot0; a.wv_slot0 = wv_slot0; a.w_stride = w_stride;
+    a.ou = ou; a.ov = ov;
+    a.status = status;
     SFB_CUDA(timed(KID_SWEEP_COMPRESS, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));
   }
   return SFB_OK;
@@ -393,7 +407,8 @@ int run_attention_grads(const Dims& d, const Workspace& w, const float* gC_u, co
     launch_pack(gC_v, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);
     return launch_pack(gC_u, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);
   }));
-  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, K, 0, 0, 1, st));
+  SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, packed_view(w.xu, d.H2, K, w.n1p), packed_view(w.xv, d.W2, K, w.n1p),
+                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_unpack(w.ou, gA_v, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
     return launch_unpack(w.ov, gA_u, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
@@ -432,9 +447,10 @@ extern "C" {
 
 size_t sfb_workspace_bytes(int op, const sfb_shape* shape) {
   Dims d;
-  if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_SEPARATION_BACKWARD) return 0;
+  if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_SEPARATION_FEATURE_BACKWARD_CF) return 0;
   const bool need_kc = op == SFB_OP_COMPRESSION_FORWARD || op == SFB_OP_COMPRESSION_BACKWARD ||
-                       op == SFB_OP_SEPARATION_BACKWARD;
+                       op == SFB_OP_SEPARATION_BACKWARD || op == SFB_OP_COMPRESSION_CF ||
+                       op == SFB_OP_SEPARATION_FEATURE_BACKWARD_CF;
   if (check_shape(shape, need_kc, &d) != SFB_OK) return 0;
   return carve(d, nullptr, plan_for(op, d)).bytes;
 }
@@ -469,9 +485,9 @@ int sfb_max_avg_forward_static(const float* F1, const float* F2, float* MA_u, fl
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = SWEEP_MAXAVG;
-  a.n1p = w.n1p;
-  a.pu = w.ou;
-  a.pv = w.ov;
+  a.n_valid = w.n1p;
+  a.pu = packed_view(w.ou, d.H2, MAXAVG_SLOTS, w.n1p);
+  a.pv = packed_view(w.ov, d.W2, MAXAVG_SLOTS, w.n1p);
   a.status = w.status;
   SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_aux, st));
   SFB_CUDA(launch_unpack(w.ou, MA_u, d.B, d.N1(), w.n1p, 2, d.H2, MAXAVG_SLOTS, 0, 1, 2, 0, st));
@@ -505,7 +521,8 @@ int sfb_compression_forward(const float* F1, const float* F2, const float* A_u, 
     launch_pack(A_u, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);         // w_u[k][v] = XV slot k
     return launch_pack(A_v, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);  // w_v[k][u] = XU slot k
   }));
-  SFB_TRY(run_compress_sweeps(d, w, tm_f1, tm_f2, K, 0, 0, 1, st));
+  SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, packed_view(w.xu, d.H2, K, w.n1p), packed_view(w.xv, d.W2, K, w.n1p),
+                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_unpack(w.ou, C_u, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
     return launch_unpack(w.ov, C_v, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
@@ -639,6 +656,111 @@ int sfb_separation_backward(const float* F1, const float* F2, const int32_t* AM_
   return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
 }
 
+int sfb_max_argmax_avg_forward_cf(const float* F1, const float* F2, float* SEP_v, float* SEP_u, int32_t* AM_u,
+                                  int32_t* AM_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                                  void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, false, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(SEP_v); SFB_CHECK_PTR(SEP_u);
+  const bool with_argmax = AM_u != nullptr || AM_v != nullptr;
+  if (with_argmax) { SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v); }
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_MAX_AVG_FORWARD_CF, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2, tm_aux;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_TRY(map_aux(&tm_aux, d, w.aux));
+  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st); }));
+  const int N1 = d.N1();
+  SweepArgs a;
+  memset(&a, 0, sizeof(a));
+  a.d = d;
+  a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
+  a.n_valid = N1;
+  a.pu = cf_view(SEP_v, 2, d.H2, N1);       // per-u channels live in the tensor the call site calls sep_v
+  a.pv = cf_view(SEP_u, 2, d.W2, N1);
+  a.pu_arg = cf_view(AM_u, 1, d.H2, N1);
+  a.pv_arg = cf_view(AM_v, 1, d.W2, N1);
+  a.status = w.status;
+  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
+  return SFB_OK;
+}
+
+// compression sweep on channels-first weights / outputs (forward, or attention gradients with the upstream
+// gradients as weights)
+static int run_compress_cf(const float* F1, const float* F2, const float* W_u, const float* W_v, float* O_u, float* O_v,
+                           const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(W_u); SFB_CHECK_PTR(W_v); SFB_CHECK_PTR(O_u); SFB_CHECK_PTR(O_v);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_CF, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  const int N1 = d.N1(), K = d.Kc;
+  // W_u (B,K,W2,N1) weights per v, W_v (B,K,H2,N1) per u; O_u (B,K,H2,N1), O_v (B,K,W2,N1)
+  return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(W_v, K, d.H2, N1), cf_view(W_u, K, d.W2, N1), 0, 0, 1,
+                             cf_view(O_u, K, d.H2, N1), cf_view(O_v, K, d.W2, N1), N1, st);
+}
+
+int sfb_compression_forward_cf(const float* F1, const float* F2, const float* A_u, const float* A_v, float* C_u,
+                               float* C_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  return run_compress_cf(F1, F2, A_u, A_v, C_u, C_v, shape, workspace, workspace_bytes, stream);
+}
+
+int sfb_compression_attention_backward_cf(const float* F1, const float* F2, const float* gC_u, const float* gC_v,
+                                          float* gA_u, float* gA_v, const sfb_shape* shape, void* workspace,
+                                          size_t workspace_bytes, void* stream) {
+  // gA_v(b,k,u,p) = sum_v S * gC_v(b,k,v,p), gA_u(b,k,v,p) = sum_u S * gC_u(b,k,u,p)
+  return run_compress_cf(F1, F2, gC_v, gC_u, gA_v, gA_u, shape, workspace, workspace_bytes, stream);
+}
+
+int sfb_separation_feature_backward_cf(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
+                                       const float* gSEP_v, const float* gSEP_u, const float* A_u, const float* A_v,
+                                       const float* gC_u, const float* gC_v, float* gF1, float* gF2,
+                                       const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                                       void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v); SFB_CHECK_PTR(gSEP_v); SFB_CHECK_PTR(gSEP_u);
+  SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(gC_u); SFB_CHECK_PTR(gC_v); SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2);
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_FEATURE_BACKWARD_CF, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  const int N1 = d.N1(), K = d.Kc;
+  {
+    const int kc = chunk_channels(K), Qc = grad_slots(kc) / 4, Q = 1 + Qc;
+    SFB_CUDA(timed(KID_PACK, 4, st, [&] {
+      SlotSources su, sv;
+      // channel 0 of gSEP = max gradient, channel 1 = mean gradient (same slots as the reference layout)
+      maxavg_slot_sources(d, AM_u, AM_v, gSEP_v, gSEP_u, &su, &sv);
+      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4, Q, 0, st);
+      launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4, Q, 0, st);
+      compress_slot_sources(K, 0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
+      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4 * Qc, Q, 1, st);
+      return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4 * Qc, Q, 1, st);
+    }));
+    SFB_TRY(run_grad_pair(d, w, GRAD_FUSED, 4 * Q, 0, gF1, gF2, st));
+  }
+  for (int k0 = KC_MAX_PER_SWEEP; k0 < K; k0 += KC_MAX_PER_SWEEP) {
+    const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
+    SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+      SlotSources su, sv;
+      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
+      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
+      return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
+    }));
+    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R4, 1, gF1, gF2, st));
+  }
+  return SFB_OK;
+}
+
 int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,
                     size_t workspace_bytes, void* stream) {
   Dims d;
@@ -655,7 +777,7 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = SWEEP_DUMP;
-  a.n1p = w.n1p;
+  a.n_valid = w.n1p;
   a.dump = S;
   a.status = w.status;
   SFB_CUDA(timed(KID_SWEEP_DUMP, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));

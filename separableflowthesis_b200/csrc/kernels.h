@@ -34,23 +34,32 @@ constexpr int KC_MAX_PER_SWEEP = 4;  // attention channels handled by one compre
 enum SweepMode : int { SWEEP_MAXAVG = 0, SWEEP_MAXARGAVG = 1, SWEEP_COMPRESS = 2, SWEEP_DUMP = 3 };
 enum GradMode : int { GRAD_MAXAVG = 0, GRAD_COMPRESS = 1, GRAD_FUSED = 2 };
 
-// Correlation sweep.  Everything indexed by an image-1 pixel is read and written in "packed" layout
-// (displacement, slot, pixel) with the pixel fastest and the pixel count padded to n1p (multiple of
-// 128), so that the 32 lanes of a warp (32 consecutive pixels) touch one 128-byte line:
-//   max/avg    : outputs PU (B, H2, 3, n1p), PV (B, W2, 3, n1p); slots 0 = max, 1 = mean, 2 = argmax bits
-//   compression: weights  w_v[k][u] = XU[b][u][wv_slot0 + k*w_stride][p]   (B, H2, Rw, n1p)
-//                         w_u[k][v] = XV[b][v][wu_slot0 + k*w_stride][p]   (B, W2, Rw, n1p)
-//                outputs  OU (B, H2, Ro, n1p) slot k = sum_v S*w_u,  OV (B, W2, Ro, n1p) slot k = sum_u S*w_v
+// A tensor indexed by (sample b, displacement d, slot, image-1 pixel p) with the pixel fastest:
+// element at base + b*sb + d*sd + slot*ss + p.  Two instances of this are used:
+//   "packed"         workspace arrays (B, D, slots, n1p): sb = D*slots*n1p, sd = slots*n1p, ss = n1p
+//   "channels-first" user tensors   (B, slots, D, N1)  : sb = slots*D*N1,  sd = N1,        ss = D*N1
+// (the layout torch's Conv3d produces and consumes at the call site, core/corr.py:437-446).
+struct PixView {
+  float* base;
+  long long sb;      // elements between samples
+  uint32_t sd, ss;   // elements between displacements / slots (one sample spans < 2^32 elements: host-checked)
+};
+
+// Correlation sweep.  Everything indexed by an image-1 pixel is read and written through PixViews, so a
+// warp's 32 lanes (32 consecutive pixels) touch one or two 128-byte lines per access.
+//   max/avg    : outputs pu (per u) / pv (per v): slots 0 = max, 1 = mean; argmax (int32 bits) in pu_arg / pv_arg
+//   compression: weights  w_v[k][u] = xu(b, u, wv_slot0 + k*w_stride, p),  w_u[k][v] = xv(b, v, wu_slot0 + k*w_stride, p)
+//                outputs  ou(b, u, k, p) = sum_v S*w_u,  ov(b, v, k, p) = sum_u S*w_v
+// Lanes with p >= n_valid compute but never touch memory (n_valid = n1p for packed arrays, N1 otherwise).
 struct SweepArgs {
   Dims d;
   int mode;
-  int n1p;
+  int n_valid;
   int k0, kc;            // compression: first channel and number of channels (<= KC_MAX_PER_SWEEP) of this launch
-  float* pu; float* pv;  // max/avg packed outputs
-  const float* xu; const float* xv;
-  int Rw, wu_slot0, wv_slot0, w_stride;
-  float* ou; float* ov;
-  int Ro;
+  PixView pu, pv, pu_arg, pv_arg;
+  PixView xu, xv;
+  int wu_slot0, wv_slot0, w_stride;
+  PixView ou, ov;
   float* dump;           // SWEEP_DUMP: dense S (B,N1,H2,W2), test use only
   int* status;           // device status word
 };
@@ -89,6 +98,9 @@ constexpr int MAX_SLOTS = 8;
 struct SlotSources {
   SlotSource s[MAX_SLOTS];
 };
+// Same, from channels-first sources: dst[b][d][q][p][j] = scale * src[b][k][d][p], src is (B, Ksrc, D, N1).
+cudaError_t launch_pack_interleaved_cf(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
+                                       int Qtot, int q0, cudaStream_t stream);
 // Writes R4 (4 or 8) slots = R4/4 groups starting at group q0 of dst (B, D, Qtot, n1p, 4); pixels N1 <= p < n1p
 // and slots without a source are zero.
 cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,

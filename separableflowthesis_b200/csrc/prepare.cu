@@ -137,6 +137,40 @@ cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, i
   return cudaGetLastError();
 }
 
+// Channels-first sources are already pixel-fastest: one thread per pixel gathers the four slots of a group
+// and stores them as one 16-byte word.  grid (n1p/256, D, B), block 256.
+template <int Q>
+__global__ void pack_interleaved_cf_kernel(const SlotSources src, float4* __restrict__ dst, int N1, int n1p, int D,
+                                           int Qtot, int q0) {
+  const int p = blockIdx.x * 256 + threadIdx.x, d = blockIdx.y, b = blockIdx.z;
+  if (p >= n1p) return;
+#pragma unroll
+  for (int q = 0; q < Q; ++q) {
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const SlotSource& ss = src.s[4 * q + j];
+      uint32_t w = 0;
+      if (ss.src != nullptr && p < N1) {
+        w = __ldg(static_cast<const uint32_t*>(ss.src) + (((size_t)b * ss.Ksrc + ss.k) * D + d) * N1 + p);
+        if (ss.scale != 0.f) w = __float_as_uint(__uint_as_float(w) * ss.scale);
+      }
+      v[j] = __uint_as_float(w);
+    }
+    dst[(((size_t)b * D + d) * Qtot + q0 + q) * n1p + p] = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
+cudaError_t launch_pack_interleaved_cf(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
+                                       int Qtot, int q0, cudaStream_t stream) {
+  const dim3 grid((n1p + 255) / 256, D, B);
+  float4* out = reinterpret_cast<float4*>(dst);
+  if (R4 == 4) pack_interleaved_cf_kernel<1><<<grid, 256, 0, stream>>>(src, out, N1, n1p, D, Qtot, q0);
+  else if (R4 == 8) pack_interleaved_cf_kernel<2><<<grid, 256, 0, stream>>>(src, out, N1, n1p, D, Qtot, q0);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
 cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,
                         int R, int r0, int rstride, float scale, cudaStream_t stream) {
   const dim3 grid((D + 31) / 32, n1p / PACK_PX, B * K), block(32, 8);

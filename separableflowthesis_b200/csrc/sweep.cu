@@ -112,7 +112,8 @@ __device__ void sweep_mma(SweepSmem& sm, const SweepArgs& a, const SweepSched& s
 struct EpiCtx {
   int wg;           // epilogue warpgroup 0 / 1
   int lane;
-  int p;            // pixel index inside the padded sample: m0 + 32*quarter + lane  (< n1p)
+  int p;            // pixel index inside the sample: m0 + 32*quarter + lane
+  bool valid;       // p < n_valid: lanes past the end compute but never touch memory
   uint32_t tbase;   // TMEM address of this warp's lane quarter, column 0
 };
 
@@ -150,9 +151,13 @@ __device__ __forceinline__ void max16_first(const float* r, float& m, int& arg) 
 template <bool ARG>
 __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const EpiCtx& e) {
   const int H2 = a.d.H2, W2 = a.d.W2;
-  const size_t n1p = a.n1p;
-  float* pu = a.pu + (size_t)sc.b * H2 * 3 * n1p + e.p;  // (u, slot) at pu[(u*3 + slot) * n1p]
-  float* pv = a.pv + (size_t)sc.b * W2 * 3 * n1p + e.p;
+  // per-thread views: value of (displacement d, slot) at ptr[d*sd + slot*ss]
+  float* pu = a.pu.base + sc.b * a.pu.sb + e.p;
+  float* pv = a.pv.base + sc.b * a.pv.sb + e.p;
+  float* pua = ARG ? a.pu_arg.base + sc.b * a.pu_arg.sb + e.p : nullptr;
+  float* pva = ARG ? a.pv_arg.base + sc.b * a.pv_arg.sb + e.p : nullptr;
+  const uint32_t usd = a.pu.sd, uss = a.pu.ss, vsd = a.pv.sd, vss = a.pv.ss, uasd = a.pu_arg.sd, vasd = a.pv_arg.sd;
+  const bool valid = e.valid;
 
   float cm[SWEEP_VT];
   int ca[SWEEP_VT];
@@ -168,7 +173,7 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
     float rold[SW_RW];
 #pragma unroll
     for (int ul = 0; ul < SW_RW; ++ul)
-      rold[ul] = (vb > 0 && ul < nu) ? pu[(size_t)((ubase + ul) * 3) * n1p] : -CUDART_INF_F;
+      rold[ul] = (valid && vb > 0 && ul < nu) ? pu[(ubase + ul) * usd] : -CUDART_INF_F;
 
     if (!epi_wait(sm, a, t)) return;
     const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N + e.wg * (SW_RW * SWEEP_VT);
@@ -204,9 +209,9 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
 #pragma unroll
             for (int j = 0; j < SWEEP_VT; ++j) cm[j] = fmaxf(cm[j], r[j]);
           }
-          if (vb == 0 || m > rold[ul]) {  // strict: the lowest column block wins ties
-            pu[(size_t)(u * 3) * n1p] = m;
-            if (ARG) pu[(size_t)(u * 3 + 2) * n1p] = __int_as_float(v0 + arg);
+          if (valid && (vb == 0 || m > rold[ul])) {  // strict: the lowest column block wins ties
+            pu[u * usd] = m;
+            if (ARG) pua[u * uasd] = __int_as_float(v0 + arg);
           }
         }
       }
@@ -217,9 +222,9 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
       if (e.wg == 1) {
 #pragma unroll
         for (int j = 0; j < SWEEP_VT; ++j) {
-          if (j < nv) {
-            pv[(size_t)((v0 + j) * 3) * n1p] = cm[j];
-            if (ARG) pv[(size_t)((v0 + j) * 3 + 2) * n1p] = __int_as_float(ca[j]);
+          if (valid && j < nv) {
+            pv[(v0 + j) * vsd] = cm[j];
+            if (ARG) pva[(v0 + j) * vasd] = __int_as_float(ca[j]);
           }
         }
         __threadfence_block();
@@ -230,15 +235,16 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
         if (!__all_sync(0xffffffffu, ok)) return;
 #pragma unroll
         for (int j = 0; j < SWEEP_VT; ++j) {
-          if (j < nv) {
-            float* dst = pv + (size_t)((v0 + j) * 3) * n1p;
+          if (valid && j < nv) {
+            float* dst = pv + (v0 + j) * vsd;
             const float om = __ldcg(dst);
             float best = cm[j];
             int besta = ca[j];
             if (ARG) {
-              const int oa = __float_as_int(__ldcg(dst + 2 * n1p));
+              float* dsta = pva + (v0 + j) * vasd;
+              const int oa = __float_as_int(__ldcg(dsta));
               if (om > best || (om == best && oa < besta)) { best = om; besta = oa; }  // lowest u on ties
-              dst[2 * n1p] = __int_as_float(besta);
+              *dsta = __int_as_float(besta);
             } else {
               best = fmaxf(best, om);
             }
@@ -263,8 +269,9 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
           const int r = r0 + j;
-          if (r < H2) pu[(size_t)(r * 3 + 1) * n1p] = s[j];
-          else if (r < naux) pv[(size_t)((r - H2) * 3 + 1) * n1p] = s[j];
+          if (!valid) continue;
+          if (r < H2) pu[r * usd + uss] = s[j];
+          else if (r < naux) pv[(r - H2) * vsd + vss] = s[j];
         }
       }
     }
@@ -275,19 +282,23 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
 __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const EpiCtx& e) {
   constexpr int KW = KC_MAX_PER_SWEEP / 2;  // channels of one warpgroup: local channels wg, wg + 2
   const int H2 = a.d.H2, W2 = a.d.W2;
-  const size_t n1p = a.n1p;
-  const float* xu = a.xu + (size_t)sc.b * H2 * a.Rw * n1p + e.p;
-  const float* xv = a.xv + (size_t)sc.b * W2 * a.Rw * n1p + e.p;
-  float* ou = a.ou + (size_t)sc.b * H2 * a.Ro * n1p + e.p;
-  float* ov = a.ov + (size_t)sc.b * W2 * a.Ro * n1p + e.p;
-  int nk = 0, wu_slot[KW], wv_slot[KW], o_slot[KW];
+  const bool valid = e.valid;
+  const uint32_t xusd = a.xu.sd, xvsd = a.xv.sd, ousd = a.ou.sd, ovsd = a.ov.sd;
+  // this thread's pixel in sample b of each view; (displacement d, slot) at ptr[d*sd + slot*ss], 32-bit offsets
+  const float* xu = a.xu.base + sc.b * a.xu.sb + e.p;
+  const float* xv = a.xv.base + sc.b * a.xv.sb + e.p;
+  float* ou = a.ou.base + sc.b * a.ou.sb + e.p;
+  float* ov = a.ov.base + sc.b * a.ov.sb + e.p;
+  int nk = 0;
+  uint32_t wu_off[KW], wv_off[KW], ou_off[KW], ov_off[KW];  // slot offsets of this group's channels
 #pragma unroll
   for (int j = 0; j < KW; ++j) {
     const int kl = e.wg + 2 * j;
     if (kl < a.kc) nk = j + 1;
-    wu_slot[j] = a.wu_slot0 + (a.k0 + kl) * a.w_stride;
-    wv_slot[j] = a.wv_slot0 + (a.k0 + kl) * a.w_stride;
-    o_slot[j] = a.k0 + kl;
+    wu_off[j] = (a.wu_slot0 + (a.k0 + kl) * a.w_stride) * a.xv.ss;
+    wv_off[j] = (a.wv_slot0 + (a.k0 + kl) * a.w_stride) * a.xu.ss;
+    ou_off[j] = (a.k0 + kl) * a.ou.ss;
+    ov_off[j] = (a.k0 + kl) * a.ov.ss;
   }
 
   float au[KW][SWEEP_VT], cv[KW][SWEEP_VT];
@@ -300,7 +311,7 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
       for (int j = 0; j < KW; ++j)
 #pragma unroll
         for (int i = 0; i < SWEEP_VT; ++i) {
-          au[j][i] = (j < nk && i < nv) ? __ldg(xv + (size_t)((v0 + i) * a.Rw + wu_slot[j]) * n1p) : 0.f;
+          au[j][i] = (valid && j < nk && i < nv) ? __ldg(xv + ((v0 + i) * xvsd + wu_off[j])) : 0.f;
           cv[j][i] = 0.f;
         }
     }
@@ -309,7 +320,7 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
     for (int j = 0; j < KW; ++j)
 #pragma unroll
       for (int ul = 0; ul < SWEEP_UT; ++ul)
-        av[j][ul] = (j < nk && ul < nu) ? __ldg(xu + (size_t)((u0 + ul) * a.Rw + wv_slot[j]) * n1p) : 0.f;
+        av[j][ul] = (valid && j < nk && ul < nu) ? __ldg(xu + ((u0 + ul) * xusd + wv_off[j])) : 0.f;
 
     if (!epi_wait(sm, a, t)) return;
     const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N;
@@ -332,8 +343,8 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
                   r = fmaf(s[h * SWEEP_VT + i], au[j][i], r);
                   cv[j][i] = fmaf(s[h * SWEEP_VT + i], av[j][ul], cv[j][i]);
                 }
-                if (j < nk) {
-                  float* dst = ou + (size_t)((u0 + ul) * a.Ro + o_slot[j]) * n1p;
+                if (valid && j < nk) {
+                  float* dst = ou + ((u0 + ul) * ousd + ou_off[j]);
                   if (vb == 0) *dst = r;     // first column block initialises the output
                   else atomicAdd(dst, r);    // later blocks accumulate (same thread, same address: ordered)
                 }
@@ -350,7 +361,7 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
       for (int j = 0; j < KW; ++j)
 #pragma unroll
         for (int i = 0; i < SWEEP_VT; ++i)
-          if (j < nk && i < nv) ov[(size_t)((v0 + i) * a.Ro + o_slot[j]) * n1p] = cv[j][i];
+          if (valid && j < nk && i < nv) ov[(v0 + i) * ovsd + ov_off[j]] = cv[j][i];
     }
     if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
@@ -441,6 +452,7 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
     e.wg = (warp - 2) >> 2;
     e.lane = lane;
     e.p = sc.m0 + q * 32 + lane;
+    e.valid = e.p < a.n_valid;
     e.tbase = sm.tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     if (MODE == SWEEP_MAXAVG) epilogue_maxavg<false>(sm, a, sc, e);
     else if (MODE == SWEEP_MAXARGAVG) epilogue_maxavg<true>(sm, a, sc, e);

@@ -155,3 +155,58 @@ class FusedSelfCompressionFunction(Function):
             ctx.state.pending = (a_u, a_v, gc_u, gc_v)
             torch.autograd.Variable._execution_engine.queue_callback(_guard_pending(ctx.state))
         return None, None, ga_u, ga_v, None
+
+
+# --------------------------------------------------------------------------------------------------
+# Channels-first pair for the call site: same fused backward, and every per-pixel tensor already has the
+# (B, K, D, H1, W1) layout of the Conv3d attention modules, so the call site's permute copies disappear.
+class SeparationMaxAvgCF(Function):
+    @staticmethod
+    def forward(ctx, img1_features_l0, img2_features_lk, state, with_argmax):
+        assert img1_features_l0.is_contiguous() and img2_features_lk.is_contiguous()
+        with torch.cuda.device_of(img1_features_l0):
+            sep_v, sep_u, am_u, am_v = MemorySaver.max_argmax_avg_forward_cf(img1_features_l0, img2_features_lk,
+                                                                             with_argmax)
+        if with_argmax:
+            ctx.save_for_backward(img1_features_l0, img2_features_lk, am_u, am_v)
+        ctx.state = state
+        ctx.with_argmax = with_argmax
+        return sep_v, sep_u
+
+    @staticmethod
+    def backward(ctx, grad_sep_v, grad_sep_u):
+        if not ctx.with_argmax:
+            raise NotImplementedError("max avg backward pass is not implemented: use max argmax avg")
+        f1, f2, am_u, am_v = ctx.saved_tensors
+        pending, ctx.state.pending = ctx.state.pending, None
+        if pending is None:
+            raise RuntimeError("channels-first separation backward needs the compression node's backward first "
+                               "(use AlternateCorrBlockSepflow(..., channels_first=False) for max/avg alone)")
+        a_u, a_v, gc_u, gc_v = pending
+        with torch.cuda.device_of(grad_sep_v):
+            g1, g2 = MemorySaver.separation_feature_backward_cf(f1, f2, am_u, am_v, grad_sep_v.contiguous(),
+                                                                grad_sep_u.contiguous(), a_u, a_v, gc_u, gc_v)
+        return g1, g2, None, None
+
+
+class SeparationCompressionCF(Function):
+    @staticmethod
+    def forward(ctx, img1_features_l0, img2_features_lk, a_u, a_v, state):
+        assert img1_features_l0.is_contiguous() and img2_features_lk.is_contiguous()
+        assert a_u.is_contiguous() and a_v.is_contiguous()
+        with torch.cuda.device_of(img1_features_l0):
+            c_u, c_v = MemorySaver.compression_forward_cf(img1_features_l0, img2_features_lk, a_u, a_v)
+        ctx.save_for_backward(img1_features_l0, img2_features_lk, a_u, a_v)
+        ctx.state = state
+        return c_u, c_v
+
+    @staticmethod
+    def backward(ctx, grad_c_u, grad_c_v):
+        f1, f2, a_u, a_v = ctx.saved_tensors
+        gc_u, gc_v = grad_c_u.contiguous(), grad_c_v.contiguous()
+        with torch.cuda.device_of(gc_u):
+            ga_u, ga_v = MemorySaver.compression_attention_backward_cf(f1, f2, gc_u, gc_v)
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            ctx.state.pending = (a_u, a_v, gc_u, gc_v)
+            torch.autograd.Variable._execution_engine.queue_callback(_guard_pending(ctx.state))
+        return None, None, ga_u, ga_v, None

@@ -59,6 +59,10 @@ def _workspace(nbytes: int, device: torch.device, stream: int) -> torch.Tensor:
     return ws
 
 
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else None)
+
+
 def _call(name: str, op: int, shape: _lib.SfbShape, device: torch.device, tensors) -> None:
     lib = _lib.load()
     with torch.cuda.device(device):
@@ -68,7 +72,7 @@ def _call(name: str, op: int, shape: _lib.SfbShape, device: torch.device, tensor
             # run the entry point anyway so that the library reports the precise reason
             nbytes = 256
         ws = _workspace(nbytes, device, stream)
-        rc = getattr(lib, name)(*[ctypes.c_void_p(t.data_ptr()) for t in tensors], ctypes.byref(shape),
+        rc = getattr(lib, name)(*[_ptr(t) for t in tensors], ctypes.byref(shape),
                                 ctypes.c_void_p(ws.data_ptr()), ctypes.c_size_t(ws.numel()),
                                 ctypes.c_void_p(stream))
         if rc != _lib.SFB_OK:
@@ -223,6 +227,76 @@ def separation_feature_backward(img1_features_l0, img2_features_lk, argmax_outpu
     _call("sfb_separation_feature_backward", _lib.OP_SEPARATION_BACKWARD, s, dev,
           (F1, F2, argmax_output_u, argmax_output_v, grad_MaxAvg_u, grad_MaxAvg_v, attention_weights_u,
            attention_weights_v, grad_compressed_output_u, grad_compressed_output_v, gF1, gF2))
+    return [gF1, gF2]
+
+
+# ------------------------------------------------------------------------------------------------------
+# Channels-first variants (no counterpart in the reference's module): the tensors have the layout the
+# call site feeds to / gets from its Conv3d modules, (B, K, D, H1, W1), so it needs no permute copies.
+def max_argmax_avg_forward_cf(img1_features_l0, img2_features_lk, with_argmax=True) -> List[torch.Tensor]:
+    """[sep_v (B,2,H2,H1,W1), sep_u (B,2,W2,H1,W1), AM_u (B,H2,H1,W1), AM_v (B,W2,H1,W1)]: channel 0 = max,
+    1 = mean; sep_v holds the per-u channels (the reference's maxavg_u permuted, core/corr.py:428-429)."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    sep_v = torch.empty(s.B, 2, s.H2, s.H1, s.W1, dtype=torch.float32, device=dev)
+    sep_u = torch.empty(s.B, 2, s.W2, s.H1, s.W1, dtype=torch.float32, device=dev)
+    am_u = torch.empty(s.B, s.H2, s.H1, s.W1, dtype=torch.int32, device=dev) if with_argmax else None
+    am_v = torch.empty(s.B, s.W2, s.H1, s.W1, dtype=torch.int32, device=dev) if with_argmax else None
+    _call("sfb_max_argmax_avg_forward_cf", _lib.OP_MAX_AVG_FORWARD_CF, s, dev, (F1, F2, sep_v, sep_u, am_u, am_v))
+    return [sep_v, sep_u, am_u, am_v]
+
+
+def _check_attention_cf(s, a_u, a_v, dev, names=("attention_weights_u", "attention_weights_v")):
+    _check(a_u, names[0], torch.float32, 5)
+    s.Kc = a_u.shape[1]
+    _check_like(a_u, names[0], (s.B, s.Kc, s.W2, s.H1, s.W1), torch.float32, dev)
+    _check_like(a_v, names[1], (s.B, s.Kc, s.H2, s.H1, s.W1), torch.float32, dev)
+    if s.Kc < 1:
+        raise RuntimeError("attention weights need at least one channel")
+
+
+def compression_forward_cf(img1_features_l0, img2_features_lk, a_u, a_v) -> List[torch.Tensor]:
+    """a_u (B,Kc,W2,H1,W1), a_v (B,Kc,H2,H1,W1) -> [c_u (B,Kc,H2,H1,W1), c_v (B,Kc,W2,H1,W1)]."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_attention_cf(s, a_u, a_v, dev)
+    c_u = torch.empty(s.B, s.Kc, s.H2, s.H1, s.W1, dtype=torch.float32, device=dev)
+    c_v = torch.empty(s.B, s.Kc, s.W2, s.H1, s.W1, dtype=torch.float32, device=dev)
+    _call("sfb_compression_forward_cf", _lib.OP_COMPRESSION_CF, s, dev, (F1, F2, a_u, a_v, c_u, c_v))
+    return [c_u, c_v]
+
+
+def compression_attention_backward_cf(img1_features_l0, img2_features_lk, gc_u, gc_v) -> List[torch.Tensor]:
+    """gc_u (B,Kc,H2,H1,W1), gc_v (B,Kc,W2,H1,W1) -> [ga_u (B,Kc,W2,H1,W1), ga_v (B,Kc,H2,H1,W1)]."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_attention_cf(s, gc_v, gc_u, dev, ("grad_compressed_output_v", "grad_compressed_output_u"))
+    ga_u = torch.empty(s.B, s.Kc, s.W2, s.H1, s.W1, dtype=torch.float32, device=dev)
+    ga_v = torch.empty(s.B, s.Kc, s.H2, s.H1, s.W1, dtype=torch.float32, device=dev)
+    _call("sfb_compression_attention_backward_cf", _lib.OP_COMPRESSION_CF, s, dev, (F1, F2, gc_u, gc_v, ga_u, ga_v))
+    return [ga_u, ga_v]
+
+
+def separation_feature_backward_cf(img1_features_l0, img2_features_lk, am_u, am_v, g_sep_v, g_sep_u, a_u, a_v,
+                                   gc_u, gc_v) -> List[torch.Tensor]:
+    """[gF1, gF2] summed over the max/avg and the compression node, all per-pixel tensors channels-first."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_attention_cf(s, a_u, a_v, dev)
+    _check_like(am_u, "argmax_u", (s.B, s.H2, s.H1, s.W1), torch.int32, dev)
+    _check_like(am_v, "argmax_v", (s.B, s.W2, s.H1, s.W1), torch.int32, dev)
+    _check_like(g_sep_v, "grad_sep_v", (s.B, 2, s.H2, s.H1, s.W1), torch.float32, dev)
+    _check_like(g_sep_u, "grad_sep_u", (s.B, 2, s.W2, s.H1, s.W1), torch.float32, dev)
+    _check_like(gc_u, "grad_c_u", (s.B, s.Kc, s.H2, s.H1, s.W1), torch.float32, dev)
+    _check_like(gc_v, "grad_c_v", (s.B, s.Kc, s.W2, s.H1, s.W1), torch.float32, dev)
+    gF1 = torch.empty_like(F1)
+    gF2 = torch.empty_like(F2)
+    _call("sfb_separation_feature_backward_cf", _lib.OP_SEPARATION_FEATURE_BACKWARD_CF, s, dev,
+          (F1, F2, am_u, am_v, g_sep_v, g_sep_u, a_u, a_v, gc_u, gc_v, gF1, gF2))
     return [gF1, gF2]
 
 

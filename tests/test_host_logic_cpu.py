@@ -22,8 +22,8 @@ def oracle_backend(monkeypatch):
     monkeypatch.setattr(functions, "MemorySaver", orc)
 
 
-@pytest.mark.parametrize("fuse_backward", [True, False])
-def test_block_matches_reference_dense_path(golden_dir, oracle_backend, fuse_backward):
+@pytest.mark.parametrize("fuse_backward,channels_first", [(True, True), (True, False), (False, False)])
+def test_block_matches_reference_dense_path(golden_dir, oracle_backend, fuse_backward, channels_first):
     g = np.load(os.path.join(golden_dir, "block_dense_b2_c16_9x11_k2.npz"))
     f1 = _t(g["f1"]).requires_grad_(True)
     f2 = _t(g["f2"]).requires_grad_(True)
@@ -34,7 +34,8 @@ def test_block_matches_reference_dense_path(golden_dir, oracle_backend, fuse_bac
             conv.weight.copy_(_t(g[f"w{i}"]))
             conv.bias.copy_(_t(g[f"b{i}"]))
         convs.append(conv)
-    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True, fuse_backward=fuse_backward)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True, fuse_backward=fuse_backward,
+                                        channels_first=channels_first)
     sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(convs))
     assert (sep_u - _t(g["sep_u"])).abs().max().item() < 1e-11
     assert (sep_v - _t(g["sep_v"])).abs().max().item() < 1e-11
@@ -82,12 +83,14 @@ def test_fused_backward_without_feature_gradients(oracle_backend):
     f2 = torch.randn(1, 8, 5, 6, dtype=torch.float64)
     convs = [torch.nn.Conv3d(2, 2, 3, padding=1).double() for _ in range(2)]
     outs = []
-    for fuse in (True, False):
+    for fuse, cf in ((True, True), (True, False), (False, False)):
         for c in convs:
             c.zero_grad()
-        blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=1, support_backward=True, fuse_backward=fuse)
+        blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=1, support_backward=True, fuse_backward=fuse,
+                                            channels_first=cf)
         su, sv = blk(None, sep=True, attention_weights=tuple(convs))
         (su.sum() + (sv * sv).sum()).backward()
         outs.append([c.weight.grad.clone() for c in convs])
-    for a, b in zip(*outs):
-        assert torch.allclose(a, b, atol=1e-12)
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert torch.allclose(a, b, atol=1e-12)

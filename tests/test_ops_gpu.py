@@ -162,6 +162,42 @@ def test_separation_backward_is_the_sum_of_both_backward_ops(shape, cuda_device)
     assert relerr(out[2], r_c[2]) < TOL and relerr(out[3], r_c[3]) < TOL
 
 
+@pytest.mark.parametrize("shape", SHAPES)
+def test_channels_first_ops(shape, cuda_device):
+    """The (B,K,D,H1,W1)-layout entry points against the oracle's channels-first definitions (= the
+    reference-layout results permuted the way core/corr.py:428-429,445-446 permutes them)."""
+    B, H1, W1, H2, W2, C, Kc = shape
+    F1, F2, A_u, A_v, g = make_inputs(shape, 9)
+    a_u = A_u.permute(0, 3, 4, 1, 2).contiguous()
+    a_v = A_v.permute(0, 3, 4, 1, 2).contiguous()
+    dev = cuda_device
+    sep_v, sep_u, am_u, am_v = ops.max_argmax_avg_forward_cf(F1.to(dev), F2.to(dev))
+    r_sep_v, r_sep_u, r_am_u, r_am_v = orc.max_argmax_avg_forward_cf(F1.double(), F2.double())
+    assert sep_v.shape == r_sep_v.shape and sep_u.shape == r_sep_u.shape and am_u.shape == r_am_u.shape
+    assert relerr(sep_v, r_sep_v) < TOL and relerr(sep_u, r_sep_u) < TOL
+    gap_u, gap_v = orc.top2_margins(F1, F2)   # (B,H1,W1,H2) and (B,H1,W1,W2)
+    assert ((am_u.cpu() == r_am_u) | (gap_u.permute(0, 3, 1, 2) <= MARGIN)).all()
+    assert ((am_v.cpu() == r_am_v) | (gap_v.permute(0, 3, 1, 2) <= MARGIN)).all()
+    s2_v, s2_u, none_u, none_v = ops.max_argmax_avg_forward_cf(F1.to(dev), F2.to(dev), with_argmax=False)
+    assert none_u is None and torch.equal(s2_v, sep_v) and torch.equal(s2_u, sep_u)
+    c_u, c_v = ops.compression_forward_cf(F1.to(dev), F2.to(dev), a_u.to(dev), a_v.to(dev))
+    r_c_u, r_c_v = orc.compression_forward_cf(F1.double(), F2.double(), a_u.double(), a_v.double())
+    assert relerr(c_u, r_c_u) < TOL and relerr(c_v, r_c_v) < TOL
+    gc_u = torch.randn(r_c_u.shape, generator=g)
+    gc_v = torch.randn(r_c_v.shape, generator=g)
+    ga_u, ga_v = ops.compression_attention_backward_cf(F1.to(dev), F2.to(dev), gc_u.to(dev), gc_v.to(dev))
+    r_ga_u, r_ga_v = orc.compression_attention_backward_cf(F1.double(), F2.double(), gc_u.double(), gc_v.double())
+    assert relerr(ga_u, r_ga_u) < TOL and relerr(ga_v, r_ga_v) < TOL
+    g_sep_v = torch.randn(r_sep_v.shape, generator=g)
+    g_sep_u = torch.randn(r_sep_u.shape, generator=g)
+    gF1, gF2 = ops.separation_feature_backward_cf(*[t.to(dev) for t in (F1, F2, r_am_u, r_am_v, g_sep_v, g_sep_u,
+                                                                         a_u, a_v, gc_u, gc_v)])
+    r1, r2 = orc.separation_feature_backward_cf(F1.double(), F2.double(), r_am_u, r_am_v, g_sep_v.double(),
+                                                g_sep_u.double(), a_u.double(), a_v.double(), gc_u.double(),
+                                                gc_v.double())
+    assert relerr(gF1, r1) < TOL and relerr(gF2, r2) < TOL
+
+
 def test_backward_is_deterministic(cuda_device):
     """Gradients accumulate in TMEM, not with atomics: two runs are bit-identical."""
     shape = (2, 24, 40, 24, 40, 128, 2)
@@ -198,7 +234,8 @@ def test_golden_op_vectors(golden_dir, cuda_device):
         assert relerr(C_v, torch.from_numpy(gold[f"l{level}_C_v"]).permute(0, 3, 4, 1, 2)) < TOL
 
 
-def test_block_against_reference_dense_vectors(golden_dir, cuda_device):
+@pytest.mark.parametrize("fuse_backward,channels_first", [(True, True), (True, False), (False, False)])
+def test_block_against_reference_dense_vectors(golden_dir, cuda_device, fuse_backward, channels_first):
     """The whole call site (4 pyramid levels, Conv3d attention, autograd) on the GPU against the
     vectors of the reference's dense CorrBlock.  Gradients flow through argmax choices; the seeded
     case has no near-ties at the MARGIN level, so the same tolerance applies."""
@@ -212,7 +249,8 @@ def test_block_against_reference_dense_vectors(golden_dir, cuda_device):
             conv.weight.copy_(torch.from_numpy(gold[f"w{i}"]).float())
             conv.bias.copy_(torch.from_numpy(gold[f"b{i}"]).float())
         convs.append(conv)
-    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True, fuse_backward=fuse_backward,
+                                        channels_first=channels_first)
     sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(convs))
     assert relerr(sep_u, torch.from_numpy(gold["sep_u"])) < TOL
     assert relerr(sep_v, torch.from_numpy(gold["sep_v"])) < TOL
