@@ -60,7 +60,9 @@ enum {
   SFB_OP_SEPARATION_BACKWARD = 5,
   SFB_OP_MAX_AVG_FORWARD_CF = 6,
   SFB_OP_COMPRESSION_CF = 7,               /* compression forward and attention backward, channels-first */
-  SFB_OP_SEPARATION_FEATURE_BACKWARD_CF = 8
+  SFB_OP_SEPARATION_FEATURE_BACKWARD_CF = 8,
+  SFB_OP_SEPARATION_LEVEL_FORWARD = 9,
+  SFB_OP_SEPARATION_LEVEL_BACKWARD = 10
 };
 
 /* Scratch bytes an op needs for `shape` (0 if the shape is invalid). */
@@ -152,6 +154,44 @@ int sfb_separation_feature_backward_cf(const float* F1, const float* F2, const i
                                        const float* gC_u, const float* gC_v, float* gF1, float* gF2,
                                        const sfb_shape* shape, void* workspace, size_t workspace_bytes,
                                        void* stream);
+
+/* Attention weights of the call site (core/corr.py:437-442 with the modules of core/sepflow.py:59-60):
+ *   A = softmax over the displacement axis of Conv3d(2 -> Kc, kernel 3, padding 1)(X)
+ * X (B,2,D,H1,W1) with `x_batch_stride` elements between samples (so X may be the first two channels of a
+ * (B,K,D,H1,W1) tensor), weight (Kc,2,3,3,3), bias (Kc), A (B,Kc,D,H1,W1).  FP32 arithmetic.  1 <= Kc <= 64. */
+int sfb_attention_forward(const float* X, int64_t x_batch_stride, const float* weight, const float* bias, float* A,
+                          int32_t B, int32_t Kc, int32_t D, int32_t H1, int32_t W1, void* stream);
+/* Its backward.  gA (B,Kc,D,H1,W1) holds dLoss/dA on entry and is overwritten with the logit gradients;
+ * gX (B,2,D,H1,W1) = add + dLoss/dX, where `add` (shape of X, `add_batch_stride` elements between samples) may
+ * be NULL; gweight (Kc,2,3,3,3), gbias (Kc).  Sums run in a fixed order (bit-reproducible).  `workspace` holds
+ * per-block partial sums, sfb_attention_backward_workspace_bytes() bytes. */
+size_t sfb_attention_backward_workspace_bytes(int32_t B, int32_t Kc, int32_t D, int32_t H1, int32_t W1);
+int sfb_attention_backward(const float* X, int64_t x_batch_stride, const float* weight, const float* A, float* gA,
+                           const float* add, int64_t add_batch_stride, float* gX, float* gweight, float* gbias,
+                           int32_t B, int32_t Kc, int32_t D, int32_t H1, int32_t W1, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* One pyramid level of the call site in one call (core/corr.py:419-457, everything between the feature
+ * permutes and the upsampling): max/avg sweep, attention weights, compression sweep, written straight into
+ * the concatenated tensors
+ *   SEP_u (B, 2+Kc, W2, H1, W1): channels 0,1 = max_u S, mean_u S;  2.. = C_v
+ *   SEP_v (B, 2+Kc, H2, H1, W1): channels 0,1 = max_v S, mean_v S;  2.. = C_u
+ * attention1 = (weight_u, bias_u) acts on SEP_u[:, :2] and gives A_u (B,Kc,W2,H1,W1); attention2 = (weight_v,
+ * bias_v) on SEP_v[:, :2] gives A_v (B,Kc,H2,H1,W1).  A_u, A_v and (if not NULL) AM_u (B,H2,H1,W1), AM_v
+ * (B,W2,H1,W1) are outputs the backward needs. */
+int sfb_separation_level_forward(const float* F1, const float* F2, const float* weight_u, const float* bias_u,
+                                 const float* weight_v, const float* bias_v, float* SEP_u, float* SEP_v,
+                                 int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+/* Backward of the level: from gSEP_u, gSEP_v (shapes of SEP_u, SEP_v) to gF1, gF2 and the gradients of the four
+ * attention parameters.  Three contractions: the attention gradients (one sweep), then gF1 and gF2 from the
+ * summed dLoss/dS of the max/avg and compression parts (one GEMM pair). */
+int sfb_separation_level_backward(const float* F1, const float* F2, const float* weight_u, const float* weight_v,
+                                  const float* SEP_u, const float* SEP_v, const int32_t* AM_u, const int32_t* AM_v,
+                                  const float* A_u, const float* A_v, const float* gSEP_u, const float* gSEP_v,
+                                  float* gF1, float* gF2, float* gweight_u, float* gbias_u, float* gweight_v,
+                                  float* gbias_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                                  void* stream);
 
 /* Test aid with no counterpart in the reference ops: writes the dense volume S (B,H1,W1,H2,W2) of a
  * SMALL problem through the same tensor-core pipeline (the reference builds it with torch.matmul,

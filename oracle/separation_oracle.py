@@ -242,6 +242,47 @@ def separation_feature_backward_cf(F1, F2, am_u, am_v, g_sep_v, g_sep_u, a_u, a_
                                        _from_cf(gc_u), _from_cf(gc_v))
 
 
+# Attention weights of the call site and one whole pyramid level, exactly as the reference chains them
+# (core/corr.py:425-457 with the Conv3d(2, Kc, 3, padding=1) modules of core/sepflow.py:59-60).
+def attention_forward(x, weight, bias):
+    """a = softmax over the displacement axis of Conv3d(x) (core/corr.py:437-442); x (B,2,D,H1,W1)."""
+    return torch.nn.functional.conv3d(x, weight, bias, padding=1).softmax(dim=2)
+
+
+def attention_backward(x, weight, a, grad_a, add=None):
+    """[gx (+ add), gweight, gbias] of attention_forward, given its output ``a``: the softmax backward in
+    closed form, the convolution's by autograd."""
+    gl = a * (grad_a - (grad_a * a).sum(dim=2, keepdim=True))
+    with torch.enable_grad():   # callers may sit inside an autograd backward, where grad mode is off
+        x = x.detach().clone().requires_grad_(True)
+        weight = weight.detach().clone().requires_grad_(True)
+        bias = torch.zeros(weight.shape[0], dtype=weight.dtype, device=weight.device, requires_grad=True)
+        torch.nn.functional.conv3d(x, weight, bias, padding=1).backward(gl)
+    return [x.grad if add is None else x.grad + add, weight.grad, bias.grad]
+
+
+def separation_level_forward(F1, F2, weight_u, bias_u, weight_v, bias_v, with_argmax=True):
+    """[sep_u (B,2+Kc,W2,H1,W1), sep_v (B,2+Kc,H2,H1,W1), am_u, am_v, a_u, a_v] (core/corr.py:425-457)."""
+    ma_v2, ma_u2, am_u, am_v = max_argmax_avg_forward_cf(F1, F2, with_argmax)   # sep_v (per u), sep_u (per v)
+    a_u = attention_forward(ma_u2, weight_u, bias_u)
+    a_v = attention_forward(ma_v2, weight_v, bias_v)
+    c_u, c_v = compression_forward_cf(F1, F2, a_u, a_v)
+    return [torch.cat((ma_u2, c_v), dim=1), torch.cat((ma_v2, c_u), dim=1), am_u, am_v, a_u, a_v]
+
+
+def separation_level_backward(F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u, g_sep_v):
+    """[gF1, gF2, gweight_u, gbias_u, gweight_v, gbias_v]: the chain rule through the three ops and the two
+    attention modules, with the forward's argmax and attention weights given."""
+    gc_v = g_sep_u[:, 2:].contiguous()
+    gc_u = g_sep_v[:, 2:].contiguous()
+    ga_u, ga_v = compression_attention_backward_cf(F1, F2, gc_u, gc_v)
+    gm_u, gw_u, gb_u = attention_backward(sep_u[:, :2], weight_u, a_u, ga_u, g_sep_u[:, :2])
+    gm_v, gw_v, gb_v = attention_backward(sep_v[:, :2], weight_v, a_v, ga_v, g_sep_v[:, :2])
+    gm_u, gm_v = gm_u.contiguous(), gm_v.contiguous()
+    gF1, gF2 = separation_feature_backward_cf(F1, F2, am_u, am_v, gm_v, gm_u, a_u, a_v, gc_u, gc_v)
+    return [gF1, gF2, gw_u, gb_u, gw_v, gb_v]
+
+
 def top2_margins(F1: torch.Tensor, F2: torch.Tensor):
     """Gap between the largest and second-largest entry of S along v (per (p,u)) and
     along u (per (p,v)), computed in float64.  An argmax is required to be bit-exact only

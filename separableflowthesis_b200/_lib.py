@@ -27,6 +27,8 @@ OP_SEPARATION_BACKWARD = 5
 OP_MAX_AVG_FORWARD_CF = 6
 OP_COMPRESSION_CF = 7
 OP_SEPARATION_FEATURE_BACKWARD_CF = 8
+OP_SEPARATION_LEVEL_FORWARD = 9
+OP_SEPARATION_LEVEL_BACKWARD = 10
 
 # Every symbol include/sepflow_b200.h declares.
 EXPORTED_SYMBOLS = (
@@ -37,7 +39,8 @@ EXPORTED_SYMBOLS = (
     "sfb_max_avg_forward_static", "sfb_static_scratch_bytes", "sfb_separation_backward",
     "sfb_compression_attention_backward", "sfb_separation_feature_backward",
     "sfb_max_argmax_avg_forward_cf", "sfb_compression_forward_cf", "sfb_compression_attention_backward_cf",
-    "sfb_separation_feature_backward_cf",
+    "sfb_separation_feature_backward_cf", "sfb_attention_forward", "sfb_attention_backward_workspace_bytes",
+    "sfb_attention_backward", "sfb_separation_level_forward", "sfb_separation_level_backward",
 )
 
 
@@ -68,10 +71,18 @@ def load() -> ctypes.CDLL:
                        ("sfb_separation_backward", 14), ("sfb_compression_attention_backward", 6),
                        ("sfb_separation_feature_backward", 12), ("sfb_max_argmax_avg_forward_cf", 6),
                        ("sfb_compression_forward_cf", 6), ("sfb_compression_attention_backward_cf", 6),
-                       ("sfb_separation_feature_backward_cf", 12)):
+                       ("sfb_separation_feature_backward_cf", 12), ("sfb_separation_level_forward", 12),
+                       ("sfb_separation_level_backward", 18)):
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [P] * nptr + tail
+    I32, I64 = ctypes.c_int32, ctypes.c_int64
+    lib.sfb_attention_forward.restype = ctypes.c_int
+    lib.sfb_attention_forward.argtypes = [P, I64, P, P, P, I32, I32, I32, I32, I32, P]
+    lib.sfb_attention_backward_workspace_bytes.restype = SZ
+    lib.sfb_attention_backward_workspace_bytes.argtypes = [I32] * 5
+    lib.sfb_attention_backward.restype = ctypes.c_int
+    lib.sfb_attention_backward.argtypes = [P, I64, P, P, P, P, I64, P, P, P, I32, I32, I32, I32, I32, P, SZ, P]
     lib.sfb_max_avg_forward_static.restype = ctypes.c_int
     lib.sfb_max_avg_forward_static.argtypes = [P, P, P, P, SH, P]
     lib.sfb_static_scratch_bytes.restype = SZ

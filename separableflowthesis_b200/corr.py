@@ -7,7 +7,12 @@ Differences from the reference that do not change results: the scaled channels-l
 ``fuse_backward`` (default) the feature gradients of the max/avg node and the compression node of a level,
 which autograd would add, come out of one pair of gradient GEMMs instead of two; with ``channels_first``
 (default, used whenever attention weights are given) the ops read and write the (B,K,D,H1,W1) tensors of the
-Conv3d attention directly, which removes the permute copies of core/corr.py:428-429,445-446,451-452.
+Conv3d attention directly, which removes the permute copies of core/corr.py:428-429,445-446,451-452; with
+``fuse_attention`` (default) a level whose attention modules are the Conv3d(2, Kc, 3, padding=1) of
+core/sepflow.py:59-60 is one autograd node whose forward and backward are one library call each (the
+Conv3d + softmax run in the library's stencil kernels and the concatenations of core/corr.py:454-457 are written
+in place); a level that already has the level-0 displacement range skips the trilinear resampling, which is
+the identity there.
 """
 from __future__ import annotations
 
@@ -18,7 +23,14 @@ import torch.nn.functional as F
 
 from .functions import (ComputeMaxArgmaxAvgFunction, ComputeMaxAvgFunction, ComputeSelfCompressionFunction,
                         FusedMaxArgmaxAvgFunction, FusedSelfCompressionFunction, SeparationCompressionCF,
-                        SeparationMaxAvgCF, SeparationState)
+                        SeparationLevelFunction, SeparationMaxAvgCF, SeparationState)
+
+
+def _is_standard_attention(m) -> bool:
+    """True for the module the reference builds: Conv3d(2, Kc, 3, padding=1) (core/sepflow.py:59-60)."""
+    return (isinstance(m, torch.nn.Conv3d) and m.in_channels == 2 and tuple(m.kernel_size) == (3, 3, 3)
+            and tuple(m.padding) == (1, 1, 1) and tuple(m.stride) == (1, 1, 1) and tuple(m.dilation) == (1, 1, 1)
+            and m.groups == 1 and m.padding_mode == "zeros" and m.bias is not None and m.out_channels <= 64)
 
 
 class AlternateCorrBlockSepflow:
@@ -27,13 +39,14 @@ class AlternateCorrBlockSepflow:
     (core/corr.py:356-358)."""
 
     def __init__(self, fmap1, fmap2, guid, num_levels=4, radius=4, support_backward=False, fuse_backward=True,
-                 channels_first=True):
+                 channels_first=True, fuse_attention=True):
         if guid is not None:
             raise Exception("Cannot use NLF while not storing the 4d correlation volume")
         self.max_avg_function = ComputeMaxArgmaxAvgFunction if support_backward else ComputeMaxAvgFunction
         self.support_backward = support_backward
         self.fuse_backward = fuse_backward
         self.channels_first = channels_first
+        self.fuse_attention = fuse_attention
         self.num_levels = num_levels
         self.radius = radius
         self.fmap1_l0 = fmap1
@@ -45,6 +58,12 @@ class AlternateCorrBlockSepflow:
     def separate_level(self, F1, level, attention_weights):
         """One pyramid level: returns (sep_u (B,K,W2,H1,W1), sep_v (B,K,H2,H1,W1)) before upsampling."""
         F2 = self.pyramid[level].permute(0, 2, 3, 1).contiguous()
+        if (self.channels_first and self.fuse_backward and self.fuse_attention and attention_weights is not None
+                and all(_is_standard_attention(m) for m in attention_weights)
+                and attention_weights[0].out_channels == attention_weights[1].out_channels):
+            attention1, attention2 = attention_weights
+            return SeparationLevelFunction.apply(F1, F2, attention1.weight, attention1.bias, attention2.weight,
+                                                 attention2.bias, self.support_backward)
         if self.channels_first and self.fuse_backward and attention_weights is not None:
             state = SeparationState()
             sep_v, sep_u = SeparationMaxAvgCF.apply(F1, F2, state, self.support_backward)
@@ -82,8 +101,15 @@ class AlternateCorrBlockSepflow:
         sep_u_lvls, sep_v_lvls = [], []
         for level in range(self.num_levels):
             sep_u, sep_v = self.separate_level(F1, level, attention_weights)
-            sep_u_lvls.append(F.interpolate(sep_u, [w1, h1, w1], mode="trilinear", align_corners=True))
-            sep_v_lvls.append(F.interpolate(sep_v, [h1, h1, w1], mode="trilinear", align_corners=True))
+            # align_corners resampling to the size a tensor already has copies it: skip
+            if sep_u.shape[2] != w1:
+                sep_u = F.interpolate(sep_u, [w1, h1, w1], mode="trilinear", align_corners=True)
+            if sep_v.shape[2] != h1:
+                sep_v = F.interpolate(sep_v, [h1, h1, w1], mode="trilinear", align_corners=True)
+            sep_u_lvls.append(sep_u)
+            sep_v_lvls.append(sep_v)
+        if self.num_levels == 1:
+            return sep_u_lvls[0], sep_v_lvls[0]
         return torch.cat(sep_u_lvls, dim=1), torch.cat(sep_v_lvls, dim=1)
 
     def __call__(self, coords, sep=False, attention_weights=None):

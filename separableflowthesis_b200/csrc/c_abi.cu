@@ -70,13 +70,15 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // ---- optional per-kernel timing (off by default): CUDA events around each launch on its own stream ----
 enum KernelId : int {
   KID_PREPARE = 0, KID_PACK, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
-  KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_GRAD_FUSED_IMG1, KID_GRAD_FUSED_IMG2, KID_COUNT
+  KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_GRAD_FUSED_IMG1, KID_GRAD_FUSED_IMG2, KID_ATTENTION_FWD,
+  KID_ATTENTION_BWD, KID_COUNT
 };
 const char* const kKernelNames[KID_COUNT] = {
     "prepare(round_copy+f2_means)", "pack_kernel/unpack_kernel", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
     "grad_gemm_kernel<maxavg,image1-major>", "grad_gemm_kernel<maxavg,image2-major>",
     "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>",
-    "grad_gemm_kernel<fused,image1-major>", "grad_gemm_kernel<fused,image2-major>"};
+    "grad_gemm_kernel<fused,image1-major>", "grad_gemm_kernel<fused,image2-major>",
+    "attention_forward_kernel", "attention backward (logit, input, weight grads)"};
 struct TimingRec { cudaEvent_t e0, e1; int id; int launches; };
 std::mutex g_timing_mu;
 bool g_timing_on = false;
@@ -135,6 +137,11 @@ struct Workspace {
   float* ov;   // packed outputs, (B, W2, Ro, n1p)
   float* gxu;  // interleaved gradient-GEMM operands, (B, H2, n1p, Rg)
   float* gxv;  // interleaved gradient-GEMM operands, (B, W2, n1p, Rg)
+  float* ga_u;  // level backward: attention gradients (B, Kc, W2, N1) / (B, Kc, H2, N1) ...
+  float* ga_v;
+  float* gm_u;  // ... total gradients of the max/avg channels (B, 2, W2, N1) / (B, 2, H2, N1) ...
+  float* gm_v;
+  float* at_partial;  // ... and the attention backward's per-block partial sums
   int n1p;
   size_t bytes;
 };
@@ -151,22 +158,24 @@ PixView cf_view(const void* base, int slots, int D, int N1) {
 }
 
 // What an op keeps in the workspace: the mean rows of F2, Rx packed input slots, Ro packed output slots.
-struct WsPlan { bool aux; int Rx; int Ro; int Rg; };
+struct WsPlan { bool aux; int Rx; int Ro; int Rg; bool level_bwd; };
 constexpr int MAXAVG_SLOTS = 3;  // max, mean, argmax bits
 int chunk_channels(int Kc) { return Kc < KC_MAX_PER_SWEEP ? Kc : KC_MAX_PER_SWEEP; }
 int grad_slots(int kc) { return 2 * kc <= 4 ? 4 : 8; }  // two slots per channel, rounded up to a multiple of 4
 
 WsPlan plan_for(int op, const Dims& d) {
   switch (op) {
-    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS, 0};
-    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc, 0};
-    case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, 0, 0, 4};
-    case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc))};
-    case SFB_OP_SEPARATION_BACKWARD: return {false, d.Kc, d.Kc, 4 + grad_slots(chunk_channels(d.Kc))};
-    case SFB_OP_MAX_AVG_FORWARD_CF: return {true, 0, 0, 0};
-    case SFB_OP_COMPRESSION_CF: return {false, 0, 0, 0};
-    case SFB_OP_SEPARATION_FEATURE_BACKWARD_CF: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc))};
-    default: return {false, 0, 0, 0};
+    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS, 0, false};
+    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc, 0, false};
+    case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, 0, 0, 4, false};
+    case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc)), false};
+    case SFB_OP_SEPARATION_BACKWARD: return {false, d.Kc, d.Kc, 4 + grad_slots(chunk_channels(d.Kc)), false};
+    case SFB_OP_MAX_AVG_FORWARD_CF: return {true, 0, 0, 0, false};
+    case SFB_OP_COMPRESSION_CF: return {false, 0, 0, 0, false};
+    case SFB_OP_SEPARATION_FEATURE_BACKWARD_CF: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc)), false};
+    case SFB_OP_SEPARATION_LEVEL_FORWARD: return {true, 0, 0, 0, false};
+    case SFB_OP_SEPARATION_LEVEL_BACKWARD: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc)), true};
+    default: return {false, 0, 0, 0, false};
   }
 }
 
@@ -191,6 +200,15 @@ Workspace carve(const Dims& d, void* base, const WsPlan& plan) {
   w.ov = plan.Ro ? take((size_t)d.B * d.W2 * plan.Ro * w.n1p) : nullptr;
   w.gxu = plan.Rg ? take((size_t)d.B * d.H2 * plan.Rg * w.n1p) : nullptr;
   w.gxv = plan.Rg ? take((size_t)d.B * d.W2 * plan.Rg * w.n1p) : nullptr;
+  w.ga_u = w.ga_v = w.gm_u = w.gm_v = w.at_partial = nullptr;
+  if (plan.level_bwd) {
+    const size_t n1 = (size_t)d.N1();
+    w.ga_u = take((size_t)d.B * d.Kc * d.W2 * n1);
+    w.ga_v = take((size_t)d.B * d.Kc * d.H2 * n1);
+    w.gm_u = take((size_t)d.B * 2 * d.W2 * n1);
+    w.gm_v = take((size_t)d.B * 2 * d.H2 * n1);
+    w.at_partial = take(attention_partial_floats(AttentionDims{d.B, d.Kc, d.H2 > d.W2 ? d.H2 : d.W2, d.H1, d.W1}));
+  }
   w.bytes = off;
   return w;
 }
@@ -208,7 +226,7 @@ int check_shape(const sfb_shape* s, bool need_kc, Dims* d) {
     return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image 1 has more than 2^21 pixels or image 2 more than 2^30");
   {  // element offsets inside one sample's packed array are 32-bit in the kernels
     const long long n1p = ((long long)s->H1 * s->W1 + TILE_M - 1) / TILE_M * TILE_M;
-    const long long slots = 8;
+    const long long slots = s->Kc + 2 > 8 ? s->Kc + 2 : 8;
     if (n1p * slots * (s->H2 > s->W2 ? s->H2 : s->W2) >= (1ll << 32))
       return fail(SFB_ERR_UNSUPPORTED_SHAPE, "H1*W1*max(H2,W2)*slots exceeds 2^32 elements per sample");
   }
@@ -382,15 +400,17 @@ void maxavg_slot_sources(const Dims& d, const int32_t* AM_u, const int32_t* AM_v
 }
 // Interleaved slots of the compression backward for channels k0 .. k0+kc-1, local channel j:
 // XU 2j = gC_u, 2j+1 = A_v;  XV 2j = A_u, 2j+1 = gC_v, so that G[p,u,v] = sum_slots XU[u,p,slot] * XV[v,p,slot].
+// The gradients may be channels g0.. of a tensor with gK channels (the concatenated tensors of the call site).
 void compress_slot_sources(int K, int k0, int kc, const float* A_u, const float* A_v, const float* gC_u,
-                           const float* gC_v, SlotSources* su, SlotSources* sv) {
+                           const float* gC_v, SlotSources* su, SlotSources* sv, int gK = 0, int g0 = 0) {
+  if (gK == 0) gK = K;
   memset(su, 0, sizeof(*su));
   memset(sv, 0, sizeof(*sv));
   for (int j = 0; j < kc; ++j) {
-    su->s[2 * j] = {gC_u, K, k0 + j, 0.f};
+    su->s[2 * j] = {gC_u, gK, g0 + k0 + j, 0.f};
     su->s[2 * j + 1] = {A_v, K, k0 + j, 0.f};
     sv->s[2 * j] = {A_u, K, k0 + j, 0.f};
-    sv->s[2 * j + 1] = {gC_v, K, k0 + j, 0.f};
+    sv->s[2 * j + 1] = {gC_v, gK, g0 + k0 + j, 0.f};
   }
 }
 
@@ -447,10 +467,11 @@ extern "C" {
 
 size_t sfb_workspace_bytes(int op, const sfb_shape* shape) {
   Dims d;
-  if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_SEPARATION_FEATURE_BACKWARD_CF) return 0;
+  if (op < SFB_OP_MAX_AVG_FORWARD || op > SFB_OP_SEPARATION_LEVEL_BACKWARD) return 0;
   const bool need_kc = op == SFB_OP_COMPRESSION_FORWARD || op == SFB_OP_COMPRESSION_BACKWARD ||
                        op == SFB_OP_SEPARATION_BACKWARD || op == SFB_OP_COMPRESSION_CF ||
-                       op == SFB_OP_SEPARATION_FEATURE_BACKWARD_CF;
+                       op == SFB_OP_SEPARATION_FEATURE_BACKWARD_CF || op == SFB_OP_SEPARATION_LEVEL_FORWARD ||
+                       op == SFB_OP_SEPARATION_LEVEL_BACKWARD;
   if (check_shape(shape, need_kc, &d) != SFB_OK) return 0;
   return carve(d, nullptr, plan_for(op, d)).bytes;
 }
@@ -720,6 +741,40 @@ int sfb_compression_attention_backward_cf(const float* F1, const float* F2, cons
   return run_compress_cf(F1, F2, gC_v, gC_u, gA_v, gA_u, shape, workspace, workspace_bytes, stream);
 }
 
+// Channels-first form of run_fused_feature_grads: gMA sources gM_v (B,2,H2,N1) / gM_u (B,2,W2,N1); the compression
+// gradients are channels g0.. of tensors with gK channels.
+static int run_fused_feature_grads_cf(const Dims& d, const Workspace& w, const int32_t* AM_u, const int32_t* AM_v,
+                                      const float* gM_v, const float* gM_u, const float* A_u, const float* A_v,
+                                      const float* gC_u, const float* gC_v, int gK, int g0, float* gF1, float* gF2,
+                                      cudaStream_t st) {
+  const int N1 = d.N1(), K = d.Kc;
+  {
+    const int kc = chunk_channels(K), Qc = grad_slots(kc) / 4, Q = 1 + Qc;
+    SFB_CUDA(timed(KID_PACK, 4, st, [&] {
+      SlotSources su, sv;
+      // channel 0 = max gradient, channel 1 = mean gradient (same slots as the reference layout)
+      maxavg_slot_sources(d, AM_u, AM_v, gM_v, gM_u, &su, &sv);
+      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4, Q, 0, st);
+      launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4, Q, 0, st);
+      compress_slot_sources(K, 0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, gK, g0);
+      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4 * Qc, Q, 1, st);
+      return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4 * Qc, Q, 1, st);
+    }));
+    SFB_TRY(run_grad_pair(d, w, GRAD_FUSED, 4 * Q, 0, gF1, gF2, st));
+  }
+  for (int k0 = KC_MAX_PER_SWEEP; k0 < K; k0 += KC_MAX_PER_SWEEP) {
+    const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
+    SFB_CUDA(timed(KID_PACK, 2, st, [&] {
+      SlotSources su, sv;
+      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, gK, g0);
+      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
+      return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
+    }));
+    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R4, 1, gF1, gF2, st));
+  }
+  return SFB_OK;
+}
+
 int sfb_separation_feature_backward_cf(const float* F1, const float* F2, const int32_t* AM_u, const int32_t* AM_v,
                                        const float* gSEP_v, const float* gSEP_u, const float* A_u, const float* A_v,
                                        const float* gC_u, const float* gC_v, float* gF1, float* gF2,
@@ -733,32 +788,147 @@ int sfb_separation_feature_backward_cf(const float* F1, const float* F2, const i
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_FEATURE_BACKWARD_CF, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
-  const int N1 = d.N1(), K = d.Kc;
-  {
-    const int kc = chunk_channels(K), Qc = grad_slots(kc) / 4, Q = 1 + Qc;
-    SFB_CUDA(timed(KID_PACK, 4, st, [&] {
-      SlotSources su, sv;
-      // channel 0 of gSEP = max gradient, channel 1 = mean gradient (same slots as the reference layout)
-      maxavg_slot_sources(d, AM_u, AM_v, gSEP_v, gSEP_u, &su, &sv);
-      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4, Q, 0, st);
-      launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4, Q, 0, st);
-      compress_slot_sources(K, 0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
-      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4 * Qc, Q, 1, st);
-      return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4 * Qc, Q, 1, st);
-    }));
-    SFB_TRY(run_grad_pair(d, w, GRAD_FUSED, 4 * Q, 0, gF1, gF2, st));
-  }
-  for (int k0 = KC_MAX_PER_SWEEP; k0 < K; k0 += KC_MAX_PER_SWEEP) {
-    const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
-    SFB_CUDA(timed(KID_PACK, 2, st, [&] {
-      SlotSources su, sv;
-      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
-      launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
-      return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
-    }));
-    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R4, 1, gF1, gF2, st));
-  }
+  return run_fused_feature_grads_cf(d, w, AM_u, AM_v, gSEP_v, gSEP_u, A_u, A_v, gC_u, gC_v, d.Kc, 0, gF1, gF2, st);
+}
+
+// ---- attention weights: Conv3d(2 -> Kc, 3, padding 1) + softmax over the displacement axis ----
+static int check_attention_dims(int B, int Kc, int D, int H1, int W1, AttentionDims* ad) {
+  if (B < 1 || Kc < 1 || D < 1 || H1 < 1 || W1 < 1)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "B, Kc, D, H1, W1 must be >= 1 (got %d %d %d %d %d)", B, Kc, D, H1, W1);
+  if (Kc > 64) return fail(SFB_ERR_UNSUPPORTED_SHAPE, "Kc=%d unsupported: at most 64 attention channels", Kc);
+  if ((long long)H1 * W1 > (1ll << 21)) return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image 1 has more than 2^21 pixels");
+  *ad = AttentionDims{B, Kc, D, H1, W1};
   return SFB_OK;
+}
+
+int sfb_attention_forward(const float* X, int64_t x_batch_stride, const float* weight, const float* bias, float* A,
+                          int32_t B, int32_t Kc, int32_t D, int32_t H1, int32_t W1, void* stream) {
+  AttentionDims ad;
+  SFB_TRY(check_attention_dims(B, Kc, D, H1, W1, &ad));
+  if (X == nullptr || weight == nullptr || bias == nullptr || A == nullptr)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "X, weight, bias and A must not be NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_ATTENTION_FWD, (Kc + 3) / 4, st,
+                 [&] { return launch_attention_forward(ad, X, x_batch_stride, weight, bias, A, st); }));
+  return SFB_OK;
+}
+
+size_t sfb_attention_backward_workspace_bytes(int32_t B, int32_t Kc, int32_t D, int32_t H1, int32_t W1) {
+  AttentionDims ad;
+  if (check_attention_dims(B, Kc, D, H1, W1, &ad) != SFB_OK) return 0;
+  return align_up(attention_partial_floats(ad) * sizeof(float), 256);
+}
+
+static int attention_backward_launches(int Kc) { return (Kc + 3) / 4 + 4; }
+
+int sfb_attention_backward(const float* X, int64_t x_batch_stride, const float* weight, const float* A, float* gA,
+                           const float* add, int64_t add_batch_stride, float* gX, float* gweight, float* gbias,
+                           int32_t B, int32_t Kc, int32_t D, int32_t H1, int32_t W1, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  AttentionDims ad;
+  SFB_TRY(check_attention_dims(B, Kc, D, H1, W1, &ad));
+  if (X == nullptr || weight == nullptr || A == nullptr || gA == nullptr || gX == nullptr || gweight == nullptr ||
+      gbias == nullptr)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "X, weight, A, gA, gX, gweight and gbias must not be NULL");
+  if (workspace == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "workspace is NULL");
+  const size_t need = sfb_attention_backward_workspace_bytes(B, Kc, D, H1, W1);
+  if (workspace_bytes < need)
+    return fail(SFB_ERR_WORKSPACE_TOO_SMALL, "workspace has %zu bytes, %zu needed", workspace_bytes, need);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_ATTENTION_BWD, attention_backward_launches(Kc), st, [&] {
+    return launch_attention_backward(ad, X, x_batch_stride, weight, A, gA, add, add_batch_stride, gX, gweight, gbias,
+                                     static_cast<float*>(workspace), st);
+  }));
+  return SFB_OK;
+}
+
+// ---- one pyramid level of the call site ----
+// channels c0.. of a concatenated (B, Ktot, D, N1) tensor as a pixel view
+static PixView cf_channels(const void* base, int Ktot, int c0, int D, int N1) {
+  return PixView{static_cast<float*>(const_cast<void*>(base)) + (size_t)c0 * D * N1, (long long)Ktot * D * N1,
+                 (uint32_t)N1, (uint32_t)(D * N1)};
+}
+
+int sfb_separation_level_forward(const float* F1, const float* F2, const float* weight_u, const float* bias_u,
+                                 const float* weight_v, const float* bias_v, float* SEP_u, float* SEP_v,
+                                 int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  AttentionDims ad;
+  SFB_TRY(check_attention_dims(d.B, d.Kc, d.H2, d.H1, d.W1, &ad));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(SEP_u); SFB_CHECK_PTR(SEP_v); SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v);
+  if (weight_u == nullptr || bias_u == nullptr || weight_v == nullptr || bias_v == nullptr)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "attention weights and biases must not be NULL");
+  const bool with_argmax = AM_u != nullptr || AM_v != nullptr;
+  if (with_argmax) { SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v); }
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_LEVEL_FORWARD, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2, tm_aux;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_TRY(map_aux(&tm_aux, d, w.aux));
+  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st); }));
+  const int N1 = d.N1(), K = d.Kc, Kt = 2 + d.Kc;
+  SweepArgs a;
+  memset(&a, 0, sizeof(a));
+  a.d = d;
+  a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
+  a.n_valid = N1;
+  a.pu = cf_channels(SEP_v, Kt, 0, d.H2, N1);  // per-u channels live in the tensor the call site calls sep_v
+  a.pv = cf_channels(SEP_u, Kt, 0, d.W2, N1);
+  a.pu_arg = cf_view(AM_u, 1, d.H2, N1);
+  a.pv_arg = cf_view(AM_v, 1, d.W2, N1);
+  a.status = w.status;
+  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
+  const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
+  SFB_CUDA(timed(KID_ATTENTION_FWD, 2 * ((K + 3) / 4), st, [&] {
+    launch_attention_forward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u, sb_u, weight_u, bias_u, A_u, st);
+    return launch_attention_forward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v, sb_v, weight_v, bias_v, A_v, st);
+  }));
+  // C_u (per u, weights A_u per v) -> SEP_v channels 2.., C_v -> SEP_u channels 2..
+  return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(A_v, K, d.H2, N1), cf_view(A_u, K, d.W2, N1), 0, 0, 1,
+                             cf_channels(SEP_v, Kt, 2, d.H2, N1), cf_channels(SEP_u, Kt, 2, d.W2, N1), N1, st);
+}
+
+int sfb_separation_level_backward(const float* F1, const float* F2, const float* weight_u, const float* weight_v,
+                                  const float* SEP_u, const float* SEP_v, const int32_t* AM_u, const int32_t* AM_v,
+                                  const float* A_u, const float* A_v, const float* gSEP_u, const float* gSEP_v,
+                                  float* gF1, float* gF2, float* gweight_u, float* gbias_u, float* gweight_v,
+                                  float* gbias_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                                  void* stream) {
+  Dims d;
+  SFB_TRY(check_shape(shape, true, &d));
+  AttentionDims ad;
+  SFB_TRY(check_attention_dims(d.B, d.Kc, d.H2, d.H1, d.W1, &ad));
+  SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(SEP_u); SFB_CHECK_PTR(SEP_v); SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v);
+  SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v); SFB_CHECK_PTR(gSEP_u); SFB_CHECK_PTR(gSEP_v); SFB_CHECK_PTR(gF1); SFB_CHECK_PTR(gF2);
+  if (weight_u == nullptr || weight_v == nullptr || gweight_u == nullptr || gbias_u == nullptr || gweight_v == nullptr ||
+      gbias_v == nullptr)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "attention weights and their gradient buffers must not be NULL");
+  Workspace w;
+  SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_LEVEL_BACKWARD, &w));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tm_f1, tm_f2;
+  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  const int N1 = d.N1(), K = d.Kc, Kt = 2 + d.Kc;
+  // attention gradients: gA_v(b,k,u,p) = sum_v S * gC_v(b,k,v,p), gA_u(b,k,v,p) = sum_u S * gC_u(b,k,u,p), with
+  // gC_u = gSEP_v[:, 2:] (per u) and gC_v = gSEP_u[:, 2:] (per v) in the role of the weights
+  SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_channels(gSEP_v, Kt, 2, d.H2, N1),
+                              cf_channels(gSEP_u, Kt, 2, d.W2, N1), 0, 0, 1, cf_view(w.ga_v, K, d.H2, N1),
+                              cf_view(w.ga_u, K, d.W2, N1), N1, st));
+  // through softmax and Conv3d: parameter gradients, and the total gradients of the max/avg channels
+  const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
+  SFB_CUDA(timed(KID_ATTENTION_BWD, 2 * attention_backward_launches(K), st, [&] {
+    launch_attention_backward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u, sb_u, weight_u, A_u, w.ga_u, gSEP_u, sb_u,
+                              w.gm_u, gweight_u, gbias_u, w.at_partial, st);
+    return launch_attention_backward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v, sb_v, weight_v, A_v, w.ga_v, gSEP_v,
+                                     sb_v, w.gm_v, gweight_v, gbias_v, w.at_partial, st);
+  }));
+  return run_fused_feature_grads_cf(d, w, AM_u, AM_v, w.gm_v, w.gm_u, A_u, A_v, gSEP_v, gSEP_u, Kt, 2, gF1, gF2, st);
 }
 
 int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,

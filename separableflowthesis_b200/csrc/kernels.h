@@ -124,4 +124,21 @@ cudaError_t launch_sweep(const SweepArgs& a, const CUtensorMap& tm_f1, const CUt
 cudaError_t launch_grad_gemm(const GradArgs& a, const CUtensorMap& tm_y, const CUtensorMap& tm_xu,
                              const CUtensorMap& tm_xv, cudaStream_t stream);
 
+
+// Attention weights A = softmax over d of Conv3d(2 -> Kc, 3x3x3, padding 1)(X) on channels-first tensors
+// (core/corr.py:437-442): X (B, 2, D, H1, W1) with `x_sb` elements between samples, weight (Kc, 2, 3, 3, 3),
+// bias (Kc), A (B, Kc, D, H1, W1).
+struct AttentionDims {
+  int B, Kc, D, H1, W1;
+};
+cudaError_t launch_attention_forward(const AttentionDims& d, const float* x, long long x_sb, const float* weight,
+                                     const float* bias, float* a, cudaStream_t stream);
+// Floats of scratch the backward needs for its per-block partial sums.
+size_t attention_partial_floats(const AttentionDims& d);
+// Backward: `g` holds dLoss/dA on entry and the logit gradients on return; gx (B, 2, D, H1, W1) = add + dLoss/dX
+// where `add` (same shape, `add_sb` elements between samples) may be null; gweight (Kc, 2, 3, 3, 3), gbias (Kc).
+cudaError_t launch_attention_backward(const AttentionDims& d, const float* x, long long x_sb, const float* weight,
+                                      const float* a, float* g, const float* add, long long add_sb, float* gx,
+                                      float* gweight, float* gbias, float* partial, cudaStream_t stream);
+
 }  // namespace sfb

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import torch
 from torch.autograd import Function
+from torch.autograd.function import once_differentiable
 
 from . import ops as MemorySaver
 
@@ -210,3 +211,34 @@ class SeparationCompressionCF(Function):
             ctx.state.pending = (a_u, a_v, gc_u, gc_v)
             torch.autograd.Variable._execution_engine.queue_callback(_guard_pending(ctx.state))
         return None, None, ga_u, ga_v, None
+
+
+# --------------------------------------------------------------------------------------------------
+# One pyramid level as a single autograd node: max/avg sweep, both attention modules (Conv3d(2, Kc, 3,
+# padding=1) + softmax over the displacement axis, core/corr.py:437-442) and the compression sweep, writing
+# the concatenated tensors of core/corr.py:454-457 directly.  The backward is one call as well.
+class SeparationLevelFunction(Function):
+    @staticmethod
+    def forward(ctx, img1_features_l0, img2_features_lk, weight_u, bias_u, weight_v, bias_v, with_argmax):
+        assert img1_features_l0.is_contiguous() and img2_features_lk.is_contiguous()
+        with torch.cuda.device_of(img1_features_l0):
+            sep_u, sep_v, am_u, am_v, a_u, a_v = MemorySaver.separation_level_forward(
+                img1_features_l0, img2_features_lk, weight_u.contiguous(), bias_u.contiguous(),
+                weight_v.contiguous(), bias_v.contiguous(), with_argmax)
+        if with_argmax:
+            ctx.save_for_backward(img1_features_l0, img2_features_lk, weight_u, weight_v, sep_u, sep_v, am_u, am_v,
+                                  a_u, a_v)
+        ctx.with_argmax = with_argmax
+        return sep_u, sep_v
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_sep_u, grad_sep_v):
+        if not ctx.with_argmax:
+            raise NotImplementedError("max avg backward pass is not implemented: use max argmax avg")
+        f1, f2, weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v = ctx.saved_tensors
+        with torch.cuda.device_of(grad_sep_u):
+            g1, g2, gw_u, gb_u, gw_v, gb_v = MemorySaver.separation_level_backward(
+                f1, f2, weight_u.contiguous(), weight_v.contiguous(), sep_u, sep_v, am_u, am_v, a_u, a_v,
+                grad_sep_u.contiguous(), grad_sep_v.contiguous())
+        return g1, g2, gw_u, gb_u, gw_v, gb_v, None

@@ -300,6 +300,115 @@ def separation_feature_backward_cf(img1_features_l0, img2_features_lk, am_u, am_
     return [gF1, gF2]
 
 
+# ------------------------------------------------------------------------------------------------------
+# Attention weights of the call site and the whole level in one call (no counterpart in the reference's
+# module; the reference runs torch's Conv3d and softmax between its ops, core/corr.py:437-442).
+def _check_attention_params(weight, bias, name, dev):
+    _check(weight, name + ".weight", torch.float32, 5)
+    Kc = weight.shape[0]
+    _check_like(weight, name + ".weight", (Kc, 2, 3, 3, 3), torch.float32, dev)
+    _check_like(bias, name + ".bias", (Kc,), torch.float32, dev)
+    return Kc
+
+
+def _raise_on(rc, name):
+    if rc != _lib.SFB_OK:
+        lib = _lib.load()
+        raise RuntimeError(f"{name}: {lib.sfb_status_string(rc).decode()}: {lib.sfb_last_error().decode()}")
+
+
+def attention_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """softmax(Conv3d(2 -> Kc, 3, padding=1)(x), dim=2) for x (B,2,D,H1,W1); x may be a channel slice
+    ``t[:, :2]`` of a contiguous (B,K,D,H1,W1) tensor."""
+    if not (isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.float32 and x.dim() == 5 and x.shape[1] == 2):
+        raise RuntimeError("x must be a CUDA float32 tensor of shape (B, 2, D, H1, W1)")
+    B, _, D, H1, W1 = x.shape
+    if not x[0].is_contiguous():
+        raise RuntimeError("x must be contiguous within a sample")
+    Kc = _check_attention_params(weight, bias, "attention", x.device)
+    a = torch.empty(B, Kc, D, H1, W1, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _raise_on(lib.sfb_attention_forward(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(a), B, Kc, D, H1, W1,
+                                            ctypes.c_void_p(stream)), "sfb_attention_forward")
+    return a
+
+
+def attention_backward(x, weight, a, grad_a, add=None) -> List[torch.Tensor]:
+    """[gx (B,2,D,H1,W1), gweight, gbias] of ``attention_forward`` for upstream gradient ``grad_a``; ``add`` (shape
+    of x, may be a channel slice) is added to gx.  ``grad_a`` is left untouched (a copy is consumed)."""
+    B, _, D, H1, W1 = x.shape
+    dev = x.device
+    Kc = weight.shape[0]
+    _check_like(weight, "weight", (Kc, 2, 3, 3, 3), torch.float32, dev)
+    _check_like(a, "a", (B, Kc, D, H1, W1), torch.float32, dev)
+    _check_like(grad_a, "grad_a", (B, Kc, D, H1, W1), torch.float32, dev)
+    g = grad_a.clone()
+    gx = torch.empty(B, 2, D, H1, W1, dtype=torch.float32, device=dev)
+    gw = torch.empty_like(weight)
+    gb = torch.empty(Kc, dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        nbytes = lib.sfb_attention_backward_workspace_bytes(B, Kc, D, H1, W1)
+        ws = _workspace(max(nbytes, 256), dev, stream)
+        _raise_on(lib.sfb_attention_backward(_ptr(x), x.stride(0), _ptr(weight), _ptr(a), _ptr(g), _ptr(add),
+                                             add.stride(0) if add is not None else 0, _ptr(gx), _ptr(gw), _ptr(gb),
+                                             B, Kc, D, H1, W1, ctypes.c_void_p(ws.data_ptr()),
+                                             ctypes.c_size_t(ws.numel()), ctypes.c_void_p(stream)),
+                  "sfb_attention_backward")
+    return [gx, gw, gb]
+
+
+def separation_level_forward(img1_features_l0, img2_features_lk, weight_u, bias_u, weight_v, bias_v,
+                             with_argmax=True) -> List[torch.Tensor]:
+    """One pyramid level of the call site (core/corr.py:419-457 up to the upsampling):
+    [sep_u (B,2+Kc,W2,H1,W1), sep_v (B,2+Kc,H2,H1,W1), am_u, am_v, a_u (B,Kc,W2,H1,W1), a_v (B,Kc,H2,H1,W1)];
+    (weight_u, bias_u) are the parameters of the reference's ``attention1``, which acts on sep_u."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    s.Kc = _check_attention_params(weight_u, bias_u, "attention1", dev)
+    if _check_attention_params(weight_v, bias_v, "attention2", dev) != s.Kc:
+        raise RuntimeError("attention1 and attention2 must have the same number of output channels")
+    f32 = dict(dtype=torch.float32, device=dev)
+    sep_u = torch.empty(s.B, 2 + s.Kc, s.W2, s.H1, s.W1, **f32)
+    sep_v = torch.empty(s.B, 2 + s.Kc, s.H2, s.H1, s.W1, **f32)
+    am_u = torch.empty(s.B, s.H2, s.H1, s.W1, dtype=torch.int32, device=dev) if with_argmax else None
+    am_v = torch.empty(s.B, s.W2, s.H1, s.W1, dtype=torch.int32, device=dev) if with_argmax else None
+    a_u = torch.empty(s.B, s.Kc, s.W2, s.H1, s.W1, **f32)
+    a_v = torch.empty(s.B, s.Kc, s.H2, s.H1, s.W1, **f32)
+    _call("sfb_separation_level_forward", _lib.OP_SEPARATION_LEVEL_FORWARD, s, dev,
+          (F1, F2, weight_u, bias_u, weight_v, bias_v, sep_u, sep_v, am_u, am_v, a_u, a_v))
+    return [sep_u, sep_v, am_u, am_v, a_u, a_v]
+
+
+def separation_level_backward(img1_features_l0, img2_features_lk, weight_u, weight_v, sep_u, sep_v, am_u, am_v,
+                              a_u, a_v, g_sep_u, g_sep_v) -> List[torch.Tensor]:
+    """[gF1, gF2, gweight_u, gbias_u, gweight_v, gbias_v] of ``separation_level_forward``."""
+    F1, F2 = img1_features_l0, img2_features_lk
+    s = _check_pair(F1, F2)
+    dev = F1.device
+    _check_attention_cf(s, a_u, a_v, dev)
+    _check_like(weight_u, "attention1.weight", (s.Kc, 2, 3, 3, 3), torch.float32, dev)
+    _check_like(weight_v, "attention2.weight", (s.Kc, 2, 3, 3, 3), torch.float32, dev)
+    _check_like(am_u, "argmax_u", (s.B, s.H2, s.H1, s.W1), torch.int32, dev)
+    _check_like(am_v, "argmax_v", (s.B, s.W2, s.H1, s.W1), torch.int32, dev)
+    for t, name, D in ((sep_u, "sep_u", s.W2), (sep_v, "sep_v", s.H2), (g_sep_u, "grad_sep_u", s.W2),
+                       (g_sep_v, "grad_sep_v", s.H2)):
+        _check_like(t, name, (s.B, 2 + s.Kc, D, s.H1, s.W1), torch.float32, dev)
+    gF1 = torch.empty_like(F1)
+    gF2 = torch.empty_like(F2)
+    gw_u, gw_v = torch.empty_like(weight_u), torch.empty_like(weight_v)
+    gb_u = torch.empty(s.Kc, dtype=torch.float32, device=dev)
+    gb_v = torch.empty(s.Kc, dtype=torch.float32, device=dev)
+    _call("sfb_separation_level_backward", _lib.OP_SEPARATION_LEVEL_BACKWARD, s, dev,
+          (F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u, g_sep_v, gF1, gF2, gw_u, gb_u,
+           gw_v, gb_v))
+    return [gF1, gF2, gw_u, gb_u, gw_v, gb_v]
+
+
 def corr_volume(img1_features_l0, img2_features_lk) -> torch.Tensor:
     """Test aid: the dense volume S (B,H1,W1,H2,W2) of a small problem, through the tensor-core pipeline."""
     F1, F2 = img1_features_l0, img2_features_lk

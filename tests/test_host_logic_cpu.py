@@ -22,8 +22,11 @@ def oracle_backend(monkeypatch):
     monkeypatch.setattr(functions, "MemorySaver", orc)
 
 
-@pytest.mark.parametrize("fuse_backward,channels_first", [(True, True), (True, False), (False, False)])
-def test_block_matches_reference_dense_path(golden_dir, oracle_backend, fuse_backward, channels_first):
+VARIANTS = [(True, True, True), (True, True, False), (True, False, False), (False, False, False)]
+
+
+@pytest.mark.parametrize("fuse_backward,channels_first,fuse_attention", VARIANTS)
+def test_block_matches_reference_dense_path(golden_dir, oracle_backend, fuse_backward, channels_first, fuse_attention):
     g = np.load(os.path.join(golden_dir, "block_dense_b2_c16_9x11_k2.npz"))
     f1 = _t(g["f1"]).requires_grad_(True)
     f2 = _t(g["f2"]).requires_grad_(True)
@@ -35,7 +38,7 @@ def test_block_matches_reference_dense_path(golden_dir, oracle_backend, fuse_bac
             conv.bias.copy_(_t(g[f"b{i}"]))
         convs.append(conv)
     blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True, fuse_backward=fuse_backward,
-                                        channels_first=channels_first)
+                                        channels_first=channels_first, fuse_attention=fuse_attention)
     sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(convs))
     assert (sep_u - _t(g["sep_u"])).abs().max().item() < 1e-11
     assert (sep_v - _t(g["sep_v"])).abs().max().item() < 1e-11
@@ -83,11 +86,11 @@ def test_fused_backward_without_feature_gradients(oracle_backend):
     f2 = torch.randn(1, 8, 5, 6, dtype=torch.float64)
     convs = [torch.nn.Conv3d(2, 2, 3, padding=1).double() for _ in range(2)]
     outs = []
-    for fuse, cf in ((True, True), (True, False), (False, False)):
+    for fuse, cf, fa in VARIANTS:
         for c in convs:
             c.zero_grad()
         blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=1, support_backward=True, fuse_backward=fuse,
-                                            channels_first=cf)
+                                            channels_first=cf, fuse_attention=fa)
         su, sv = blk(None, sep=True, attention_weights=tuple(convs))
         (su.sum() + (sv * sv).sum()).backward()
         outs.append([c.weight.grad.clone() for c in convs])

@@ -198,6 +198,78 @@ def test_channels_first_ops(shape, cuda_device):
     assert relerr(gF1, r1) < TOL and relerr(gF2, r2) < TOL
 
 
+ATT_TOL = 2e-5   # fp32 stencil + softmax against the float64 oracle
+
+# (B, Kc, D, H1, W1)
+ATT_SHAPES = [(1, 1, 1, 1, 1), (2, 2, 3, 2, 5), (1, 3, 7, 9, 11), (2, 4, 24, 13, 37), (1, 5, 9, 6, 130), (1, 9, 4, 5, 7)]
+
+
+@pytest.mark.parametrize("shape", ATT_SHAPES)
+def test_attention_forward_backward(shape, cuda_device):
+    """Conv3d(2 -> Kc, 3, padding 1) + softmax over the displacement axis (core/corr.py:437-442) and its
+    backward, against torch's own float64 conv3d / softmax / autograd.  The input is a channel slice of a
+    wider tensor, as at the call site."""
+    B, Kc, D, H1, W1 = shape
+    g = torch.Generator().manual_seed(21)
+    wide = torch.randn(B, 2 + Kc, D, H1, W1, generator=g)
+    weight = torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.3
+    bias = torch.randn(Kc, generator=g)
+    grad_a = torch.randn(B, Kc, D, H1, W1, generator=g)
+    add = torch.randn(B, 2 + Kc, D, H1, W1, generator=g)
+    dev = cuda_device
+    wide_d, add_d = wide.to(dev), add.to(dev)
+    a = ops.attention_forward(wide_d[:, :2], weight.to(dev), bias.to(dev))
+    r_a = orc.attention_forward(wide[:, :2].double(), weight.double(), bias.double())
+    assert a.shape == r_a.shape and relerr(a, r_a) < ATT_TOL
+    assert (a.sum(dim=2) - 1).abs().max().item() < 1e-5
+    gx, gw, gb = ops.attention_backward(wide_d[:, :2], weight.to(dev), a, grad_a.to(dev), add_d[:, :2])
+    r_gx, r_gw, r_gb = orc.attention_backward(wide[:, :2].double(), weight.double(), a.double().cpu(), grad_a.double(),
+                                              add[:, :2].double())
+    assert relerr(gx, r_gx) < ATT_TOL and relerr(gw, r_gw) < ATT_TOL
+    assert (gb.double().cpu() - r_gb).abs().max().item() < ATT_TOL * max(r_gw.abs().max().item(), 1.0)
+    gx0, gw0, gb0 = ops.attention_backward(wide_d[:, :2], weight.to(dev), a, grad_a.to(dev))
+    assert relerr(gx0, r_gx - add[:, :2].double()) < ATT_TOL and torch.equal(gw0, gw) and torch.equal(gb0, gb)
+
+
+LEVEL_SHAPES = [s for s in SHAPES if s[1] * s[2] >= 15]
+
+
+@pytest.mark.parametrize("shape", LEVEL_SHAPES)
+def test_separation_level(shape, cuda_device):
+    """One pyramid level in one call (core/corr.py:419-457) against the oracle's chain of the three ops and the
+    two attention modules; the backward is checked with the device forward's own argmax / attention weights."""
+    B, H1, W1, H2, W2, C, Kc = shape
+    F1, F2, _, _, g = make_inputs(shape, 13)
+    params = [torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(Kc, generator=g) * 0.1,
+              torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(Kc, generator=g) * 0.1]
+    dev = cuda_device
+    F1d, F2d = F1.to(dev), F2.to(dev)
+    wu, bu, wv, bv = [t.to(dev) for t in params]
+    sep_u, sep_v, am_u, am_v, a_u, a_v = ops.separation_level_forward(F1d, F2d, wu, bu, wv, bv)
+    ref = orc.separation_level_forward(F1.double(), F2.double(), *[t.double() for t in params])
+    assert sep_u.shape == ref[0].shape and sep_v.shape == ref[1].shape
+    # the attention weights see max/avg values that carry the TF32 error, through a softmax: same budget
+    assert relerr(sep_u, ref[0]) < 2 * TOL and relerr(sep_v, ref[1]) < 2 * TOL
+    assert relerr(a_u, ref[4]) < 2 * TOL and relerr(a_v, ref[5]) < 2 * TOL
+    inf = ops.separation_level_forward(F1d, F2d, wu, bu, wv, bv, with_argmax=False)
+    assert inf[2] is None and torch.equal(inf[0], sep_u) and torch.equal(inf[1], sep_v)
+    g_sep_u = torch.randn(sep_u.shape, generator=g)
+    g_sep_v = torch.randn(sep_v.shape, generator=g)
+    out = ops.separation_level_backward(F1d, F2d, wu, wv, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u.to(dev),
+                                        g_sep_v.to(dev))
+    r = orc.separation_level_backward(F1.double(), F2.double(), params[0].double(), params[2].double(),
+                                      sep_u.double().cpu(), sep_v.double().cpu(), am_u.cpu(), am_v.cpu(),
+                                      a_u.double().cpu(), a_v.double().cpu(), g_sep_u.double(), g_sep_v.double())
+    assert relerr(out[0], r[0]) < TOL and relerr(out[1], r[1]) < TOL
+    for i in (2, 4):
+        assert relerr(out[i], r[i]) < TOL
+        assert (out[i + 1].double().cpu() - r[i + 1]).abs().max().item() < TOL * max(r[i].abs().max().item(), 1.0)
+    again = ops.separation_level_backward(F1d, F2d, wu, wv, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u.to(dev),
+                                          g_sep_v.to(dev))
+    for x, y in zip(out, again):
+        assert torch.equal(x, y)
+
+
 def test_backward_is_deterministic(cuda_device):
     """Gradients accumulate in TMEM, not with atomics: two runs are bit-identical."""
     shape = (2, 24, 40, 24, 40, 128, 2)
@@ -234,8 +306,9 @@ def test_golden_op_vectors(golden_dir, cuda_device):
         assert relerr(C_v, torch.from_numpy(gold[f"l{level}_C_v"]).permute(0, 3, 4, 1, 2)) < TOL
 
 
-@pytest.mark.parametrize("fuse_backward,channels_first", [(True, True), (True, False), (False, False)])
-def test_block_against_reference_dense_vectors(golden_dir, cuda_device, fuse_backward, channels_first):
+@pytest.mark.parametrize("fuse_backward,channels_first,fuse_attention",
+                         [(True, True, True), (True, True, False), (True, False, False), (False, False, False)])
+def test_block_against_reference_dense_vectors(golden_dir, cuda_device, fuse_backward, channels_first, fuse_attention):
     """The whole call site (4 pyramid levels, Conv3d attention, autograd) on the GPU against the
     vectors of the reference's dense CorrBlock.  Gradients flow through argmax choices; the seeded
     case has no near-ties at the MARGIN level, so the same tolerance applies."""
@@ -250,7 +323,7 @@ def test_block_against_reference_dense_vectors(golden_dir, cuda_device, fuse_bac
             conv.bias.copy_(torch.from_numpy(gold[f"b{i}"]).float())
         convs.append(conv)
     blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, support_backward=True, fuse_backward=fuse_backward,
-                                        channels_first=channels_first)
+                                        channels_first=channels_first, fuse_attention=fuse_attention)
     sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(convs))
     assert relerr(sep_u, torch.from_numpy(gold["sep_u"])) < TOL
     assert relerr(sep_v, torch.from_numpy(gold["sep_v"])) < TOL
