@@ -103,9 +103,21 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------- workload
-def make_job(cfg, shard, device):
+def attention_parameters(Kc, device=None):
+    """Seeded N(0, 0.02) parameters of the two Conv3d(2, Kc, 3, padding=1) attention modules:
+    [weight_u, bias_u, weight_v, bias_v]."""
+    g = torch.Generator().manual_seed(SEED + 99)
+    out = []
+    for _ in range(2):
+        out.append(torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.02)
+        out.append(torch.randn(Kc, generator=g) * 0.02)
+    return [t.to(device) for t in out] if device is not None else out
+
+
+def make_job(cfg, shard, device, path="ops"):
     """Seeded N(0,1) features of this rank's shard (drawn for the whole job, then sliced, so every
-    world size sees the same data), softmaxed random attention weights and N(0,1) upstream gradients."""
+    world size sees the same data) and N(0,1) upstream gradients; for the five reference ops also softmaxed
+    random attention weights, for the level calls the attention parameters."""
     B, H, W, Kc = cfg["B"], cfg["H"], cfg["W"], cfg["Kc"]
     g = torch.Generator().manual_seed(SEED)
     f1 = torch.randn(B, C_FEAT, H, W, generator=g)
@@ -118,6 +130,13 @@ def make_job(cfg, shard, device):
     b, h = F1.shape[0], F1.shape[1]
     gd = torch.Generator(device=device).manual_seed(SEED + 1 + shard.rank)
     job.update(F1=F1, F2=F2)
+    job["cells"] = b * h * W * H * W
+    if path == "level":
+        job["att"] = attention_parameters(Kc, device)
+        if cfg["bwd"]:
+            job["gSEP_u"] = torch.randn(b, 2 + Kc, W, h, W, generator=gd, device=device)
+            job["gSEP_v"] = torch.randn(b, 2 + Kc, H, h, W, generator=gd, device=device)
+        return job
     if Kc > 0:
         job["A_u"] = torch.randn(b, h, W, Kc, W, generator=gd, device=device).softmax(-1)
         job["A_v"] = torch.randn(b, h, W, Kc, H, generator=gd, device=device).softmax(-1)
@@ -127,13 +146,28 @@ def make_job(cfg, shard, device):
         if Kc > 0:
             job["gC_u"] = torch.randn(b, h, W, Kc, H, generator=gd, device=device)
             job["gC_v"] = torch.randn(b, h, W, Kc, W, generator=gd, device=device)
-    job["cells"] = b * h * W * H * W
     return job
 
 
+def run_level(ms, cfg, job):
+    """The hot path on device-resident inputs as the call site runs it: one library call for the level's
+    forward (max/avg sweep, attention weights, compression sweep) and one for its backward."""
+    F1, F2 = job["F1"], job["F2"]
+    wu, bu, wv, bv = job["att"]
+    out = ms.separation_level_forward(F1, F2, wu, bu, wv, bv, with_argmax=cfg["bwd"])
+    if cfg["bwd"]:
+        sep_u, sep_v, am_u, am_v, a_u, a_v = out
+        out = out + ms.separation_level_backward(F1, F2, wu, wv, sep_u, sep_v, am_u, am_v, a_u, a_v, job["gSEP_u"],
+                                                 job["gSEP_v"])
+    return out
+
+
 def run_ops(ms, cfg, job, fused=True):
-    """The hot path on device-resident inputs.  With `fused` the two backward ops run as the library's
-    one-call backward (same outputs; the feature gradients of the two ops arrive already summed)."""
+    """The hot path on device-resident inputs through the five ops of the reference's module (random softmaxed
+    attention weights stand in for the Conv3d modules the call site runs between them).  With `fused` the two
+    backward ops run as the library's one-call backward (same outputs; feature gradients arrive summed)."""
+    if "att" in job:
+        return run_level(ms, cfg, job)
     F1, F2 = job["F1"], job["F2"]
     if cfg["bwd"]:
         MA_u, MA_v, AM_u, AM_v = ms.max_argmax_avg_forward(F1, F2)
@@ -179,13 +213,13 @@ class E2E:
         self.h2 = job["f2_nchw"].pin_memory()
         self.att = None
         if cfg["Kc"] > 0:
-            g = torch.Generator().manual_seed(SEED + 99)
+            params = attention_parameters(cfg["Kc"])
             self.att = []
-            for _ in range(2):
+            for i in range(2):
                 conv = torch.nn.Conv3d(2, cfg["Kc"], 3, padding=1)
                 with torch.no_grad():
-                    conv.weight.copy_(torch.randn(conv.weight.shape, generator=g) * 0.02)
-                    conv.bias.copy_(torch.randn(conv.bias.shape, generator=g) * 0.02)
+                    conv.weight.copy_(params[2 * i])
+                    conv.bias.copy_(params[2 * i + 1])
                 self.att.append(conv.to(device))
         self.up = None
         self.host_out = torch.empty(1024, dtype=torch.float32).pin_memory()
@@ -242,13 +276,18 @@ def cpu_sample(cfg, rows, threads):
     gC_u = torch.randn(1, rows, W, max(Kc, 1), H, generator=g)
     gC_v = torch.randn(1, rows, W, max(Kc, 1), W, generator=g)
 
+    att = attention_parameters(Kc) if Kc > 0 else None
+    gS_u = torch.randn(1, 2 + Kc, W, rows, W, generator=g)
+    gS_v = torch.randn(1, 2 + Kc, H, rows, W, generator=g)
+
     def run():
+        if Kc > 0:   # the level as the reference's dense path chains it: ops + Conv3d attention + softmax
+            fw = orc.separation_level_forward(F1, F2, *att)
+            if cfg["bwd"]:
+                orc.separation_level_backward(F1, F2, att[0], att[2], *fw, gS_u, gS_v)
+            return
         fw = orc.max_argmax_avg_forward(F1, F2)
-        if Kc > 0:
-            orc.compression_forward(F1, F2, A_u, A_v)
         if cfg["bwd"]:
-            if Kc > 0:
-                orc.compression_backward(F1, F2, A_u, A_v, gC_u, gC_v)
             orc.max_argmax_avg_backward(F1, F2, fw[2], fw[3], gMA_u, gMA_v)
     return run, rows * W * H * W
 
@@ -272,7 +311,8 @@ def time_cpu(cfg, budget_s, steps=None, warmup=1):
     dt = (time.perf_counter() - t0) / n_steps
     return dict(value=cells / dt, unit="cells/s", cores=threads, kind="port",
                 sample=f"{rows} of {cfg['H']} image-1 rows of one sample ({cells} cells) per step, {n_steps} steps, "
-                       f"oracle (dense torch CPU fp32 matmul/einsum + max/mean), {threads} threads"), dt, n_steps
+                       f"oracle (dense torch CPU fp32 matmul/einsum + max/mean + conv3d/softmax attention), "
+                       f"{threads} threads"), dt, n_steps
 
 
 # --------------------------------------------------------------------------------------- main
@@ -322,6 +362,10 @@ def main():
     ap.add_argument("--no-roofline", action="store_true", help="skip the per-kernel timing pass and the TF32 peak run")
     ap.add_argument("--unfused", action="store_true",
                     help="run the two backward ops as the reference's two separate calls instead of the one-call backward")
+    ap.add_argument("--path", default="auto", choices=["auto", "level", "ops"],
+                    help="level: one library call per pyramid-level forward / backward, as the call site runs it "
+                         "(attention Conv3d + softmax included); ops: the five ops of the reference's module with "
+                         "random attention weights; auto: level when the config has attention channels")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small ncu captures)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
@@ -357,7 +401,13 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     shard = sharding.make_shard(cfg["B"], cfg["H"], world, rank)
-    job = make_job(cfg, shard, device)
+    path = args.path
+    if path == "auto":
+        path = "level" if cfg["Kc"] > 0 and shard.g_rows == 1 and not args.unfused else "ops"
+    if path == "level" and (cfg["Kc"] == 0 or shard.g_rows > 1):
+        raise SystemExit("--path level needs attention channels and whole image-1 rows per rank (the 3x3x3 "
+                         "attention stencil crosses row shards)")
+    job = make_job(cfg, shard, device, path)
 
     def barrier():
         if world > 1:
@@ -405,10 +455,13 @@ def main():
         report = _lib.kernel_timing_report()
         _lib.kernel_timing(False)
     roofline, kernels = None, []
+    # kernels of this library per step: counted by the library when the timing pass ran, else from the op list
+    launches = (sum(r[2] for r in report) // min(args.steps, 3)) if report else launches_per_step(cfg)
     if rank == 0 and report:
         tot = sum(r[1] for r in report)
         kernels = [{"kernel": n, "launches": l, "ms_per_launch": t / l, "share": t / tot} for n, t, l in report]
-        name, t, l = max((r for r in report if not r[0].startswith("prepare")), key=lambda r: r[1])
+        name, t, l = max((r for r in report if r[0].startswith(("sweep_kernel", "grad_gemm_kernel"))),
+                         key=lambda r: r[1])   # the dominant contraction kernel
         tf32_burst, tf32_sust = measure_tf32_peak(device)
         fl = 2.0 * C_FEAT * job["cells"]            # one contraction over this rank's cells per launch
         achieved = fl / (t / l * 1e-3) / 1e12
@@ -459,11 +512,12 @@ def main():
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "tf32 operands (fp32 in HBM), fp32 accumulate", "data": "synthetic",
-        "config": {"workload": cfg["name"], "cells_per_step": total_cells, "flop_per_cell": flops_per_cell(cfg),
+        "config": {"workload": cfg["name"], "path": path, "cells_per_step": total_cells,
+                   "flop_per_cell": flops_per_cell(cfg),
                    "sharding": f"batch x rows = {shard.g_batch} x {shard.g_rows}",
                    "l2": "inputs larger than L2" if args.config >= 3 else "inputs smaller than L2 (launch-bound case)"},
         "useful_tflops": value * flops_per_cell(cfg) / 1e12,
-        "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step(cfg) * args.steps,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps,
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,
     }
     emit(line)

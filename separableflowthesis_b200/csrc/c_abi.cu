@@ -48,6 +48,14 @@ int make_map(CUtensorMap* tm, const float* base, int rank, const uint64_t* dims,
              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+  // The driver call needs a context that is current to this thread.  A thread that has made no runtime call yet
+  // (an autograd worker whose first node is one of these ops) has none; cudaFree(0) binds the primary context.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaError_t e = cudaFree(nullptr);
+    if (e != cudaSuccess) return fail(SFB_ERR_CUDA, "cudaFree(0): %s", cudaGetErrorString(e));
+    context_bound = true;
+  }
   cuuint64_t gdim[5], gstride[5];
   cuuint32_t bdim[5], estride[5];
   uint64_t stride = sizeof(float);

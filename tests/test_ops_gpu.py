@@ -270,6 +270,38 @@ def test_separation_level(shape, cuda_device):
         assert torch.equal(x, y)
 
 
+def test_ops_from_a_fresh_thread(cuda_device):
+    """A thread that has not touched CUDA yet (an autograd worker whose first node is one of these ops) can call
+    every entry point: the library binds the device context itself before it builds tensor maps."""
+    import threading
+    shape = (1, 6, 9, 6, 9, 16, 2)
+    F1, F2, _, _, g = make_inputs(shape, 17)
+    params = [torch.randn(2, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(2, generator=g) * 0.1,
+              torch.randn(2, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(2, generator=g) * 0.1]
+    dev = cuda_device
+    F1d, F2d = F1.to(dev), F2.to(dev)
+    wu, bu, wv, bv = [t.to(dev) for t in params]
+    fw = ops.separation_level_forward(F1d, F2d, wu, bu, wv, bv)
+    gs = [torch.randn(fw[0].shape, generator=g).to(dev), torch.randn(fw[1].shape, generator=g).to(dev)]
+    ref = ops.separation_level_backward(F1d, F2d, wu, wv, *fw, *gs)
+    torch.cuda.synchronize()
+    box = {}
+
+    def work():
+        try:
+            box["out"] = ops.separation_level_backward(F1d, F2d, wu, wv, *fw, *gs)
+            torch.cuda.synchronize()
+        except Exception as e:  # surfaced below
+            box["err"] = e
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert "err" not in box, box.get("err")
+    for x, y in zip(ref, box["out"]):
+        assert torch.equal(x, y)
+
+
 def test_backward_is_deterministic(cuda_device):
     """Gradients accumulate in TMEM, not with atomics: two runs are bit-identical."""
     shape = (2, 24, 40, 24, 40, 128, 2)
