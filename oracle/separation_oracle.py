@@ -261,8 +261,16 @@ def attention_backward(x, weight, a, grad_a, add=None):
     return [x.grad if add is None else x.grad + add, weight.grad, bias.grad]
 
 
-def separation_level_forward(F1, F2, weight_u, bias_u, weight_v, bias_v, with_argmax=True):
-    """[sep_u (B,2+Kc,W2,H1,W1), sep_v (B,2+Kc,H2,H1,W1), am_u, am_v, a_u, a_v] (core/corr.py:425-457)."""
+def _from_fmaps(fmap1, fmap2, scale1):
+    """core/corr.py:419-422: channels-last copies, image 1 scaled."""
+    return fmap1.permute(0, 2, 3, 1).contiguous() * scale1, fmap2.permute(0, 2, 3, 1).contiguous()
+
+
+def separation_level_forward(F1, F2, weight_u, bias_u, weight_v, bias_v, with_argmax=True, fmaps=False, scale1=1.0):
+    """[sep_u (B,2+Kc,W2,H1,W1), sep_v (B,2+Kc,H2,H1,W1), am_u, am_v, a_u, a_v] (core/corr.py:425-457); with
+    ``fmaps`` from the model's (B,C,H,W) maps (core/corr.py:419-422)."""
+    if fmaps:
+        F1, F2 = _from_fmaps(F1, F2, scale1)
     ma_v2, ma_u2, am_u, am_v = max_argmax_avg_forward_cf(F1, F2, with_argmax)   # sep_v (per u), sep_u (per v)
     a_u = attention_forward(ma_u2, weight_u, bias_u)
     a_v = attention_forward(ma_v2, weight_v, bias_v)
@@ -270,9 +278,12 @@ def separation_level_forward(F1, F2, weight_u, bias_u, weight_v, bias_v, with_ar
     return [torch.cat((ma_u2, c_v), dim=1), torch.cat((ma_v2, c_u), dim=1), am_u, am_v, a_u, a_v]
 
 
-def separation_level_backward(F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u, g_sep_v):
+def separation_level_backward(F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u, g_sep_v,
+                              fmaps=False, scale1=1.0):
     """[gF1, gF2, gweight_u, gbias_u, gweight_v, gbias_v]: the chain rule through the three ops and the two
     attention modules, with the forward's argmax and attention weights given."""
+    if fmaps:
+        F1, F2 = _from_fmaps(F1, F2, scale1)
     gc_v = g_sep_u[:, 2:].contiguous()
     gc_u = g_sep_v[:, 2:].contiguous()
     ga_u, ga_v = compression_attention_backward_cf(F1, F2, gc_u, gc_v)
@@ -280,6 +291,9 @@ def separation_level_backward(F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am
     gm_v, gw_v, gb_v = attention_backward(sep_v[:, :2], weight_v, a_v, ga_v, g_sep_v[:, :2])
     gm_u, gm_v = gm_u.contiguous(), gm_v.contiguous()
     gF1, gF2 = separation_feature_backward_cf(F1, F2, am_u, am_v, gm_v, gm_u, a_u, a_v, gc_u, gc_v)
+    if fmaps:
+        gF1 = (gF1 * scale1).permute(0, 3, 1, 2).contiguous()
+        gF2 = gF2.permute(0, 3, 1, 2).contiguous()
     return [gF1, gF2, gw_u, gb_u, gw_v, gb_v]
 
 

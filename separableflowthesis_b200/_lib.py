@@ -41,6 +41,7 @@ EXPORTED_SYMBOLS = (
     "sfb_max_argmax_avg_forward_cf", "sfb_compression_forward_cf", "sfb_compression_attention_backward_cf",
     "sfb_separation_feature_backward_cf", "sfb_attention_forward", "sfb_attention_backward_workspace_bytes",
     "sfb_attention_backward", "sfb_separation_level_forward", "sfb_separation_level_backward",
+    "sfb_separation_level_forward_fmaps", "sfb_separation_level_backward_fmaps",
 )
 
 
@@ -83,6 +84,10 @@ def load() -> ctypes.CDLL:
     lib.sfb_attention_backward_workspace_bytes.argtypes = [I32] * 5
     lib.sfb_attention_backward.restype = ctypes.c_int
     lib.sfb_attention_backward.argtypes = [P, I64, P, P, P, P, I64, P, P, P, I32, I32, I32, I32, I32, P, SZ, P]
+    lib.sfb_separation_level_forward_fmaps.restype = ctypes.c_int
+    lib.sfb_separation_level_forward_fmaps.argtypes = [P, P, ctypes.c_float] + [P] * 10 + tail
+    lib.sfb_separation_level_backward_fmaps.restype = ctypes.c_int
+    lib.sfb_separation_level_backward_fmaps.argtypes = [P, P, ctypes.c_float] + [P] * 16 + tail
     lib.sfb_max_avg_forward_static.restype = ctypes.c_int
     lib.sfb_max_avg_forward_static.argtypes = [P, P, P, P, SH, P]
     lib.sfb_static_scratch_bytes.restype = SZ

@@ -10,8 +10,9 @@ which autograd would add, come out of one pair of gradient GEMMs instead of two;
 Conv3d attention directly, which removes the permute copies of core/corr.py:428-429,445-446,451-452; with
 ``fuse_attention`` (default) a level whose attention modules are the Conv3d(2, Kc, 3, padding=1) of
 core/sepflow.py:59-60 is one autograd node whose forward and backward are one library call each (the
-Conv3d + softmax run in the library's stencil kernels and the concatenations of core/corr.py:454-457 are written
-in place); a level that already has the level-0 displacement range skips the trilinear resampling, which is
+Conv3d + softmax run in the library's stencil kernels, the concatenations of core/corr.py:454-457 are written
+in place, and the (B,C,H,W) feature maps are read directly, which removes the channels-last and scaled copies of
+core/corr.py:419-422); a level that already has the level-0 displacement range skips the trilinear resampling, which is
 the identity there.
 """
 from __future__ import annotations
@@ -55,15 +56,21 @@ class AlternateCorrBlockSepflow:
             fmap2 = F.avg_pool2d(fmap2, 2, stride=2)
             self.pyramid.append(fmap2)
 
+    def _one_node_per_level(self, attention_weights) -> bool:
+        return (self.channels_first and self.fuse_backward and self.fuse_attention and attention_weights is not None
+                and all(_is_standard_attention(m) for m in attention_weights)
+                and attention_weights[0].out_channels == attention_weights[1].out_channels)
+
     def separate_level(self, F1, level, attention_weights):
         """One pyramid level: returns (sep_u (B,K,W2,H1,W1), sep_v (B,K,H2,H1,W1)) before upsampling."""
-        F2 = self.pyramid[level].permute(0, 2, 3, 1).contiguous()
-        if (self.channels_first and self.fuse_backward and self.fuse_attention and attention_weights is not None
-                and all(_is_standard_attention(m) for m in attention_weights)
-                and attention_weights[0].out_channels == attention_weights[1].out_channels):
+        if self._one_node_per_level(attention_weights):
+            # the library reads the (B,C,H,W) maps themselves: no channels-last copies, no scaled copy of fmap1
             attention1, attention2 = attention_weights
-            return SeparationLevelFunction.apply(F1, F2, attention1.weight, attention1.bias, attention2.weight,
-                                                 attention2.bias, self.support_backward)
+            return SeparationLevelFunction.apply(self.fmap1_l0.contiguous(), self.pyramid[level].contiguous(),
+                                                 attention1.weight, attention1.bias, attention2.weight,
+                                                 attention2.bias, self.support_backward, True,
+                                                 1.0 / math.sqrt(self.fmap1_l0.shape[1]))
+        F2 = self.pyramid[level].permute(0, 2, 3, 1).contiguous()
         if self.channels_first and self.fuse_backward and attention_weights is not None:
             state = SeparationState()
             sep_v, sep_u = SeparationMaxAvgCF.apply(F1, F2, state, self.support_backward)
@@ -97,7 +104,9 @@ class AlternateCorrBlockSepflow:
         """All levels, each trilinearly resampled to the level-0 displacement range and concatenated
         over channels: sep_u (B, K*levels, W, H, W), sep_v (B, K*levels, H, H, W) (core/corr.py:384-477)."""
         batch, fdim, h1, w1 = self.fmap1_l0.shape
-        F1 = self.fmap1_l0.permute(0, 2, 3, 1).contiguous() / math.sqrt(fdim)
+        F1 = None
+        if not self._one_node_per_level(attention_weights):
+            F1 = self.fmap1_l0.permute(0, 2, 3, 1).contiguous() / math.sqrt(fdim)
         sep_u_lvls, sep_v_lvls = [], []
         for level in range(self.num_levels):
             sep_u, sep_v = self.separate_level(F1, level, attention_weights)

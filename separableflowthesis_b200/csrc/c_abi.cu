@@ -363,8 +363,9 @@ int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, co
   return SFB_OK;
 }
 
+// out_cf: the gradients are written channel-major, (B, C, pixels), gF1 multiplied by scale1.
 int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accumulate, float* gF1, float* gF2,
-                  cudaStream_t st) {
+                  cudaStream_t st, int out_cf = 0, float scale1 = 1.f) {
   CUtensorMap tm_y, tm_xu, tm_xv;
   GradArgs a;
   memset(&a, 0, sizeof(a));
@@ -381,8 +382,10 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2 and 2-row blocks of XU.
   SFB_TRY(map_f2_tile(&tm_y, d, w.F2r, GG_UT, GG_VT, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
   SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, TILE_M / 2, GG_UT));  // two 64-pixel boxes per block
+  a.out_cf = out_cf;
   a.image2_major = 0;
   a.out = gF1;
+  a.out_scale = scale1;
   SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(a, tm_y, tm_xu, tm_xu /* unused */, st); }));
   // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1, XU and XV.
   SFB_TRY(map_f1_rows(&tm_y, d, w.F1r, GG_KJ, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
@@ -390,6 +393,7 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   SFB_TRY(map_operands(&tm_xv, w.gxv, d.B, d.W2, Q, w.n1p, GG_KJ, GG_ROW_VT));
   a.image2_major = 1;
   a.out = gF2;
+  a.out_scale = 1.f;
   SFB_CUDA(timed(kid + 1, 1, st, [&] { return launch_grad_gemm(a, tm_y, tm_xu, tm_xv, st); }));
   return SFB_OK;
 }
@@ -754,7 +758,7 @@ int sfb_compression_attention_backward_cf(const float* F1, const float* F2, cons
 static int run_fused_feature_grads_cf(const Dims& d, const Workspace& w, const int32_t* AM_u, const int32_t* AM_v,
                                       const float* gM_v, const float* gM_u, const float* A_u, const float* A_v,
                                       const float* gC_u, const float* gC_v, int gK, int g0, float* gF1, float* gF2,
-                                      cudaStream_t st) {
+                                      cudaStream_t st, int out_cf = 0, float scale1 = 1.f) {
   const int N1 = d.N1(), K = d.Kc;
   {
     const int kc = chunk_channels(K), Qc = grad_slots(kc) / 4, Q = 1 + Qc;
@@ -768,7 +772,7 @@ static int run_fused_feature_grads_cf(const Dims& d, const Workspace& w, const i
       launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4 * Qc, Q, 1, st);
       return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4 * Qc, Q, 1, st);
     }));
-    SFB_TRY(run_grad_pair(d, w, GRAD_FUSED, 4 * Q, 0, gF1, gF2, st));
+    SFB_TRY(run_grad_pair(d, w, GRAD_FUSED, 4 * Q, 0, gF1, gF2, st, out_cf, scale1));
   }
   for (int k0 = KC_MAX_PER_SWEEP; k0 < K; k0 += KC_MAX_PER_SWEEP) {
     const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
@@ -778,7 +782,7 @@ static int run_fused_feature_grads_cf(const Dims& d, const Workspace& w, const i
       launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
       return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
     }));
-    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R4, 1, gF1, gF2, st));
+    SFB_TRY(run_grad_pair(d, w, GRAD_COMPRESS, R4, 1, gF1, gF2, st, out_cf, scale1));
   }
   return SFB_OK;
 }
@@ -857,10 +861,11 @@ static PixView cf_channels(const void* base, int Ktot, int c0, int D, int N1) {
                  (uint32_t)N1, (uint32_t)(D * N1)};
 }
 
-int sfb_separation_level_forward(const float* F1, const float* F2, const float* weight_u, const float* bias_u,
-                                 const float* weight_v, const float* bias_v, float* SEP_u, float* SEP_v,
-                                 int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape,
-                                 void* workspace, size_t workspace_bytes, void* stream) {
+// fmaps != 0: F1 / F2 are the model's feature maps (B, C, H, W); F1 is multiplied by scale1 on the way in.
+static int level_forward(const float* F1, const float* F2, int fmaps, float scale1, const float* weight_u,
+                         const float* bias_u, const float* weight_v, const float* bias_v, float* SEP_u, float* SEP_v,
+                         int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape,
+                         void* workspace, size_t workspace_bytes, void* stream) {
   Dims d;
   SFB_TRY(check_shape(shape, true, &d));
   AttentionDims ad;
@@ -877,7 +882,10 @@ int sfb_separation_level_forward(const float* F1, const float* F2, const float* 
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
   SFB_TRY(map_aux(&tm_aux, d, w.aux));
-  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] {
+    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, w.aux, w.status, st)
+                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st);
+  }));
   const int N1 = d.N1(), K = d.Kc, Kt = 2 + d.Kc;
   SweepArgs a;
   memset(&a, 0, sizeof(a));
@@ -900,12 +908,28 @@ int sfb_separation_level_forward(const float* F1, const float* F2, const float* 
                              cf_channels(SEP_v, Kt, 2, d.H2, N1), cf_channels(SEP_u, Kt, 2, d.W2, N1), N1, st);
 }
 
-int sfb_separation_level_backward(const float* F1, const float* F2, const float* weight_u, const float* weight_v,
-                                  const float* SEP_u, const float* SEP_v, const int32_t* AM_u, const int32_t* AM_v,
-                                  const float* A_u, const float* A_v, const float* gSEP_u, const float* gSEP_v,
-                                  float* gF1, float* gF2, float* gweight_u, float* gbias_u, float* gweight_v,
-                                  float* gbias_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
-                                  void* stream) {
+int sfb_separation_level_forward(const float* F1, const float* F2, const float* weight_u, const float* bias_u,
+                                 const float* weight_v, const float* bias_v, float* SEP_u, float* SEP_v,
+                                 int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  return level_forward(F1, F2, 0, 1.f, weight_u, bias_u, weight_v, bias_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v, shape,
+                       workspace, workspace_bytes, stream);
+}
+
+int sfb_separation_level_forward_fmaps(const float* fmap1, const float* fmap2, float scale1, const float* weight_u,
+                                       const float* bias_u, const float* weight_v, const float* bias_v, float* SEP_u,
+                                       float* SEP_v, int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v,
+                                       const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream) {
+  return level_forward(fmap1, fmap2, 1, scale1, weight_u, bias_u, weight_v, bias_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v,
+                       shape, workspace, workspace_bytes, stream);
+}
+
+static int level_backward(const float* F1, const float* F2, int fmaps, float scale1, const float* weight_u,
+                          const float* weight_v, const float* SEP_u, const float* SEP_v, const int32_t* AM_u,
+                          const int32_t* AM_v, const float* A_u, const float* A_v, const float* gSEP_u,
+                          const float* gSEP_v, float* gF1, float* gF2, float* gweight_u, float* gbias_u,
+                          float* gweight_v, float* gbias_v, const sfb_shape* shape, void* workspace,
+                          size_t workspace_bytes, void* stream) {
   Dims d;
   SFB_TRY(check_shape(shape, true, &d));
   AttentionDims ad;
@@ -921,7 +945,10 @@ int sfb_separation_level_backward(const float* F1, const float* F2, const float*
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
   SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] {
+    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, nullptr, w.status, st)
+                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st);
+  }));
   const int N1 = d.N1(), K = d.Kc, Kt = 2 + d.Kc;
   // attention gradients: gA_v(b,k,u,p) = sum_v S * gC_v(b,k,v,p), gA_u(b,k,v,p) = sum_u S * gC_u(b,k,u,p), with
   // gC_u = gSEP_v[:, 2:] (per u) and gC_v = gSEP_u[:, 2:] (per v) in the role of the weights
@@ -936,8 +963,32 @@ int sfb_separation_level_backward(const float* F1, const float* F2, const float*
     return launch_attention_backward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v, sb_v, weight_v, A_v, w.ga_v, gSEP_v,
                                      sb_v, w.gm_v, gweight_v, gbias_v, w.at_partial, st);
   }));
-  return run_fused_feature_grads_cf(d, w, AM_u, AM_v, w.gm_v, w.gm_u, A_u, A_v, gSEP_v, gSEP_u, Kt, 2, gF1, gF2, st);
+  return run_fused_feature_grads_cf(d, w, AM_u, AM_v, w.gm_v, w.gm_u, A_u, A_v, gSEP_v, gSEP_u, Kt, 2, gF1, gF2, st,
+                                    fmaps, fmaps ? scale1 : 1.f);
 }
+
+int sfb_separation_level_backward(const float* F1, const float* F2, const float* weight_u, const float* weight_v,
+                                  const float* SEP_u, const float* SEP_v, const int32_t* AM_u, const int32_t* AM_v,
+                                  const float* A_u, const float* A_v, const float* gSEP_u, const float* gSEP_v,
+                                  float* gF1, float* gF2, float* gweight_u, float* gbias_u, float* gweight_v,
+                                  float* gbias_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                                  void* stream) {
+  return level_backward(F1, F2, 0, 1.f, weight_u, weight_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v, gSEP_u, gSEP_v, gF1, gF2,
+                        gweight_u, gbias_u, gweight_v, gbias_v, shape, workspace, workspace_bytes, stream);
+}
+
+int sfb_separation_level_backward_fmaps(const float* fmap1, const float* fmap2, float scale1, const float* weight_u,
+                                        const float* weight_v, const float* SEP_u, const float* SEP_v,
+                                        const int32_t* AM_u, const int32_t* AM_v, const float* A_u, const float* A_v,
+                                        const float* gSEP_u, const float* gSEP_v, float* gfmap1, float* gfmap2,
+                                        float* gweight_u, float* gbias_u, float* gweight_v, float* gbias_v,
+                                        const sfb_shape* shape, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+  return level_backward(fmap1, fmap2, 1, scale1, weight_u, weight_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v, gSEP_u, gSEP_v,
+                        gfmap1, gfmap2, gweight_u, gbias_u, gweight_v, gbias_v, shape, workspace, workspace_bytes,
+                        stream);
+}
+
 
 int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,
                     size_t workspace_bytes, void* stream) {

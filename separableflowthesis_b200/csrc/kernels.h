@@ -81,6 +81,8 @@ struct GradArgs {
   int R4;                // slots per pixel in the interleaved operands: 4 or 8
   int n1p;               // padded pixel count of the interleaved operands
   int accumulate;        // 0: out = result, 1: out += result (later channel chunks of the compression op)
+  int out_cf;            // 0: out is (B, pixels, C); 1: out is (B, C, pixels), the layout of the model's feature maps
+  float out_scale;       // the result is multiplied by this before it is stored / added (out_cf only)
   const float* xu;
   const float* xv;
   float* out;            // gF1 (B,N1,C) or gF2 (B,N2,C)
@@ -110,6 +112,11 @@ cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, i
 // row/column mean rows of F2, and clears the status word.
 cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
                            int* status, cudaStream_t stream);
+// The same from the model's feature maps fmap1 (B, C, H1, W1), fmap2 (B, C, H2, W2): F1r = round(scale1 * fmap1)
+// transposed to (B, H1, W1, C), F2r = round(fmap2) transposed (core/corr.py:419-422 does this with
+// permute().contiguous() and a division).
+cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
+                              float* F2r, float* aux, int* status, cudaStream_t stream);
 // Pack: dst[b][d][r0 + k*rstride][p] = scale * src[b][p][ksrc0 + k][d] for k < K (raw 32-bit copy when
 // scale == 0), zero for N1 <= p < n1p.  src is (B, N1, Ksrc, D), dst is (B, D, R, n1p).
 cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,

@@ -187,6 +187,42 @@ cudaError_t launch_unpack(const float* src, void* dst, int B, int N1, int n1p, i
   return cudaGetLastError();
 }
 
+// (B, C, N) -> (B, N, C), scaled and rounded to TF32.  32 x 32 tiles through shared memory; grid
+// (ceil(N/32), ceil(C/32), B), block (32, 8).
+__global__ void transpose_round_kernel(const float* __restrict__ in, float* __restrict__ out, int C, int N,
+                                       float scale) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z, p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int c = c0 + j, p = p0 + tx;
+    tile[j][tx] = (c < C && p < N) ? __ldg(in + ((size_t)b * C + c) * N + p) : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int p = p0 + j, c = c0 + tx;
+    if (p < N && c < C) out[((size_t)b * N + p) * C + c] = round_tf32(tile[tx][j] * scale);
+  }
+}
+
+cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
+                              float* F2r, float* aux, int* status, cudaStream_t stream) {
+  cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  if (err != cudaSuccess) return err;
+  const dim3 block(32, 8);
+  transpose_round_kernel<<<dim3((d.N1() + 31) / 32, (d.C + 31) / 32, d.B), block, 0, stream>>>(fmap1, F1r, d.C, d.N1(),
+                                                                                               scale1);
+  transpose_round_kernel<<<dim3((d.N2() + 31) / 32, (d.C + 31) / 32, d.B), block, 0, stream>>>(fmap2, F2r, d.C, d.N2(),
+                                                                                               1.f);
+  if (aux != nullptr) {  // mean rows from the transposed copy (already rounded: the means differ by < 2^-12 relative)
+    const dim3 grid(d.H2 + d.W2, d.B);
+    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2r, aux, d.H2, d.W2, d.C);
+  }
+  return cudaGetLastError();
+}
+
 cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
                            int* status, cudaStream_t stream) {
   cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), stream);

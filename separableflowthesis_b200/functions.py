@@ -219,12 +219,15 @@ class SeparationCompressionCF(Function):
 # the concatenated tensors of core/corr.py:454-457 directly.  The backward is one call as well.
 class SeparationLevelFunction(Function):
     @staticmethod
-    def forward(ctx, img1_features_l0, img2_features_lk, weight_u, bias_u, weight_v, bias_v, with_argmax):
+    def forward(ctx, img1_features_l0, img2_features_lk, weight_u, bias_u, weight_v, bias_v, with_argmax,
+                fmaps=False, scale1=1.0):
+        """With ``fmaps`` the features are the model's maps (B,C,H,W) and ``scale1`` multiplies image 1's."""
         assert img1_features_l0.is_contiguous() and img2_features_lk.is_contiguous()
+        ctx.fmaps, ctx.scale1 = fmaps, scale1
         with torch.cuda.device_of(img1_features_l0):
             sep_u, sep_v, am_u, am_v, a_u, a_v = MemorySaver.separation_level_forward(
                 img1_features_l0, img2_features_lk, weight_u.contiguous(), bias_u.contiguous(),
-                weight_v.contiguous(), bias_v.contiguous(), with_argmax)
+                weight_v.contiguous(), bias_v.contiguous(), with_argmax, fmaps, scale1)
         if with_argmax:
             ctx.save_for_backward(img1_features_l0, img2_features_lk, weight_u, weight_v, sep_u, sep_v, am_u, am_v,
                                   a_u, a_v)
@@ -240,5 +243,5 @@ class SeparationLevelFunction(Function):
         with torch.cuda.device_of(grad_sep_u):
             g1, g2, gw_u, gb_u, gw_v, gb_v = MemorySaver.separation_level_backward(
                 f1, f2, weight_u.contiguous(), weight_v.contiguous(), sep_u, sep_v, am_u, am_v, a_u, a_v,
-                grad_sep_u.contiguous(), grad_sep_v.contiguous())
-        return g1, g2, gw_u, gb_u, gw_v, gb_v, None
+                grad_sep_u.contiguous(), grad_sep_v.contiguous(), ctx.fmaps, ctx.scale1)
+        return g1, g2, gw_u, gb_u, gw_v, gb_v, None, None, None

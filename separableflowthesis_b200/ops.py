@@ -60,6 +60,8 @@ def _workspace(nbytes: int, device: torch.device, stream: int) -> torch.Tensor:
 
 
 def _ptr(t):
+    if isinstance(t, float):
+        return ctypes.c_float(t)
     return ctypes.c_void_p(t.data_ptr() if t is not None else None)
 
 
@@ -361,13 +363,28 @@ def attention_backward(x, weight, a, grad_a, add=None) -> List[torch.Tensor]:
     return [gx, gw, gb]
 
 
+def _check_fmaps(fmap1: torch.Tensor, fmap2: torch.Tensor) -> _lib.SfbShape:
+    """The model's feature maps (B, C, H, W), as core/corr.py:340-382 holds them."""
+    _check(fmap1, "fmap1", torch.float32, 4)
+    _check(fmap2, "fmap2", torch.float32, 4)
+    if fmap1.device != fmap2.device:
+        raise RuntimeError("fmap1 and fmap2 must be on the same device")
+    if fmap1.shape[0] != fmap2.shape[0] or fmap1.shape[1] != fmap2.shape[1]:
+        raise RuntimeError(f"batch / feature dimensions differ: {tuple(fmap1.shape)} vs {tuple(fmap2.shape)}")
+    B, C, H1, W1 = fmap1.shape
+    _, _, H2, W2 = fmap2.shape
+    return _lib.SfbShape(B, H1, W1, H2, W2, C, 0)
+
+
 def separation_level_forward(img1_features_l0, img2_features_lk, weight_u, bias_u, weight_v, bias_v,
-                             with_argmax=True) -> List[torch.Tensor]:
+                             with_argmax=True, fmaps=False, scale1=1.0) -> List[torch.Tensor]:
     """One pyramid level of the call site (core/corr.py:419-457 up to the upsampling):
     [sep_u (B,2+Kc,W2,H1,W1), sep_v (B,2+Kc,H2,H1,W1), am_u, am_v, a_u (B,Kc,W2,H1,W1), a_v (B,Kc,H2,H1,W1)];
-    (weight_u, bias_u) are the parameters of the reference's ``attention1``, which acts on sep_u."""
+    (weight_u, bias_u) are the parameters of the reference's ``attention1``, which acts on sep_u.
+    With ``fmaps`` the two feature arguments are the model's maps (B,C,H,W) and image 1's is multiplied by
+    ``scale1`` inside the library (the permute + division of core/corr.py:419-422)."""
     F1, F2 = img1_features_l0, img2_features_lk
-    s = _check_pair(F1, F2)
+    s = _check_fmaps(F1, F2) if fmaps else _check_pair(F1, F2)
     dev = F1.device
     s.Kc = _check_attention_params(weight_u, bias_u, "attention1", dev)
     if _check_attention_params(weight_v, bias_v, "attention2", dev) != s.Kc:
@@ -379,16 +396,21 @@ def separation_level_forward(img1_features_l0, img2_features_lk, weight_u, bias_
     am_v = torch.empty(s.B, s.W2, s.H1, s.W1, dtype=torch.int32, device=dev) if with_argmax else None
     a_u = torch.empty(s.B, s.Kc, s.W2, s.H1, s.W1, **f32)
     a_v = torch.empty(s.B, s.Kc, s.H2, s.H1, s.W1, **f32)
-    _call("sfb_separation_level_forward", _lib.OP_SEPARATION_LEVEL_FORWARD, s, dev,
-          (F1, F2, weight_u, bias_u, weight_v, bias_v, sep_u, sep_v, am_u, am_v, a_u, a_v))
+    if fmaps:
+        _call("sfb_separation_level_forward_fmaps", _lib.OP_SEPARATION_LEVEL_FORWARD, s, dev,
+              (F1, F2, float(scale1), weight_u, bias_u, weight_v, bias_v, sep_u, sep_v, am_u, am_v, a_u, a_v))
+    else:
+        _call("sfb_separation_level_forward", _lib.OP_SEPARATION_LEVEL_FORWARD, s, dev,
+              (F1, F2, weight_u, bias_u, weight_v, bias_v, sep_u, sep_v, am_u, am_v, a_u, a_v))
     return [sep_u, sep_v, am_u, am_v, a_u, a_v]
 
 
 def separation_level_backward(img1_features_l0, img2_features_lk, weight_u, weight_v, sep_u, sep_v, am_u, am_v,
-                              a_u, a_v, g_sep_u, g_sep_v) -> List[torch.Tensor]:
-    """[gF1, gF2, gweight_u, gbias_u, gweight_v, gbias_v] of ``separation_level_forward``."""
+                              a_u, a_v, g_sep_u, g_sep_v, fmaps=False, scale1=1.0) -> List[torch.Tensor]:
+    """[gF1, gF2, gweight_u, gbias_u, gweight_v, gbias_v] of ``separation_level_forward`` (feature gradients in the
+    layout of the feature arguments)."""
     F1, F2 = img1_features_l0, img2_features_lk
-    s = _check_pair(F1, F2)
+    s = _check_fmaps(F1, F2) if fmaps else _check_pair(F1, F2)
     dev = F1.device
     _check_attention_cf(s, a_u, a_v, dev)
     _check_like(weight_u, "attention1.weight", (s.Kc, 2, 3, 3, 3), torch.float32, dev)
@@ -403,9 +425,11 @@ def separation_level_backward(img1_features_l0, img2_features_lk, weight_u, weig
     gw_u, gw_v = torch.empty_like(weight_u), torch.empty_like(weight_v)
     gb_u = torch.empty(s.Kc, dtype=torch.float32, device=dev)
     gb_v = torch.empty(s.Kc, dtype=torch.float32, device=dev)
-    _call("sfb_separation_level_backward", _lib.OP_SEPARATION_LEVEL_BACKWARD, s, dev,
-          (F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u, g_sep_v, gF1, gF2, gw_u, gb_u,
-           gw_v, gb_v))
+    name = "sfb_separation_level_backward_fmaps" if fmaps else "sfb_separation_level_backward"
+    head = (F1, F2, float(scale1)) if fmaps else (F1, F2)
+    _call(name, _lib.OP_SEPARATION_LEVEL_BACKWARD, s, dev,
+          head + (weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u, g_sep_v, gF1, gF2, gw_u, gb_u,
+                  gw_v, gb_v))
     return [gF1, gF2, gw_u, gb_u, gw_v, gb_v]
 
 

@@ -268,6 +268,21 @@ def test_separation_level(shape, cuda_device):
                                           g_sep_v.to(dev))
     for x, y in zip(out, again):
         assert torch.equal(x, y)
+    # the same level from the model's (B,C,H,W) feature maps, scale applied inside (core/corr.py:419-422)
+    scale = 1.0 / C ** 0.5
+    fmap1 = (F1 * C ** 0.5).permute(0, 3, 1, 2).contiguous()
+    fmap2 = F2.permute(0, 3, 1, 2).contiguous()
+    fw = ops.separation_level_forward(fmap1.to(dev), fmap2.to(dev), wu, bu, wv, bv, fmaps=True, scale1=scale)
+    assert relerr(fw[0], ref[0]) < 2 * TOL and relerr(fw[1], ref[1]) < 2 * TOL
+    outm = ops.separation_level_backward(fmap1.to(dev), fmap2.to(dev), wu, wv, *fw, g_sep_u.to(dev), g_sep_v.to(dev),
+                                         fmaps=True, scale1=scale)
+    rm = orc.separation_level_backward(fmap1.double(), fmap2.double(), params[0].double(), params[2].double(),
+                                       fw[0].double().cpu(), fw[1].double().cpu(), fw[2].cpu(), fw[3].cpu(),
+                                       fw[4].double().cpu(), fw[5].double().cpu(), g_sep_u.double(), g_sep_v.double(),
+                                       fmaps=True, scale1=scale)
+    assert outm[0].shape == fmap1.shape and outm[1].shape == fmap2.shape
+    assert relerr(outm[0], rm[0]) < TOL and relerr(outm[1], rm[1]) < TOL
+    assert relerr(outm[2], rm[2]) < TOL and relerr(outm[4], rm[4]) < TOL
 
 
 def test_ops_from_a_fresh_thread(cuda_device):
