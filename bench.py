@@ -206,9 +206,11 @@ class E2E:
     AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
     gradients -> loss-sized results back on the host."""
 
-    def __init__(self, cfg, job, device):
+    def __init__(self, cfg, job, device, chunks=1):
         import separableflowthesis_b200 as sfb
         self.sfb, self.cfg, self.device = sfb, cfg, device
+        self.chunks = chunks
+        self.copy_stream = torch.cuda.Stream(device=device)
         self.h1 = job["f1_nchw"].pin_memory()
         self.h2 = job["f2_nchw"].pin_memory()
         self.att = None
@@ -227,35 +229,56 @@ class E2E:
         self.d2h = 0
 
     def step(self):
+        """One step: this step's features host -> device, separation forward + backward, results -> host.  The batch
+        is processed as `self.chunks` micro-batches through the same public call; the copy of micro-batch i+1 runs on
+        a second stream while micro-batch i computes (gradients of the shared attention parameters accumulate
+        across micro-batches as autograd does for any repeated use)."""
         cfg, dev = self.cfg, self.device
-        f1 = self.h1.to(dev, non_blocking=True)
-        f2 = self.h2.to(dev, non_blocking=True)
+        n = self.h1.shape[0]
+        chunks = max(1, min(self.chunks, n))
+        bounds = [(i * n // chunks, (i + 1) * n // chunks) for i in range(chunks)]
+        main = torch.cuda.current_stream()
+        staged = []
+        with torch.cuda.stream(self.copy_stream):
+            for b0, b1 in bounds:
+                f1 = self.h1[b0:b1].to(dev, non_blocking=True)
+                f2 = self.h2[b0:b1].to(dev, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.copy_stream)
+                staged.append((f1, f2, ev))
+        params = [p for c in (self.att or []) for p in c.parameters()]
+        for p in params:
+            p.grad = None
+        pieces, keep = [], []
+        for (b0, b1), (f1, f2, ev) in zip(bounds, staged):
+            main.wait_event(ev)
+            if cfg["bwd"]:
+                f1.requires_grad_(True)
+                f2.requires_grad_(True)
+            blk = self.sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=1, support_backward=cfg["bwd"])
+            with torch.set_grad_enabled(cfg["bwd"]):
+                sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(self.att) if self.att else None)
+            if cfg["bwd"]:
+                if self.up is None:
+                    gd = torch.Generator(device=dev).manual_seed(SEED + 7)
+                    shape_u = (n,) + tuple(sep_u.shape[1:])
+                    shape_v = (n,) + tuple(sep_v.shape[1:])
+                    self.up = (torch.randn(shape_u, generator=gd, device=dev),
+                               torch.randn(shape_v, generator=gd, device=dev))
+                torch.autograd.backward([sep_u, sep_v], [self.up[0][b0:b1], self.up[1][b0:b1]])
+                pieces += [f1.grad.sum().reshape(1), f2.grad.sum().reshape(1)]
+            else:
+                pieces += [sep_u.sum().reshape(1), sep_v.sum().reshape(1)]
+            keep.append((f1, f2))
         if cfg["bwd"]:
-            f1.requires_grad_(True)
-            f2.requires_grad_(True)
-        blk = self.sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=1, support_backward=cfg["bwd"])
-        with torch.set_grad_enabled(cfg["bwd"]):
-            sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(self.att) if self.att else None)
-        if cfg["bwd"]:
-            if self.up is None:
-                gd = torch.Generator(device=dev).manual_seed(SEED + 7)
-                self.up = (torch.randn(sep_u.shape, generator=gd, device=dev),
-                           torch.randn(sep_v.shape, generator=gd, device=dev))
-            params = [p for c in (self.att or []) for p in c.parameters()]
-            for p in params:
-                p.grad = None
-            torch.autograd.backward([sep_u, sep_v], list(self.up))
             from separableflowthesis_b200 import sharding
             flat = sharding.reduce_parameter_grads(params)  # NCCL all-reduce when world_size > 1
-            pieces = [f1.grad.sum().reshape(1), f2.grad.sum().reshape(1)]
             if flat is not None:
                 pieces.append(flat[:1000])
-            res = torch.cat(pieces)
-        else:
-            res = torch.stack((sep_u.sum(), sep_v.sum()))
+        res = torch.cat(pieces)
         self.host_out[:res.numel()].copy_(res, non_blocking=True)
         self.d2h = res.numel() * 4
-        torch.cuda.current_stream().synchronize()
+        main.synchronize()
         return float(self.host_out[0])
 
 
@@ -366,6 +389,9 @@ def main():
                     help="level: one library call per pyramid-level forward / backward, as the call site runs it "
                          "(attention Conv3d + softmax included); ops: the five ops of the reference's module with "
                          "random attention weights; auto: level when the config has attention channels")
+    ap.add_argument("--e2e-chunks", type=int, default=2,
+                    help="micro-batches per end-to-end step (the host->device copy of one overlaps the compute of the "
+                         "previous one); 1 = copy everything, then compute")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small ncu captures)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
@@ -481,7 +507,7 @@ def main():
     # ---- end to end through the public API with host buffers ----
     e2e = None
     if not args.no_e2e:
-        runner = E2E(cfg, job, device)
+        runner = E2E(cfg, job, device, chunks=args.e2e_chunks)
         for _ in range(min(args.warmup, 3)):
             runner.step()
         barrier()
@@ -496,7 +522,8 @@ def main():
                "h2d_bytes_per_step": int(sum_over_ranks(float(runner.h2d))),
                "d2h_bytes_per_step": int(sum_over_ranks(float(runner.d2h))),
                "path": "pinned host f1,f2 (B,C,H,W) -> AlternateCorrBlockSepflow(num_levels=1).separate with "
-                       "Conv3d attention -> autograd backward -> all-reduce of attention-parameter grads -> host"}
+                       "Conv3d attention -> autograd backward -> all-reduce of attention-parameter grads -> host; "
+                       f"{runner.chunks} micro-batch(es) per step, copy of one overlapping compute of the previous"}
         del runner
 
     cpu = None
