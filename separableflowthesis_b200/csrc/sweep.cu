@@ -6,8 +6,9 @@
 // columns = 256 accumulator columns), column-blocks outermost.  Warp roles:
 //   warp 0      TMA producer: F1 tile once (stays resident), F2 tiles through a ring of stages
 //   warp 1      allocates TMEM, issues tcgen05.mma (TF32 in, FP32 accumulate), 2 accumulators in flight
-//   warps 2..9  two epilogue warpgroups; in each, one thread per image-1 pixel reads its accumulator
-//               lane with tcgen05.ld.  Both groups consume every tile and split its work.
+//   warps 2..   epilogue warpgroups (two, or four for the compression epilogue); in each, one thread per
+//               image-1 pixel reads its accumulator lane with tcgen05.ld.  All groups consume every tile and
+//               split its work.
 // Everything indexed by an image-1 pixel is read and written in the packed, pixel-fastest layout
 // (kernels.h), so a warp's 32 lanes touch one 128-byte line per access.
 // Epilogues
@@ -16,9 +17,8 @@
 //                  once per column block), row-direction max(+argmax) merged through the packed output
 //                  once per tile.  The two mean channels come from extra tiles whose "image-2 pixels"
 //                  are the row-mean and column-mean feature rows of F2 (mean_v S[u,v] = F1 . mean_v F2[u,v]).
-//   compression  : group g takes channels g, g+2.  OU[k,u] = sum_v S*w_u[k,v] (reduced per tile,
-//                  accumulated with red.add), OV[k,v] = sum_u S*w_v[k,u] (register accumulators across
-//                  the inner loop).
+//   compression  : group g takes channel g.  OU[k,u] = sum_v S*w_u[k,v] (reduced per tile, accumulated
+//                  with red.add), OV[k,v] = sum_u S*w_v[k,u] (register accumulators across the inner loop).
 // Replaces the reference kernels MemorySaver_kernel_forward.cu:128-313, :328-533, :550-753.
 #include <math_constants.h>
 
@@ -31,8 +31,11 @@ constexpr int SW_NSTAGE = 3;                    // 3 x 32 KB of F2 blocks next t
 constexpr int SW_NACC = 2;                      // 2 x 256 TMEM columns
 constexpr int SW_TILE_N = SWEEP_UT * SWEEP_VT;  // 256 accumulator columns: tcgen05.mma issues at a fixed
                                                 // rate per instruction, so the widest N does the most work
-constexpr int SW_EPI_WARPS = 8;
-constexpr int SW_THREADS = 64 + SW_EPI_WARPS * 32;
+// Epilogue warps: two warpgroups for the max/avg and dump epilogues (each takes half of a tile's rows), four for
+// the compression epilogue (each takes one channel and reads the whole tile): its work per cell is 2 FMAs per
+// channel, and with 16 warps the FP32 pipes keep up with the tensor pipe.
+__host__ __device__ constexpr int sw_epi_warps(int mode) { return mode == SWEEP_COMPRESS ? 16 : 8; }
+__host__ __device__ constexpr int sw_threads(int mode) { return 64 + sw_epi_warps(mode) * 32; }
 constexpr int SW_RW = SWEEP_UT / 2;             // tile rows of one epilogue warpgroup
 constexpr int SW_NMERGE = 4;                    // ring of column-merge barriers (> SW_NACC tiles of run-ahead)
 constexpr uint32_t SW_STAGE_BYTES = SW_TILE_N * KBLK * 4;
@@ -280,51 +283,36 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
 }
 
 __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const EpiCtx& e) {
-  constexpr int KW = KC_MAX_PER_SWEEP / 2;  // channels of one warpgroup: local channels wg, wg + 2
   const int H2 = a.d.H2, W2 = a.d.W2;
-  const bool valid = e.valid;
+  const bool active = e.wg < a.kc;            // this warpgroup's channel exists (warp-uniform)
+  const bool valid = e.valid && active;
   const uint32_t xusd = a.xu.sd, xvsd = a.xv.sd, ousd = a.ou.sd, ovsd = a.ov.sd;
-  // this thread's pixel in sample b of each view; (displacement d, slot) at ptr[d*sd + slot*ss], 32-bit offsets
-  const float* xu = a.xu.base + sc.b * a.xu.sb + e.p;
-  const float* xv = a.xv.base + sc.b * a.xv.sb + e.p;
-  float* ou = a.ou.base + sc.b * a.ou.sb + e.p;
-  float* ov = a.ov.base + sc.b * a.ov.sb + e.p;
-  int nk = 0;
-  uint32_t wu_off[KW], wv_off[KW], ou_off[KW], ov_off[KW];  // slot offsets of this group's channels
-#pragma unroll
-  for (int j = 0; j < KW; ++j) {
-    const int kl = e.wg + 2 * j;
-    if (kl < a.kc) nk = j + 1;
-    wu_off[j] = (a.wu_slot0 + (a.k0 + kl) * a.w_stride) * a.xv.ss;
-    wv_off[j] = (a.wv_slot0 + (a.k0 + kl) * a.w_stride) * a.xu.ss;
-    ou_off[j] = (a.k0 + kl) * a.ou.ss;
-    ov_off[j] = (a.k0 + kl) * a.ov.ss;
-  }
+  // this thread's pixel and channel in sample b of each view; displacement d at ptr[d*sd], 32-bit offsets
+  const int k = a.k0 + e.wg;
+  const float* wu = a.xv.base + sc.b * a.xv.sb + e.p + (a.wu_slot0 + k * a.w_stride) * a.xv.ss;  // w_u[k][v]
+  const float* wv = a.xu.base + sc.b * a.xu.sb + e.p + (a.wv_slot0 + k * a.w_stride) * a.xu.ss;  // w_v[k][u]
+  float* ou = a.ou.base + sc.b * a.ou.sb + e.p + k * a.ou.ss;
+  float* ov = a.ov.base + sc.b * a.ov.sb + e.p + k * a.ov.ss;
 
-  float au[KW][SWEEP_VT], cv[KW][SWEEP_VT];
+  float au[SWEEP_VT], cv[SWEEP_VT];
   int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_main; ++t) {
     const int v0 = vb * SWEEP_VT, u0 = ub * SWEEP_UT;
     const int nu = min(SWEEP_UT, H2 - u0), nv = min(SWEEP_VT, W2 - v0);
     if (ub == 0) {
 #pragma unroll
-      for (int j = 0; j < KW; ++j)
-#pragma unroll
-        for (int i = 0; i < SWEEP_VT; ++i) {
-          au[j][i] = (valid && j < nk && i < nv) ? __ldg(xv + ((v0 + i) * xvsd + wu_off[j])) : 0.f;
-          cv[j][i] = 0.f;
-        }
+      for (int i = 0; i < SWEEP_VT; ++i) {
+        au[i] = (valid && i < nv) ? __ldg(wu + (v0 + i) * xvsd) : 0.f;
+        cv[i] = 0.f;
+      }
     }
-    float av[KW][SWEEP_UT];
+    float av[SWEEP_UT];
 #pragma unroll
-    for (int j = 0; j < KW; ++j)
-#pragma unroll
-      for (int ul = 0; ul < SWEEP_UT; ++ul)
-        av[j][ul] = (valid && j < nk && ul < nu) ? __ldg(xu + ((u0 + ul) * xusd + wv_off[j])) : 0.f;
+    for (int ul = 0; ul < SWEEP_UT; ++ul) av[ul] = (valid && ul < nu) ? __ldg(wv + (u0 + ul) * xusd) : 0.f;
 
     if (!epi_wait(sm, a, t)) return;
     const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N;
-    if (nk > 0) {
+    if (active) {
 #pragma unroll
       for (int pr = 0; pr < SWEEP_UT / 2; ++pr) {
         if (2 * pr < nu) {  // warp-uniform; padded cells hold S = 0 (zero-filled F2 rows) and weight 0
@@ -335,19 +323,16 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
           for (int h = 0; h < 2; ++h) {
             const int ul = 2 * pr + h;
             if (ul < nu) {
+              float r = 0.f;
 #pragma unroll
-              for (int j = 0; j < KW; ++j) {
-                float r = 0.f;
-#pragma unroll
-                for (int i = 0; i < SWEEP_VT; ++i) {
-                  r = fmaf(s[h * SWEEP_VT + i], au[j][i], r);
-                  cv[j][i] = fmaf(s[h * SWEEP_VT + i], av[j][ul], cv[j][i]);
-                }
-                if (valid && j < nk) {
-                  float* dst = ou + ((u0 + ul) * ousd + ou_off[j]);
-                  if (vb == 0) *dst = r;     // first column block initialises the output
-                  else atomicAdd(dst, r);    // later blocks accumulate (same thread, same address: ordered)
-                }
+              for (int i = 0; i < SWEEP_VT; ++i) {
+                r = fmaf(s[h * SWEEP_VT + i], au[i], r);
+                cv[i] = fmaf(s[h * SWEEP_VT + i], av[ul], cv[i]);
+              }
+              if (valid) {
+                float* dst = ou + (u0 + ul) * ousd;
+                if (vb == 0) *dst = r;     // first column block initialises the output
+                else atomicAdd(dst, r);    // later blocks accumulate (same thread, same address: ordered)
               }
             }
           }
@@ -358,10 +343,8 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
     }
     if (ub == sc.n_ub - 1) {
 #pragma unroll
-      for (int j = 0; j < KW; ++j)
-#pragma unroll
-        for (int i = 0; i < SWEEP_VT; ++i)
-          if (valid && j < nk && i < nv) ov[(v0 + i) * ovsd + ov_off[j]] = cv[j][i];
+      for (int i = 0; i < SWEEP_VT; ++i)
+        if (valid && i < nv) ov[(v0 + i) * ovsd] = cv[i];
     }
     if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
@@ -399,7 +382,7 @@ __device__ void epilogue_dump(SweepSmem& sm, const SweepArgs& a, const SweepSche
 
 // ---------------------------------------------------------------------------------- kernel
 template <int MODE>
-__global__ void __launch_bounds__(SW_THREADS, 1)
+__global__ void __launch_bounds__(sw_threads(MODE), 1)
 sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ CUtensorMap tm_f2,
              const __grid_constant__ CUtensorMap tm_aux, const SweepArgs a) {
   if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier CTA gave up: do not pile on
@@ -424,8 +407,8 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
   if (threadIdx.x == 0) {
     mbar_init(&sm.f1_full, 1);
     for (int s = 0; s < SW_NSTAGE; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    for (int i = 0; i < SW_NACC; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], SW_EPI_WARPS); }
-    for (int i = 0; i < SW_NMERGE; ++i) mbar_init(&sm.merge[i], SW_EPI_WARPS / 2);
+    for (int i = 0; i < SW_NACC; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], sw_epi_warps(MODE)); }
+    for (int i = 0; i < SW_NMERGE; ++i) mbar_init(&sm.merge[i], 4);  // the four warps of max/avg group 1
     sm.abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tm_f1);
@@ -482,7 +465,7 @@ static cudaError_t launch_one(const SweepArgs& a, const CUtensorMap& tm_f1, cons
   if (err != cudaSuccess) return err;
   const int tiles_per_sample = (a.d.N1() + TILE_M - 1) / TILE_M;
   const dim3 grid(a.d.B * tiles_per_sample);
-  kern<<<grid, SW_THREADS, SW_SMEM_BYTES, stream>>>(tm_f1, tm_f2, tm_aux, a);
+  kern<<<grid, sw_threads(MODE), SW_SMEM_BYTES, stream>>>(tm_f1, tm_f2, tm_aux, a);
   return cudaGetLastError();
 }
 
