@@ -138,32 +138,46 @@ cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, i
 }
 
 // Channels-first sources are already pixel-fastest: one thread per pixel gathers the four slots of a group
-// and stores them as one 16-byte word.  grid (n1p/256, D, B), block 256.
+// and stores them as one 16-byte word, for PI_DB displacements at a time (all loads issued before the stores,
+// so that a thread keeps 4*Q*PI_DB loads in flight).  grid (n1p/256, ceil(D/PI_DB), B), block 256.
+constexpr int PI_DB = 4;
+
 template <int Q>
 __global__ void pack_interleaved_cf_kernel(const SlotSources src, float4* __restrict__ dst, int N1, int n1p, int D,
                                            int Qtot, int q0) {
-  const int p = blockIdx.x * 256 + threadIdx.x, d = blockIdx.y, b = blockIdx.z;
+  const int p = blockIdx.x * 256 + threadIdx.x, d0 = blockIdx.y * PI_DB, b = blockIdx.z;
   if (p >= n1p) return;
+  uint32_t w[PI_DB][Q][4];
 #pragma unroll
-  for (int q = 0; q < Q; ++q) {
-    float v[4];
+  for (int i = 0; i < PI_DB; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const SlotSource& ss = src.s[4 * q + j];
-      uint32_t w = 0;
-      if (ss.src != nullptr && p < N1) {
-        w = __ldg(static_cast<const uint32_t*>(ss.src) + (((size_t)b * ss.Ksrc + ss.k) * D + d) * N1 + p);
-        if (ss.scale != 0.f) w = __float_as_uint(__uint_as_float(w) * ss.scale);
+    for (int q = 0; q < Q; ++q)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const SlotSource& ss = src.s[4 * q + j];
+        w[i][q][j] = 0;
+        if (ss.src != nullptr && p < N1 && d0 + i < D)
+          w[i][q][j] = __ldg(static_cast<const uint32_t*>(ss.src) + (((size_t)b * ss.Ksrc + ss.k) * D + d0 + i) * N1 + p);
       }
-      v[j] = __uint_as_float(w);
+#pragma unroll
+  for (int i = 0; i < PI_DB; ++i) {
+    if (d0 + i >= D) break;
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float scale = src.s[4 * q + j].scale;
+        v[j] = scale != 0.f ? __uint_as_float(w[i][q][j]) * scale : __uint_as_float(w[i][q][j]);
+      }
+      dst[(((size_t)b * D + d0 + i) * Qtot + q0 + q) * n1p + p] = make_float4(v[0], v[1], v[2], v[3]);
     }
-    dst[(((size_t)b * D + d) * Qtot + q0 + q) * n1p + p] = make_float4(v[0], v[1], v[2], v[3]);
   }
 }
 
 cudaError_t launch_pack_interleaved_cf(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
                                        int Qtot, int q0, cudaStream_t stream) {
-  const dim3 grid((n1p + 255) / 256, D, B);
+  const dim3 grid((n1p + 255) / 256, (D + PI_DB - 1) / PI_DB, B);
   float4* out = reinterpret_cast<float4*>(dst);
   if (R4 == 4) pack_interleaved_cf_kernel<1><<<grid, 256, 0, stream>>>(src, out, N1, n1p, D, Qtot, q0);
   else if (R4 == 8) pack_interleaved_cf_kernel<2><<<grid, 256, 0, stream>>>(src, out, N1, n1p, D, Qtot, q0);
