@@ -209,6 +209,29 @@ int sfb_separation_level_backward_fmaps(const float* fmap1, const float* fmap2, 
                                         const sfb_shape* shape, void* workspace, size_t workspace_bytes,
                                         void* stream);
 
+/* Lookup on an aggregated 3D cost volume: the reference's CorrBlock1D (core/corr.py:513-624) for ONE of its two
+ * volumes.  corr (B,dim,D,H1,W1) is the volume as the model holds it (core/sepflow.py:184-187); the pyramid over
+ * the displacement axis (core/corr.py:543-548; levels 1..levels-1, level l = (B,dim,D>>l,H1,W1), back to back,
+ * sfb_lookup_pyramid_bytes() bytes) is built once per volume; every refinement iteration then samples
+ * 2*radius+1 linearly interpolated values per level around coord/2^l (core/corr.py:576-594):
+ *   out (B, levels*dim*(2*radius+1), H1, W1), channel (l*dim + ch)*(2*radius+1) + tap.
+ * coord (B,H1,W1) is one component of the model's coordinate tensor, `coord_batch_stride` elements between samples
+ * (for coords (B,2,H1,W1): component pointer, stride 2*H1*W1).  clamp_unit != 0 clamps every sampling position to
+ * [-1, 1] first, which is what the reference does for its first volume (core/corr.py:586).
+ * 1 <= levels <= 8.  FP32 arithmetic. */
+size_t sfb_lookup_pyramid_bytes(int32_t B, int32_t dim, int32_t D, int32_t H1, int32_t W1, int32_t levels);
+int sfb_lookup_build_pyramid(const float* corr, float* pyramid, int32_t B, int32_t dim, int32_t D, int32_t H1,
+                             int32_t W1, int32_t levels, void* stream);
+int sfb_lookup_forward(const float* corr, const float* pyramid, const float* coord, int64_t coord_batch_stride,
+                       float* out, int32_t B, int32_t dim, int32_t D, int32_t H1, int32_t W1, int32_t levels,
+                       int32_t radius, int32_t clamp_unit, void* stream);
+/* Gradient of the volume for upstream gradient gout (shape of out): gcorr (B,dim,D,H1,W1) is overwritten; gpyramid
+ * (size of the pyramid) is scratch.  No atomics: bit-reproducible.  (No gradient for coord: the model detaches it,
+ * core/sepflow.py:192.) */
+int sfb_lookup_backward(const float* gout, const float* coord, int64_t coord_batch_stride, float* gcorr,
+                        float* gpyramid, int32_t B, int32_t dim, int32_t D, int32_t H1, int32_t W1, int32_t levels,
+                        int32_t radius, int32_t clamp_unit, void* stream);
+
 /* Test aid with no counterpart in the reference ops: writes the dense volume S (B,H1,W1,H2,W2) of a
  * SMALL problem through the same tensor-core pipeline (the reference builds it with torch.matmul,
  * core/corr.py:286-289). */

@@ -297,6 +297,50 @@ def separation_level_backward(F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am
     return [gF1, gF2, gw_u, gb_u, gw_v, gb_v]
 
 
+# Lookup on the aggregated 3D volumes: the reference's CorrBlock1D (core/corr.py:513-624), one volume at a time.
+def lookup_pyramid(corr, levels):
+    """Levels 0 .. levels-1 of the displacement pyramid of corr (B,dim,D,H1,W1): average pooling by two along the
+    displacement axis (core/corr.py:543-548; the reference builds one level more than it reads)."""
+    pyr = [corr]
+    for _ in range(levels - 1):
+        B, dim, D, H1, W1 = pyr[-1].shape
+        x = pyr[-1].permute(0, 3, 4, 1, 2).reshape(B * H1 * W1, dim, 1, D)
+        x = torch.nn.functional.avg_pool2d(x, [1, 2], stride=[1, 2])
+        pyr.append(x.reshape(B, H1, W1, dim, D // 2).permute(0, 3, 4, 1, 2).contiguous())
+    return pyr
+
+
+def lookup_forward(corr, coord, levels=4, radius=4, clamp_unit=False):
+    """out (B, levels*dim*(2r+1), H1, W1) for one volume corr (B,dim,D,H1,W1) and one coordinate component coord
+    (B,H1,W1), with the reference's own chain of operations (core/corr.py:550-594): positions coord/2^l + dx, the
+    clamp to [-1,1] the reference applies to its first volume (core/corr.py:586), grid_sample with
+    align_corners=True."""
+    B, dim, D, H1, W1 = corr.shape
+    outs = []
+    for l, vol in enumerate(lookup_pyramid(corr, levels)):
+        Dl = vol.shape[2]
+        img = vol.permute(0, 3, 4, 1, 2).reshape(B * H1 * W1, dim, 1, Dl)
+        dx = torch.linspace(-radius, radius, 2 * radius + 1, dtype=corr.dtype, device=corr.device).view(1, 1, -1, 1)
+        x0 = dx + coord.reshape(B * H1 * W1, 1, 1, 1) / 2 ** l
+        y0 = torch.zeros_like(x0)
+        pos = torch.cat([x0, y0], dim=-1)
+        if clamp_unit:
+            pos = torch.clamp(pos, -1, 1)
+        xgrid, ygrid = pos.split([1, 1], dim=-1)
+        xgrid = 2 * xgrid / (Dl - 1) - 1
+        smp = torch.nn.functional.grid_sample(img, torch.cat([xgrid, ygrid], dim=-1), align_corners=True)
+        outs.append(smp.view(B, H1, W1, -1))
+    return torch.cat(outs, dim=-1).permute(0, 3, 1, 2).contiguous()
+
+
+def lookup_backward(corr_shape, coord, gout, levels=4, radius=4, clamp_unit=False):
+    """Gradient of the volume for upstream gradient gout (the lookup is linear in the volume)."""
+    with torch.enable_grad():
+        corr = torch.zeros(corr_shape, dtype=gout.dtype, device=gout.device, requires_grad=True)
+        lookup_forward(corr, coord, levels, radius, clamp_unit).backward(gout)
+    return corr.grad
+
+
 def top2_margins(F1: torch.Tensor, F2: torch.Tensor):
     """Gap between the largest and second-largest entry of S along v (per (p,u)) and
     along u (per (p,v)), computed in float64.  An argmax is required to be bit-exact only

@@ -13,9 +13,9 @@ from .functions import (  # noqa: F401
     ComputeSelfCompressionFunction,
 )
 from .modules import ComputeMaxAvgModule  # noqa: F401
-from .corr import AlternateCorrBlockSepflow  # noqa: F401
+from .corr import AlternateCorrBlockSepflow, CorrBlock1D  # noqa: F401
 
 __all__ = [
     "MemorySaver", "ComputeMaxAvgFunction", "ComputeMaxArgmaxAvgFunction",
-    "ComputeSelfCompressionFunction", "ComputeMaxAvgModule", "AlternateCorrBlockSepflow",
+    "ComputeSelfCompressionFunction", "ComputeMaxAvgModule", "AlternateCorrBlockSepflow", "CorrBlock1D",
 ]

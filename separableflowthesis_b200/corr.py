@@ -24,7 +24,8 @@ import torch.nn.functional as F
 
 from .functions import (ComputeMaxArgmaxAvgFunction, ComputeMaxAvgFunction, ComputeSelfCompressionFunction,
                         FusedMaxArgmaxAvgFunction, FusedSelfCompressionFunction, SeparationCompressionCF,
-                        SeparationLevelFunction, SeparationMaxAvgCF, SeparationState)
+                        LookupFunction, SeparationLevelFunction, SeparationMaxAvgCF, SeparationState)
+from . import ops as _ops
 
 
 def _is_standard_attention(m) -> bool:
@@ -125,3 +126,31 @@ class AlternateCorrBlockSepflow:
         if sep:
             return self.separate(attention_weights)
         raise NotImplementedError("Missing the cpp/cuda part for lookup of the 4d correlation volume without storing it")
+
+
+class CorrBlock1D:
+    """Lookup on the two aggregated 3D cost volumes: a drop-in for ``CorrBlock1D`` of the reference
+    (core/corr.py:513-624).  corr1 (B,dim,W2,H1,W1) is read with the x component of the coordinates, corr2
+    (B,dim,H2,H1,W1) with the y component; each call returns (out1, out2) of shape (B, levels*dim*(2r+1), H1, W1).
+
+    The volumes stay in the layout they arrive in (the reference permutes and reshapes them to one row per pixel,
+    core/corr.py:531-541); their displacement pyramids are built once, here.  As in the reference, the sampling
+    positions of the FIRST volume are clamped to [-1, 1] before the lookup (core/corr.py:586) and those of the second
+    are not; gradients flow to the volumes, not to the coordinates (the model detaches them, core/sepflow.py:192).
+    """
+
+    def __init__(self, corr1, corr2, num_levels=4, radius=4):
+        assert corr1.shape[:2] == corr2.shape[:2] and corr1.shape[3:] == corr2.shape[3:]
+        assert corr1.shape[2] == corr1.shape[4] and corr2.shape[2] == corr2.shape[3]  # h1 == h2 and w1 == w2
+        self.num_levels = num_levels
+        self.radius = radius
+        self.corr1 = corr1.contiguous()
+        self.corr2 = corr2.contiguous()
+        with torch.no_grad():
+            self.pyramid1 = _ops.lookup_build_pyramid(self.corr1, num_levels)
+            self.pyramid2 = _ops.lookup_build_pyramid(self.corr2, num_levels)
+
+    def __call__(self, coords):
+        out1 = LookupFunction.apply(self.corr1, self.pyramid1, coords[:, 0], self.num_levels, self.radius, True)
+        out2 = LookupFunction.apply(self.corr2, self.pyramid2, coords[:, 1], self.num_levels, self.radius, False)
+        return out1, out2

@@ -79,14 +79,15 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 enum KernelId : int {
   KID_PREPARE = 0, KID_PACK, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
   KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_GRAD_FUSED_IMG1, KID_GRAD_FUSED_IMG2, KID_ATTENTION_FWD,
-  KID_ATTENTION_BWD, KID_COUNT
+  KID_ATTENTION_BWD, KID_LOOKUP, KID_COUNT
 };
 const char* const kKernelNames[KID_COUNT] = {
     "prepare(round_copy+f2_means)", "pack_kernel/unpack_kernel", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
     "grad_gemm_kernel<maxavg,image1-major>", "grad_gemm_kernel<maxavg,image2-major>",
     "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>",
     "grad_gemm_kernel<fused,image1-major>", "grad_gemm_kernel<fused,image2-major>",
-    "attention_forward_kernel", "attention backward (logit, input, weight grads)"};
+    "attention_forward_kernel", "attention backward (logit, input, weight grads)",
+    "lookup kernels (pyramid, forward, backward)"};
 struct TimingRec { cudaEvent_t e0, e1; int id; int launches; };
 std::mutex g_timing_mu;
 bool g_timing_on = false;
@@ -989,6 +990,66 @@ int sfb_separation_level_backward_fmaps(const float* fmap1, const float* fmap2, 
                         stream);
 }
 
+
+// ---- lookup on the aggregated 3D volumes (CorrBlock1D) ----
+static int check_lookup_dims(int B, int dim, int D, int H1, int W1, int levels, int radius, LookupDims* ld) {
+  if (B < 1 || dim < 1 || D < 2 || H1 < 1 || W1 < 1)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "B, dim, H1, W1 must be >= 1 and D >= 2 (got %d %d %d %d %d)", B, dim, D, H1, W1);
+  if (levels < 1 || levels > LOOKUP_MAX_LEVELS || radius < 0 || radius > 64)
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "levels must be in [1, %d] and radius in [0, 64] (got %d, %d)",
+                LOOKUP_MAX_LEVELS, levels, radius);
+  if ((D >> (levels - 1)) < 2)
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "the coarsest level would have fewer than 2 displacements (D=%d, levels=%d)",
+                D, levels);
+  if ((long long)H1 * W1 > (1ll << 24)) return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image 1 has more than 2^24 pixels");
+  *ld = LookupDims{B, dim, D, H1, W1, levels, radius};
+  return SFB_OK;
+}
+
+size_t sfb_lookup_pyramid_bytes(int32_t B, int32_t dim, int32_t D, int32_t H1, int32_t W1, int32_t levels) {
+  LookupDims ld;
+  if (check_lookup_dims(B, dim, D, H1, W1, levels, 0, &ld) != SFB_OK) return 0;
+  return lookup_pyramid_floats(ld) * sizeof(float);
+}
+
+int sfb_lookup_build_pyramid(const float* corr, float* pyramid, int32_t B, int32_t dim, int32_t D, int32_t H1,
+                             int32_t W1, int32_t levels, void* stream) {
+  LookupDims ld;
+  SFB_TRY(check_lookup_dims(B, dim, D, H1, W1, levels, 0, &ld));
+  if (corr == nullptr || (levels > 1 && pyramid == nullptr))
+    return fail(SFB_ERR_INVALID_ARGUMENT, "corr and pyramid must not be NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_LOOKUP, levels - 1, st, [&] { return launch_lookup_pyramid(ld, corr, pyramid, st); }));
+  return SFB_OK;
+}
+
+int sfb_lookup_forward(const float* corr, const float* pyramid, const float* coord, int64_t coord_batch_stride,
+                       float* out, int32_t B, int32_t dim, int32_t D, int32_t H1, int32_t W1, int32_t levels,
+                       int32_t radius, int32_t clamp_unit, void* stream) {
+  LookupDims ld;
+  SFB_TRY(check_lookup_dims(B, dim, D, H1, W1, levels, radius, &ld));
+  if (corr == nullptr || (levels > 1 && pyramid == nullptr) || coord == nullptr || out == nullptr)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "corr, pyramid, coord and out must not be NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_LOOKUP, 1, st, [&] {
+    return launch_lookup_forward(ld, corr, pyramid, coord, coord_batch_stride, out, clamp_unit, st);
+  }));
+  return SFB_OK;
+}
+
+int sfb_lookup_backward(const float* gout, const float* coord, int64_t coord_batch_stride, float* gcorr,
+                        float* gpyramid, int32_t B, int32_t dim, int32_t D, int32_t H1, int32_t W1, int32_t levels,
+                        int32_t radius, int32_t clamp_unit, void* stream) {
+  LookupDims ld;
+  SFB_TRY(check_lookup_dims(B, dim, D, H1, W1, levels, radius, &ld));
+  if (gout == nullptr || coord == nullptr || gcorr == nullptr || (levels > 1 && gpyramid == nullptr))
+    return fail(SFB_ERR_INVALID_ARGUMENT, "gout, coord, gcorr and gpyramid must not be NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_LOOKUP, levels > 1 ? 2 : 1, st, [&] {
+    return launch_lookup_backward(ld, gout, coord, coord_batch_stride, gcorr, gpyramid, clamp_unit, st);
+  }));
+  return SFB_OK;
+}
 
 int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,
                     size_t workspace_bytes, void* stream) {

@@ -148,4 +148,21 @@ cudaError_t launch_attention_backward(const AttentionDims& d, const float* x, lo
                                       const float* a, float* g, const float* add, long long add_sb, float* gx,
                                       float* gweight, float* gbias, float* partial, cudaStream_t stream);
 
+
+// Lookup on an aggregated 3D cost volume (the reference's CorrBlock1D, core/corr.py:513-624).
+// corr (B, dim, D, H1, W1); pyramid = levels 1 .. levels-1 back to back, level l being (B, dim, D >> l, H1, W1);
+// coord: one displacement component per pixel, (B, H1, W1) with `coord_sb` elements between samples;
+// out (B, levels*dim*(2*radius+1), H1, W1).
+constexpr int LOOKUP_MAX_LEVELS = 8;
+struct LookupDims {
+  int B, dim, D, H1, W1, levels, radius;
+};
+size_t lookup_pyramid_floats(const LookupDims& d);
+cudaError_t launch_lookup_pyramid(const LookupDims& d, const float* corr, float* pyramid, cudaStream_t stream);
+cudaError_t launch_lookup_forward(const LookupDims& d, const float* corr, const float* pyramid, const float* coord,
+                                  long long coord_sb, float* out, int clamp_unit, cudaStream_t stream);
+// gcorr and gpyramid (same sizes as corr / pyramid) are overwritten; gpyramid is scratch.
+cudaError_t launch_lookup_backward(const LookupDims& d, const float* gout, const float* coord, long long coord_sb,
+                                   float* gcorr, float* gpyramid, int clamp_unit, cudaStream_t stream);
+
 }  // namespace sfb

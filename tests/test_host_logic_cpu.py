@@ -97,3 +97,35 @@ def test_fused_backward_without_feature_gradients(oracle_backend):
     for other in outs[1:]:
         for a, b in zip(outs[0], other):
             assert torch.allclose(a, b, atol=1e-12)
+
+
+def test_corrblock1d_host_logic(golden_dir, monkeypatch):
+    """CorrBlock1D drop-in (component slicing, clamp on the first volume only, pyramid reuse, autograd) with the
+    oracle in place of the CUDA ops, against the vectors of the reference's own class."""
+    from separableflowthesis_b200 import corr as corr_mod
+
+    class OracleOps:
+        @staticmethod
+        def lookup_build_pyramid(corr, levels):
+            return None
+
+        @staticmethod
+        def lookup_forward(corr, pyramid, coord, levels, radius, clamp_unit):
+            return orc.lookup_forward(corr, coord, levels, radius, clamp_unit)
+
+        @staticmethod
+        def lookup_backward(shape, coord, grad_out, levels, radius, clamp_unit):
+            return orc.lookup_backward(shape, coord, grad_out, levels, radius, clamp_unit)
+
+    monkeypatch.setattr(corr_mod, "_ops", OracleOps)
+    monkeypatch.setattr(functions, "MemorySaver", OracleOps)
+    g = np.load(os.path.join(golden_dir, "lookup1d_b1_dim2_16x24.npz"))
+    corr1 = _t(g["corr1"]).requires_grad_(True)
+    corr2 = _t(g["corr2"]).requires_grad_(True)
+    blk = sfb.CorrBlock1D(corr1, corr2, num_levels=int(g["levels"]), radius=int(g["radius"]))
+    out1, out2 = blk(_t(g["coords"]))
+    assert (out1 - _t(g["out1"]).double()).abs().max().item() < 1e-6
+    assert (out2 - _t(g["out2"]).double()).abs().max().item() < 1e-6
+    ((out1 * _t(g["w1"]).double()).sum() + (out2 * _t(g["w2"]).double()).sum()).backward()
+    assert (corr1.grad - _t(g["g_corr1"]).double()).abs().max().item() < 1e-6
+    assert (corr2.grad - _t(g["g_corr2"]).double()).abs().max().item() < 1e-6

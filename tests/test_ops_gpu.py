@@ -285,6 +285,55 @@ def test_separation_level(shape, cuda_device):
     assert relerr(outm[2], rm[2]) < TOL and relerr(outm[4], rm[4]) < TOL
 
 
+# positions pass through grid_sample's normalisation and back in float32, as in the reference's own float32 run:
+# position error ~ D * 2^-24, i.e. ~1.4e-5 of a displacement step at D = 240
+LOOKUP_TOL = 5e-5
+
+# (B, dim, D, H1, W1, levels, radius)
+LOOKUP_SHAPES = [(1, 1, 2, 1, 1, 1, 1), (2, 1, 16, 5, 7, 4, 4), (1, 3, 37, 9, 11, 3, 2), (2, 2, 240, 13, 37, 4, 4)]
+
+
+@pytest.mark.parametrize("shape", LOOKUP_SHAPES)
+@pytest.mark.parametrize("clamp", [False, True])
+def test_lookup_forward_backward(shape, clamp, cuda_device):
+    """Displacement pyramid + interpolated lookup of one aggregated volume and its backward against the oracle's
+    restatement of the reference's avg_pool2d / grid_sample chain (core/corr.py:543-594)."""
+    B, dim, D, H1, W1, levels, radius = shape
+    g = torch.Generator().manual_seed(31)
+    corr = torch.randn(B, dim, D, H1, W1, generator=g)
+    coords = torch.rand(B, 2, H1, W1, generator=g) * (D + 12) - 6     # inside, across and beyond the range
+    coords[0, 0].view(-1)[0] = 3.0                                     # an exact integer position
+    gout = torch.randn(B, levels * dim * (2 * radius + 1), H1, W1, generator=g)
+    dev = cuda_device
+    corr_d, coords_d = corr.to(dev), coords.to(dev)
+    pyr = ops.lookup_build_pyramid(corr_d, levels)
+    out = ops.lookup_forward(corr_d, pyr, coords_d[:, 0], levels, radius, clamp)
+    ref = orc.lookup_forward(corr.double(), coords[:, 0].double(), levels, radius, clamp)
+    assert out.shape == ref.shape and relerr(out, ref) < LOOKUP_TOL
+    gc = ops.lookup_backward(tuple(corr.shape), coords_d[:, 0], gout.to(dev), levels, radius, clamp)
+    rg = orc.lookup_backward(corr.shape, coords[:, 0].double(), gout.double(), levels, radius, clamp)
+    assert relerr(gc, rg) < LOOKUP_TOL
+    assert torch.equal(gc, ops.lookup_backward(tuple(corr.shape), coords_d[:, 0], gout.to(dev), levels, radius, clamp))
+
+
+def test_corrblock1d_against_reference_vectors(golden_dir, cuda_device):
+    """The CorrBlock1D drop-in (both volumes, autograd) against the vectors of the reference's own class."""
+    gold = np.load(os.path.join(golden_dir, "lookup1d_b1_dim2_16x24.npz"))
+    dev = cuda_device
+    corr1 = torch.from_numpy(gold["corr1"]).float().to(dev).requires_grad_(True)
+    corr2 = torch.from_numpy(gold["corr2"]).float().to(dev).requires_grad_(True)
+    coords = torch.from_numpy(gold["coords"]).float().to(dev)
+    blk = sfb.CorrBlock1D(corr1, corr2, num_levels=int(gold["levels"]), radius=int(gold["radius"]))
+    out1, out2 = blk(coords)
+    assert relerr(out1, torch.from_numpy(gold["out1"])) < LOOKUP_TOL
+    assert relerr(out2, torch.from_numpy(gold["out2"])) < LOOKUP_TOL
+    w1 = torch.from_numpy(gold["w1"]).to(dev)
+    w2 = torch.from_numpy(gold["w2"]).to(dev)
+    ((out1 * w1).sum() + (out2 * w2).sum()).backward()
+    assert relerr(corr1.grad, torch.from_numpy(gold["g_corr1"])) < LOOKUP_TOL
+    assert relerr(corr2.grad, torch.from_numpy(gold["g_corr2"])) < LOOKUP_TOL
+
+
 def test_ops_from_a_fresh_thread(cuda_device):
     """A thread that has not touched CUDA yet (an autograd worker whose first node is one of these ops) can call
     every entry point: the library binds the device context itself before it builds tensor maps."""

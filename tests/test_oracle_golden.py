@@ -91,3 +91,18 @@ def test_row_chunking_is_transparent(monkeypatch):
     chunked = orc.max_argmax_avg_forward(F1, F2)
     for a, b in zip(whole, chunked):
         assert torch.equal(a, b)
+
+
+def test_lookup_matches_reference_corrblock1d(golden_dir):
+    """The oracle's lookup against the outputs and volume gradients of the reference's own CorrBlock1D
+    (core/corr.py:513-624; float32 outputs, hence 1e-6)."""
+    g = np.load(os.path.join(golden_dir, "lookup1d_b1_dim2_16x24.npz"))
+    levels, radius = int(g["levels"]), int(g["radius"])
+    coords = torch.from_numpy(g["coords"])
+    for i, clamp in ((1, True), (2, False)):
+        corr = torch.from_numpy(g[f"corr{i}"])
+        out = orc.lookup_forward(corr, coords[:, i - 1], levels, radius, clamp_unit=clamp)
+        ref = torch.from_numpy(g[f"out{i}"]).double()
+        assert out.shape == ref.shape and (out - ref).abs().max().item() < 1e-6
+        gc = orc.lookup_backward(corr.shape, coords[:, i - 1], torch.from_numpy(g[f"w{i}"]).double(), levels, radius, clamp)
+        assert (gc - torch.from_numpy(g[f"g_corr{i}"]).double()).abs().max().item() < 1e-6
