@@ -201,6 +201,76 @@ def launches_per_step(cfg) -> int:
     return n
 
 
+def run_lookup_bench(args, cfg, device, emit):
+    """`--path lookup`: one refinement iteration of the reference's CorrBlock1D (core/corr.py:576-624) = the lookup of
+    both aggregated volumes (dim 1, 4 levels, radius 4) at every image-1 pixel, forward and (training configs)
+    backward, on device-resident volumes of the config's size.  HBM-bound: reported against the measured copy
+    bandwidth."""
+    import separableflowthesis_b200 as sfb
+    from separableflowthesis_b200 import _lib
+    B, H, W = cfg["B"], cfg["H"], cfg["W"]
+    levels, radius, dim = 4, 4, 1
+    gd = torch.Generator(device=device).manual_seed(SEED + 11)
+    corr1 = torch.randn(B, dim, W, H, W, generator=gd, device=device, requires_grad=cfg["bwd"])
+    corr2 = torch.randn(B, dim, H, H, W, generator=gd, device=device, requires_grad=cfg["bwd"])
+    ys, xs = torch.meshgrid(torch.arange(H, device=device), torch.arange(W, device=device), indexing="ij")
+    # a smooth displacement field (two low-frequency waves, amplitude ~8 pixels) plus sub-pixel noise, standing in
+    # for the flow estimates of a refinement iteration, which are piecewise smooth
+    yy, xx = ys.float() / H, xs.float() / W
+    flow = torch.stack((8.0 * torch.sin(6.28 * (xx + 0.5 * yy)), 6.0 * torch.cos(6.28 * (yy - 0.3 * xx))))
+    coords = (torch.stack((xs, ys)).float() + flow)[None].repeat(B, 1, 1, 1)
+    coords = coords + 0.25 * torch.randn(B, 2, H, W, generator=gd, device=device)
+    blk = sfb.CorrBlock1D(corr1, corr2, num_levels=levels, radius=radius)
+    taps = 2 * radius + 1
+    gout = torch.randn(B, levels * dim * taps, H, W, generator=gd, device=device)
+
+    def step():
+        o1, o2 = blk(coords)
+        if cfg["bwd"]:
+            corr1.grad = corr2.grad = None
+            torch.autograd.backward([o1, o2], [gout, gout])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)   # > L2: the volumes alone may fit
+    e0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    e1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    sampler = ClockSampler(device.index or 0)
+    torch.cuda.synchronize()
+    for i in range(args.steps):
+        flush.zero_()
+        e0[i].record()
+        step()
+        e1[i].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = sum(a.elapsed_time(b) for a, b in zip(e0, e1)) / args.steps
+    samples = 2.0 * B * H * W * levels * dim * taps
+    # algorithmic bytes of one iteration: every output written once; per pixel, level and channel the 2r+2 volume
+    # rows its taps touch; backward reads the output gradients and writes the volume gradients once
+    out_bytes = samples * 4
+    touched = 2.0 * B * H * W * levels * dim * (taps + 1) * 4
+    vol = 4.0 * B * dim * H * W * (H + W)
+    bytes_fwd = out_bytes + touched
+    bytes_bwd = (out_bytes + vol) if cfg["bwd"] else 0.0
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = (bytes_fwd + bytes_bwd) / (ms * 1e-3) / 1e9
+    emit({"metric": "3D cost-volume lookups/sec" + (" (fwd+bwd)" if cfg["bwd"] else " (fwd)"),
+          "value": samples / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": args.steps,
+          "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+          "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+          "config": {"workload": cfg["name"] + ": CorrBlock1D lookup, dim 1, 4 levels, radius 4, both volumes",
+                     "path": "lookup", "l2": "L2 flushed between iterations"},
+          "clocks": clocks, "gpu_launches": (2 + (2 if cfg["bwd"] else 0)) * args.steps,
+          "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                       "traffic": None, "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650"}})
+
+
 class E2E:
     """The call a user of the reference makes: channels-first feature maps in host memory ->
     AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
@@ -385,10 +455,11 @@ def main():
     ap.add_argument("--no-roofline", action="store_true", help="skip the per-kernel timing pass and the TF32 peak run")
     ap.add_argument("--unfused", action="store_true",
                     help="run the two backward ops as the reference's two separate calls instead of the one-call backward")
-    ap.add_argument("--path", default="auto", choices=["auto", "level", "ops"],
+    ap.add_argument("--path", default="auto", choices=["auto", "level", "ops", "lookup"],
                     help="level: one library call per pyramid-level forward / backward, as the call site runs it "
                          "(attention Conv3d + softmax included); ops: the five ops of the reference's module with "
-                         "random attention weights; auto: level when the config has attention channels")
+                         "random attention weights; auto: level when the config has attention channels; lookup: "
+                         "the CorrBlock1D lookup on the aggregated volumes instead of the separation")
     ap.add_argument("--e2e-chunks", type=int, default=2,
                     help="micro-batches per end-to-end step (the host->device copy of one overlaps the compute of the "
                          "previous one); 1 = copy everything, then compute")
@@ -428,6 +499,13 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     shard = sharding.make_shard(cfg["B"], cfg["H"], world, rank)
     path = args.path
+    if path == "lookup":   # the lookup on the aggregated volumes (next component after the separation), one GPU
+        if rank == 0:
+            run_lookup_bench(args, cfg, device, emit)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if path == "auto":
         path = "level" if cfg["Kc"] > 0 and shard.g_rows == 1 and not args.unfused else "ops"
     if path == "level" and (cfg["Kc"] == 0 or shard.g_rows > 1):

@@ -119,6 +119,66 @@ __global__ void lookup_fold_kernel(const LookupLevelsMut gl, int N1, int levels)
   *dst += acc;
 }
 
+// Backward in one pass for radius <= LK_RMAX: per level, the taps of a pixel touch a window of at most 2r+3
+// consecutive rows, which the thread accumulates in shared memory (its own column, no barrier); it then writes its
+// whole displacement column of the volume gradient once, folding the levels in as it goes (a level-l entry spreads
+// evenly over the 2^l level-0 entries it averaged).  No memset, no read-modify-write, no pyramid scratch.
+// grid (ceil(N1/128), B * dim)
+constexpr int LK_RMAX = 4;
+constexpr int LK_WIN = 2 * LK_RMAX + 4;
+
+__global__ void __launch_bounds__(LK_THREADS)
+lookup_backward_window_kernel(const float* __restrict__ coord, long long coord_sb, const float* __restrict__ gout,
+                              float* __restrict__ gcorr, int dim, int D, int N1, int levels, int radius,
+                              int clamp_unit) {
+  __shared__ float win[LOOKUP_MAX_LEVELS][LK_WIN][LK_THREADS];
+  const int p = blockIdx.x * LK_THREADS + threadIdx.x, b = blockIdx.y / dim, ch = blockIdx.y - b * dim;
+  if (p >= N1) return;
+  const int tid = threadIdx.x;
+  const float c = __ldg(coord + (size_t)b * coord_sb + p);
+  const int taps = 2 * radius + 1;
+  const float* go = gout + (size_t)b * levels * dim * taps * N1 + p;
+  int wbase[LOOKUP_MAX_LEVELS], Dl[LOOKUP_MAX_LEVELS];
+  int Dcur = D;
+  for (int l = 0; l < levels; ++l, Dcur /= 2) {
+    Dl[l] = Dcur;
+    for (int s = 0; s < LK_WIN; ++s) win[l][s][tid] = 0.f;
+    for (int t = 0; t < taps; ++t) {
+      const float ix = lookup_position(c, l, t, radius, clamp_unit, Dcur);
+      const float fl = floorf(ix);
+      const float w1 = ix - fl, w0 = 1.f - w1;
+      const int i0 = (int)fminf(fmaxf(fl, -2.f), (float)Dcur);
+      if (t == 0) wbase[l] = i0;
+      const float g = __ldg(go + (size_t)((l * dim + ch) * taps + t) * N1);
+      const int s0 = i0 - wbase[l];   // positions grow with t: 0 <= s0 <= 2r+1 (+1 of rounding slack)
+      if (s0 >= 0 && s0 + 1 < LK_WIN) {
+        win[l][s0][tid] += w0 * g;      // rows outside the volume are dropped when the column is written
+        win[l][s0 + 1][tid] += w1 * g;
+      }
+    }
+  }
+  float* dst = gcorr + ((size_t)(b * dim + ch) * D) * N1 + p;
+  // rows below / above every level's window get no gradient: plain zero stores
+  int lo = D, hi = 0;
+  for (int l = 0; l < levels; ++l) {
+    lo = min(lo, max(wbase[l], 0) << l);
+    hi = max(hi, min((wbase[l] + LK_WIN) << l, D));
+  }
+  lo = min(lo, D);
+  for (int i = 0; i < lo; ++i) dst[(size_t)i * N1] = 0.f;
+  for (int i = max(hi, lo); i < D; ++i) dst[(size_t)i * N1] = 0.f;
+  for (int i = lo; i < max(hi, lo); ++i) {
+    float acc = 0.f, scale = 1.f;
+    for (int l = 0; l < levels; ++l, scale *= 0.5f) {
+      const int j = i >> l;
+      if (j >= Dl[l]) break;            // dropped by the floor of an odd size: no coarser level sees it either
+      const int s = j - wbase[l];
+      if (s >= 0 && s < LK_WIN) acc = fmaf(scale, win[l][s][tid], acc);
+    }
+    dst[(size_t)i * N1] = acc;
+  }
+}
+
 // ---- launchers ---------------------------------------------------------------------------------------
 size_t lookup_pyramid_floats(const LookupDims& d) {  // levels 1 .. levels-1
   size_t n = 0;
@@ -164,9 +224,15 @@ cudaError_t launch_lookup_forward(const LookupDims& d, const float* corr, const 
 
 cudaError_t launch_lookup_backward(const LookupDims& d, const float* gout, const float* coord, long long coord_sb,
                                    float* gcorr, float* gpyramid, int clamp_unit, cudaStream_t st) {
+  const int N1 = d.H1 * d.W1;
+  if (d.radius <= LK_RMAX) {
+    const dim3 wgrid((N1 + LK_THREADS - 1) / LK_THREADS, d.B * d.dim);
+    lookup_backward_window_kernel<<<wgrid, LK_THREADS, 0, st>>>(coord, coord_sb, gout, gcorr, d.dim, d.D, N1, d.levels,
+                                                               d.radius, clamp_unit);
+    return cudaGetLastError();
+  }
   LookupLevelsMut gl;
   fill_levels(gl, d, gcorr, gpyramid);
-  const int N1 = d.H1 * d.W1;
   cudaError_t err = cudaMemsetAsync(gcorr, 0, (size_t)d.B * d.dim * d.D * N1 * sizeof(float), st);
   if (err != cudaSuccess) return err;
   const size_t pyr = lookup_pyramid_floats(d);
