@@ -276,10 +276,11 @@ class E2E:
     AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
     gradients -> loss-sized results back on the host."""
 
-    def __init__(self, cfg, job, device, chunks=1):
+    def __init__(self, cfg, job, device, chunks=1, levels=1):
         import separableflowthesis_b200 as sfb
         self.sfb, self.cfg, self.device = sfb, cfg, device
         self.chunks = chunks
+        self.levels = levels
         self.copy_stream = torch.cuda.Stream(device=device)
         self.h1 = job["f1_nchw"].pin_memory()
         self.h2 = job["f2_nchw"].pin_memory()
@@ -325,7 +326,7 @@ class E2E:
             if cfg["bwd"]:
                 f1.requires_grad_(True)
                 f2.requires_grad_(True)
-            blk = self.sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=1, support_backward=cfg["bwd"])
+            blk = self.sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=self.levels, support_backward=cfg["bwd"])
             with torch.set_grad_enabled(cfg["bwd"]):
                 sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(self.att) if self.att else None)
             if cfg["bwd"]:
@@ -463,6 +464,9 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=2,
                     help="micro-batches per end-to-end step (the host->device copy of one overlaps the compute of the "
                          "previous one); 1 = copy everything, then compute")
+    ap.add_argument("--levels", type=int, default=1,
+                    help="pyramid levels of the end-to-end block (the metric counts level-0 cells; the reference's "
+                         "model uses 4 levels = 1.33x the cells)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small ncu captures)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
@@ -585,7 +589,7 @@ def main():
     # ---- end to end through the public API with host buffers ----
     e2e = None
     if not args.no_e2e:
-        runner = E2E(cfg, job, device, chunks=args.e2e_chunks)
+        runner = E2E(cfg, job, device, chunks=args.e2e_chunks, levels=args.levels)
         for _ in range(min(args.warmup, 3)):
             runner.step()
         barrier()
@@ -599,7 +603,8 @@ def main():
         e2e = {"value": total_cells / (ms_e2e * 1e-3), "unit": unit, "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": int(sum_over_ranks(float(runner.h2d))),
                "d2h_bytes_per_step": int(sum_over_ranks(float(runner.d2h))),
-               "path": "pinned host f1,f2 (B,C,H,W) -> AlternateCorrBlockSepflow(num_levels=1).separate with "
+               "pyramid_levels": args.levels,
+               "path": f"pinned host f1,f2 (B,C,H,W) -> AlternateCorrBlockSepflow(num_levels={args.levels}).separate with "
                        "Conv3d attention -> autograd backward -> all-reduce of attention-parameter grads -> host; "
                        f"{runner.chunks} micro-batch(es) per step, copy of one overlapping compute of the previous"}
         del runner

@@ -209,6 +209,17 @@ int sfb_separation_level_backward_fmaps(const float* fmap1, const float* fmap2, 
                                         const sfb_shape* shape, void* workspace, size_t workspace_bytes,
                                         void* stream);
 
+/* Placement of one pyramid level's volumes into the concatenated outputs of the call site (core/corr.py:459-475:
+ * F.interpolate(..., [D0,H1,W1], mode='trilinear', align_corners=True), then torch.cat over levels).  H1, W1 do not
+ * change, so this is linear interpolation along the displacement axis, with torch's arithmetic.
+ *   in (B,K,Dl,H1,W1) -> K consecutive channels of a (B,Ktot,D0,H1,W1) tensor: `out` points at the first of them in
+ *   sample 0, `out_batch_stride` = Ktot*D0*H1*W1 elements.  Dl <= D0 (Dl == D0 copies).
+ * The backward is the adjoint: gin (B,K,Dl,H1,W1) from the same channel slice of the output gradient. */
+int sfb_upsample_displacement(const float* in, float* out, int64_t out_batch_stride, int32_t B, int32_t K, int32_t Dl,
+                              int32_t D0, int32_t H1, int32_t W1, void* stream);
+int sfb_upsample_displacement_backward(const float* gout, int64_t gout_batch_stride, float* gin, int32_t B, int32_t K,
+                                       int32_t Dl, int32_t D0, int32_t H1, int32_t W1, void* stream);
+
 /* Lookup on an aggregated 3D cost volume: the reference's CorrBlock1D (core/corr.py:513-624) for ONE of its two
  * volumes.  corr (B,dim,D,H1,W1) is the volume as the model holds it (core/sepflow.py:184-187); the pyramid over
  * the displacement axis (core/corr.py:543-548; levels 1..levels-1, level l = (B,dim,D>>l,H1,W1), back to back,

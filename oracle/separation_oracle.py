@@ -297,6 +297,21 @@ def separation_level_backward(F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am
     return [gF1, gF2, gw_u, gb_u, gw_v, gb_v]
 
 
+# Placement of a level's volumes into the concatenated outputs, as the reference does it (core/corr.py:459-475).
+def upsample_displacement_into(src, dst, c0):
+    K = src.shape[1]
+    dst[:, c0:c0 + K] = torch.nn.functional.interpolate(src, list(dst.shape[2:]), mode="trilinear", align_corners=True)
+
+
+def upsample_displacement_backward(grad_dst, c0, K, Dl):
+    B, _, D0, H1, W1 = grad_dst.shape
+    with torch.enable_grad():
+        src = torch.zeros(B, K, Dl, H1, W1, dtype=grad_dst.dtype, device=grad_dst.device, requires_grad=True)
+        out = torch.nn.functional.interpolate(src, [D0, H1, W1], mode="trilinear", align_corners=True)
+        out.backward(grad_dst[:, c0:c0 + K])
+    return src.grad
+
+
 # Lookup on the aggregated 3D volumes: the reference's CorrBlock1D (core/corr.py:513-624), one volume at a time.
 def lookup_pyramid(corr, levels):
     """Levels 0 .. levels-1 of the displacement pyramid of corr (B,dim,D,H1,W1): average pooling by two along the

@@ -24,7 +24,8 @@ import torch.nn.functional as F
 
 from .functions import (ComputeMaxArgmaxAvgFunction, ComputeMaxAvgFunction, ComputeSelfCompressionFunction,
                         FusedMaxArgmaxAvgFunction, FusedSelfCompressionFunction, SeparationCompressionCF,
-                        LookupFunction, SeparationLevelFunction, SeparationMaxAvgCF, SeparationState)
+                        LookupFunction, SeparationLevelFunction, SeparationMaxAvgCF, SeparationPyramidFunction,
+                        SeparationState)
 from . import ops as _ops
 
 
@@ -105,6 +106,13 @@ class AlternateCorrBlockSepflow:
         """All levels, each trilinearly resampled to the level-0 displacement range and concatenated
         over channels: sep_u (B, K*levels, W, H, W), sep_v (B, K*levels, H, H, W) (core/corr.py:384-477)."""
         batch, fdim, h1, w1 = self.fmap1_l0.shape
+        if self._one_node_per_level(attention_weights) and self.num_levels > 1:
+            # one node for the whole pyramid: levels are resampled along the displacement axis and written into
+            # their channel slices of the outputs by the library (no F.interpolate, no torch.cat)
+            attention1, attention2 = attention_weights
+            return SeparationPyramidFunction.apply(self.support_backward, 1.0 / math.sqrt(fdim), attention1.weight,
+                                                   attention1.bias, attention2.weight, attention2.bias,
+                                                   self.fmap1_l0.contiguous(), *[f.contiguous() for f in self.pyramid])
         F1 = None
         if not self._one_node_per_level(attention_weights):
             F1 = self.fmap1_l0.permute(0, 2, 3, 1).contiguous() / math.sqrt(fdim)

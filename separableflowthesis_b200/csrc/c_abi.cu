@@ -79,7 +79,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 enum KernelId : int {
   KID_PREPARE = 0, KID_PACK, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
   KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_GRAD_FUSED_IMG1, KID_GRAD_FUSED_IMG2, KID_ATTENTION_FWD,
-  KID_ATTENTION_BWD, KID_LOOKUP, KID_COUNT
+  KID_ATTENTION_BWD, KID_LOOKUP, KID_RESAMPLE, KID_COUNT
 };
 const char* const kKernelNames[KID_COUNT] = {
     "prepare(round_copy+f2_means)", "pack_kernel/unpack_kernel", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
@@ -87,7 +87,7 @@ const char* const kKernelNames[KID_COUNT] = {
     "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>",
     "grad_gemm_kernel<fused,image1-major>", "grad_gemm_kernel<fused,image2-major>",
     "attention_forward_kernel", "attention backward (logit, input, weight grads)",
-    "lookup kernels (pyramid, forward, backward)"};
+    "lookup kernels (pyramid, forward, backward)", "upsample_displacement kernels"};
 struct TimingRec { cudaEvent_t e0, e1; int id; int launches; };
 std::mutex g_timing_mu;
 bool g_timing_on = false;
@@ -990,6 +990,37 @@ int sfb_separation_level_backward_fmaps(const float* fmap1, const float* fmap2, 
                         stream);
 }
 
+
+// ---- placement of a level's volumes into the concatenated level-0-sized outputs ----
+static int check_resample(const void* a, const void* b, int B, int K, int Dl, int D0, int H1, int W1) {
+  if (a == nullptr || b == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "tensor pointers must not be NULL");
+  if (B < 1 || K < 1 || Dl < 1 || D0 < 1 || H1 < 1 || W1 < 1)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "B, K, Dl, D0, H1, W1 must be >= 1");
+  if (Dl > D0) return fail(SFB_ERR_UNSUPPORTED_SHAPE, "Dl=%d > D0=%d: only upsampling is supported", Dl, D0);
+  if (B * (long long)K > 65535 || D0 > 65535) return fail(SFB_ERR_UNSUPPORTED_SHAPE, "B*K and D0 must be <= 65535");
+  if ((long long)H1 * W1 > (1ll << 24)) return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image 1 has more than 2^24 pixels");
+  return SFB_OK;
+}
+
+int sfb_upsample_displacement(const float* in, float* out, int64_t out_batch_stride, int32_t B, int32_t K, int32_t Dl,
+                              int32_t D0, int32_t H1, int32_t W1, void* stream) {
+  SFB_TRY(check_resample(in, out, B, K, Dl, D0, H1, W1));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_RESAMPLE, 1, st, [&] {
+    return launch_upsample_displacement(in, out, out_batch_stride, B, K, Dl, D0, H1 * W1, st);
+  }));
+  return SFB_OK;
+}
+
+int sfb_upsample_displacement_backward(const float* gout, int64_t gout_batch_stride, float* gin, int32_t B, int32_t K,
+                                       int32_t Dl, int32_t D0, int32_t H1, int32_t W1, void* stream) {
+  SFB_TRY(check_resample(gout, gin, B, K, Dl, D0, H1, W1));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_RESAMPLE, 1, st, [&] {
+    return launch_upsample_displacement_adjoint(gout, gout_batch_stride, gin, B, K, Dl, D0, H1 * W1, st);
+  }));
+  return SFB_OK;
+}
 
 // ---- lookup on the aggregated 3D volumes (CorrBlock1D) ----
 static int check_lookup_dims(int B, int dim, int D, int H1, int W1, int levels, int radius, LookupDims* ld) {

@@ -149,6 +149,14 @@ cudaError_t launch_attention_backward(const AttentionDims& d, const float* x, lo
                                       float* gweight, float* gbias, float* partial, cudaStream_t stream);
 
 
+// Linear resampling along the displacement axis (core/corr.py:459-467: trilinear interpolate with unchanged H1, W1):
+// in (B, K, Dl, N1) -> K channels of a larger tensor, out[b] at out + b*out_sb, each (K, D0, N1); Dl <= D0.
+cudaError_t launch_upsample_displacement(const float* in, float* out, long long out_sb, int B, int K, int Dl, int D0,
+                                         int N1, cudaStream_t stream);
+// Its adjoint: gin (B, K, Dl, N1) from the gradient of those K channels.
+cudaError_t launch_upsample_displacement_adjoint(const float* gout, long long gout_sb, float* gin, int B, int K, int Dl,
+                                                 int D0, int N1, cudaStream_t stream);
+
 // Lookup on an aggregated 3D cost volume (the reference's CorrBlock1D, core/corr.py:513-624).
 // corr (B, dim, D, H1, W1); pyramid = levels 1 .. levels-1 back to back, level l being (B, dim, D >> l, H1, W1);
 // coord: one displacement component per pixel, (B, H1, W1) with `coord_sb` elements between samples;

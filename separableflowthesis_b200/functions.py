@@ -248,6 +248,61 @@ class SeparationLevelFunction(Function):
 
 
 # --------------------------------------------------------------------------------------------------
+# All pyramid levels as one autograd node (core/corr.py:416-475): per level the one-call forward from the feature
+# maps, then its volumes are resampled along the displacement axis and written straight into their channel slice of
+# the concatenated outputs (the reference runs F.interpolate per level and torch.cat over levels).
+class SeparationPyramidFunction(Function):
+    @staticmethod
+    def forward(ctx, with_argmax, scale1, weight_u, bias_u, weight_v, bias_v, fmap1, *fmap2_levels):
+        assert fmap1.is_contiguous() and all(f.is_contiguous() for f in fmap2_levels)
+        params = [t.contiguous() for t in (weight_u, bias_u, weight_v, bias_v)]
+        B, _, H1, W1 = fmap1.shape
+        L, Kt = len(fmap2_levels), 2 + weight_u.shape[0]
+        saved = []
+        with torch.cuda.device_of(fmap1):
+            sep_u = torch.empty(B, Kt * L, W1, H1, W1, dtype=fmap1.dtype, device=fmap1.device)
+            sep_v = torch.empty(B, Kt * L, H1, H1, W1, dtype=fmap1.dtype, device=fmap1.device)
+            for l, fmap2 in enumerate(fmap2_levels):
+                su, sv, am_u, am_v, a_u, a_v = MemorySaver.separation_level_forward(fmap1, fmap2, *params, with_argmax,
+                                                                                    True, scale1)
+                MemorySaver.upsample_displacement_into(su, sep_u, l * Kt)
+                MemorySaver.upsample_displacement_into(sv, sep_v, l * Kt)
+                saved += [su, sv, am_u, am_v, a_u, a_v]
+        ctx.with_argmax, ctx.scale1, ctx.levels = with_argmax, scale1, L
+        if with_argmax:
+            ctx.save_for_backward(fmap1, weight_u, weight_v, *fmap2_levels, *saved)
+        return sep_u, sep_v
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_sep_u, grad_sep_v):
+        if not ctx.with_argmax:
+            raise NotImplementedError("max avg backward pass is not implemented: use max argmax avg")
+        L = ctx.levels
+        fmap1, weight_u, weight_v = ctx.saved_tensors[:3]
+        fmap2_levels = ctx.saved_tensors[3:3 + L]
+        saved = ctx.saved_tensors[3 + L:]
+        wu, wv = weight_u.contiguous(), weight_v.contiguous()
+        gu, gv = grad_sep_u.contiguous(), grad_sep_v.contiguous()
+        Kt = 2 + weight_u.shape[0]
+        g1 = gw_u = gb_u = gw_v = gb_v = None
+        g2 = []
+        with torch.cuda.device_of(gu):
+            for l in range(L):
+                su, sv, am_u, am_v, a_u, a_v = saved[6 * l:6 * l + 6]
+                gsu = MemorySaver.upsample_displacement_backward(gu, l * Kt, Kt, su.shape[2])
+                gsv = MemorySaver.upsample_displacement_backward(gv, l * Kt, Kt, sv.shape[2])
+                out = MemorySaver.separation_level_backward(fmap1, fmap2_levels[l], wu, wv, su, sv, am_u, am_v, a_u, a_v,
+                                                            gsu, gsv, True, ctx.scale1)
+                g2.append(out[1])
+                if l == 0:
+                    g1, gw_u, gb_u, gw_v, gb_v = out[0], out[2], out[3], out[4], out[5]
+                else:
+                    g1 += out[0]; gw_u += out[2]; gb_u += out[3]; gw_v += out[4]; gb_v += out[5]
+        return (None, None, gw_u, gb_u, gw_v, gb_v, g1, *g2)
+
+
+# --------------------------------------------------------------------------------------------------
 # Lookup on one aggregated 3D volume (CorrBlock1D, core/corr.py:576-594).  The volume's pyramid is passed in so that
 # it is built once per volume, not once per refinement iteration.  No gradient for the coordinates: the model
 # detaches them before every lookup (core/sepflow.py:192).

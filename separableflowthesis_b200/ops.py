@@ -434,6 +434,41 @@ def separation_level_backward(img1_features_l0, img2_features_lk, weight_u, weig
 
 
 # ------------------------------------------------------------------------------------------------------
+# Placement of a level's volumes into the concatenated, level-0-sized outputs (core/corr.py:459-475).
+def upsample_displacement_into(src: torch.Tensor, dst: torch.Tensor, c0: int) -> None:
+    """dst[:, c0:c0+K] = F.interpolate(src, dst.shape[2:], mode='trilinear', align_corners=True) for src
+    (B,K,Dl,H1,W1) and a contiguous dst (B,Ktot,D0,H1,W1) with the same H1, W1 and Dl <= D0."""
+    _check(src, "src", torch.float32, 5)
+    _check(dst, "dst", torch.float32, 5)
+    B, K, Dl, H1, W1 = src.shape
+    if dst.shape[0] != B or tuple(dst.shape[3:]) != (H1, W1) or c0 < 0 or c0 + K > dst.shape[1] or dst.device != src.device:
+        raise RuntimeError(f"cannot place {tuple(src.shape)} at channel {c0} of {tuple(dst.shape)}")
+    D0 = dst.shape[2]
+    lib = _lib.load()
+    with torch.cuda.device(src.device):
+        stream = torch.cuda.current_stream(src.device).cuda_stream
+        out = ctypes.c_void_p(dst.data_ptr() + 4 * c0 * D0 * H1 * W1)
+        _raise_on(lib.sfb_upsample_displacement(_ptr(src), out, dst.stride(0), B, K, Dl, D0, H1, W1,
+                                                ctypes.c_void_p(stream)), "sfb_upsample_displacement")
+
+
+def upsample_displacement_backward(grad_dst: torch.Tensor, c0: int, K: int, Dl: int) -> torch.Tensor:
+    """Gradient of ``src`` (B,K,Dl,H1,W1) of ``upsample_displacement_into`` from the gradient of the whole dst."""
+    _check(grad_dst, "grad_dst", torch.float32, 5)
+    B, Ktot, D0, H1, W1 = grad_dst.shape
+    if c0 < 0 or c0 + K > Ktot:
+        raise RuntimeError(f"channels {c0}..{c0 + K} outside {Ktot}")
+    gsrc = torch.empty(B, K, Dl, H1, W1, dtype=torch.float32, device=grad_dst.device)
+    lib = _lib.load()
+    with torch.cuda.device(grad_dst.device):
+        stream = torch.cuda.current_stream(grad_dst.device).cuda_stream
+        g = ctypes.c_void_p(grad_dst.data_ptr() + 4 * c0 * D0 * H1 * W1)
+        _raise_on(lib.sfb_upsample_displacement_backward(g, grad_dst.stride(0), _ptr(gsrc), B, K, Dl, D0, H1, W1,
+                                                         ctypes.c_void_p(stream)), "sfb_upsample_displacement_backward")
+    return gsrc
+
+
+# ------------------------------------------------------------------------------------------------------
 # Lookup on an aggregated 3D cost volume (the reference's CorrBlock1D, core/corr.py:513-624), one volume at a time.
 def _check_volume(corr):
     _check(corr, "corr", torch.float32, 5)

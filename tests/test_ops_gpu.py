@@ -289,6 +289,25 @@ def test_separation_level(shape, cuda_device):
 # position error ~ D * 2^-24, i.e. ~1.4e-5 of a displacement step at D = 240
 LOOKUP_TOL = 5e-5
 
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1, 1, 1), (2, 3, 5, 11, 4, 7), (1, 6, 30, 240, 9, 33), (2, 2, 16, 16, 5, 130)])
+def test_upsample_displacement(shape, cuda_device):
+    """Resampling of a level's volumes along the displacement axis into a channel slice of the concatenated output
+    and its adjoint, against F.interpolate(mode='trilinear', align_corners=True) (core/corr.py:459-467)."""
+    B, K, Dl, D0, H1, W1 = shape
+    g = torch.Generator().manual_seed(41)
+    src = torch.randn(B, K, Dl, H1, W1, generator=g)
+    dev = cuda_device
+    dst = torch.full((B, K + 3, D0, H1, W1), 7.0, device=dev)
+    ops.upsample_displacement_into(src.to(dev), dst, 2)
+    ref = F.interpolate(src.double(), [D0, H1, W1], mode="trilinear", align_corners=True)
+    # the source position d*(Dl-1)/(D0-1) is formed in float32, as in torch's own float32 kernel: ~D0 * 2^-24
+    assert relerr(dst[:, 2:2 + K], ref) < 2e-5
+    assert (dst[:, :2] == 7.0).all() and (dst[:, 2 + K:] == 7.0).all()     # neighbours untouched
+    gd = torch.randn(B, K + 3, D0, H1, W1, generator=g)
+    gs = ops.upsample_displacement_backward(gd.to(dev), 2, K, Dl)
+    assert relerr(gs, orc.upsample_displacement_backward(gd.double(), 2, K, Dl)) < 2e-5
+
 # (B, dim, D, H1, W1, levels, radius)
 LOOKUP_SHAPES = [(1, 1, 2, 1, 1, 1, 1), (2, 1, 16, 5, 7, 4, 4), (1, 3, 37, 9, 11, 3, 2), (2, 2, 240, 13, 37, 4, 4)]
 
