@@ -196,18 +196,23 @@ int sfb_separation_level_backward(const float* F1, const float* F2, const float*
 /* The same two calls on the model's own feature maps fmap1 (B,C,H1,W1), fmap2 (B,C,H2,W2) (shape->H1.. as above):
  * the transposition to channels-last and the multiplication of fmap1 by scale1 = 1/sqrt(C) that core/corr.py:419-422
  * does with permute().contiguous() happen inside the rounding copy, and the gradients come back as
- * gfmap1 (B,C,H1,W1) (chain rule through scale1 included) and gfmap2 (B,C,H2,W2). */
+ * gfmap1 (B,C,H1,W1) (chain rule through scale1 included) and gfmap2 (B,C,H2,W2).
+ * Placement: with sep_channels = 0 the volumes are tensors of their own, as above.  Otherwise SEP_u / SEP_v (and
+ * gSEP_u / gSEP_v) are tensors with `sep_channels` channels -- the concatenated outputs of all pyramid levels,
+ * core/corr.py:473-475 -- and this level occupies channels sep_channel0 .. sep_channel0+2+Kc-1 (possible for the
+ * level whose displacement range is the output's, i.e. level 0). */
 int sfb_separation_level_forward_fmaps(const float* fmap1, const float* fmap2, float scale1, const float* weight_u,
                                        const float* bias_u, const float* weight_v, const float* bias_v, float* SEP_u,
-                                       float* SEP_v, int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v,
-                                       const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream);
+                                       float* SEP_v, int32_t sep_channels, int32_t sep_channel0, int32_t* AM_u,
+                                       int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape, void* workspace,
+                                       size_t workspace_bytes, void* stream);
 int sfb_separation_level_backward_fmaps(const float* fmap1, const float* fmap2, float scale1, const float* weight_u,
                                         const float* weight_v, const float* SEP_u, const float* SEP_v,
-                                        const int32_t* AM_u, const int32_t* AM_v, const float* A_u, const float* A_v,
-                                        const float* gSEP_u, const float* gSEP_v, float* gfmap1, float* gfmap2,
-                                        float* gweight_u, float* gbias_u, float* gweight_v, float* gbias_v,
-                                        const sfb_shape* shape, void* workspace, size_t workspace_bytes,
-                                        void* stream);
+                                        int32_t sep_channels, int32_t sep_channel0, const int32_t* AM_u,
+                                        const int32_t* AM_v, const float* A_u, const float* A_v, const float* gSEP_u,
+                                        const float* gSEP_v, float* gfmap1, float* gfmap2, float* gweight_u,
+                                        float* gbias_u, float* gweight_v, float* gbias_v, const sfb_shape* shape,
+                                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* Placement of one pyramid level's volumes into the concatenated outputs of the call site (core/corr.py:459-475:
  * F.interpolate(..., [D0,H1,W1], mode='trilinear', align_corners=True), then torch.cat over levels).  H1, W1 do not

@@ -266,7 +266,8 @@ def _from_fmaps(fmap1, fmap2, scale1):
     return fmap1.permute(0, 2, 3, 1).contiguous() * scale1, fmap2.permute(0, 2, 3, 1).contiguous()
 
 
-def separation_level_forward(F1, F2, weight_u, bias_u, weight_v, bias_v, with_argmax=True, fmaps=False, scale1=1.0):
+def separation_level_forward(F1, F2, weight_u, bias_u, weight_v, bias_v, with_argmax=True, fmaps=False, scale1=1.0,
+                             place=None):
     """[sep_u (B,2+Kc,W2,H1,W1), sep_v (B,2+Kc,H2,H1,W1), am_u, am_v, a_u, a_v] (core/corr.py:425-457); with
     ``fmaps`` from the model's (B,C,H,W) maps (core/corr.py:419-422)."""
     if fmaps:
@@ -275,15 +276,25 @@ def separation_level_forward(F1, F2, weight_u, bias_u, weight_v, bias_v, with_ar
     a_u = attention_forward(ma_u2, weight_u, bias_u)
     a_v = attention_forward(ma_v2, weight_v, bias_v)
     c_u, c_v = compression_forward_cf(F1, F2, a_u, a_v)
-    return [torch.cat((ma_u2, c_v), dim=1), torch.cat((ma_v2, c_u), dim=1), am_u, am_v, a_u, a_v]
+    sep_u, sep_v = torch.cat((ma_u2, c_v), dim=1), torch.cat((ma_v2, c_u), dim=1)
+    if place is not None:   # channels c0.. of the concatenated outputs of all levels
+        big_u, big_v, c0 = place
+        big_u[:, c0:c0 + sep_u.shape[1]] = sep_u
+        big_v[:, c0:c0 + sep_v.shape[1]] = sep_v
+        return [None, None, am_u, am_v, a_u, a_v]
+    return [sep_u, sep_v, am_u, am_v, a_u, a_v]
 
 
 def separation_level_backward(F1, F2, weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u, g_sep_v,
-                              fmaps=False, scale1=1.0):
+                              fmaps=False, scale1=1.0, c0=None):
     """[gF1, gF2, gweight_u, gbias_u, gweight_v, gbias_v]: the chain rule through the three ops and the two
     attention modules, with the forward's argmax and attention weights given."""
     if fmaps:
         F1, F2 = _from_fmaps(F1, F2, scale1)
+    if c0 is not None:
+        Kt = 2 + a_u.shape[1]
+        sep_u, sep_v = sep_u[:, c0:c0 + Kt], sep_v[:, c0:c0 + Kt]
+        g_sep_u, g_sep_v = g_sep_u[:, c0:c0 + Kt], g_sep_v[:, c0:c0 + Kt]
     gc_v = g_sep_u[:, 2:].contiguous()
     gc_u = g_sep_v[:, 2:].contiguous()
     ga_u, ga_v = compression_attention_backward_cf(F1, F2, gc_u, gc_v)

@@ -98,9 +98,9 @@ def load() -> ctypes.CDLL:
     lib.sfb_lookup_backward.restype = ctypes.c_int
     lib.sfb_lookup_backward.argtypes = [P, P, I64, P, P] + [I32] * 8 + [P]
     lib.sfb_separation_level_forward_fmaps.restype = ctypes.c_int
-    lib.sfb_separation_level_forward_fmaps.argtypes = [P, P, ctypes.c_float] + [P] * 10 + tail
+    lib.sfb_separation_level_forward_fmaps.argtypes = [P, P, ctypes.c_float] + [P] * 6 + [I32, I32] + [P] * 4 + tail
     lib.sfb_separation_level_backward_fmaps.restype = ctypes.c_int
-    lib.sfb_separation_level_backward_fmaps.argtypes = [P, P, ctypes.c_float] + [P] * 16 + tail
+    lib.sfb_separation_level_backward_fmaps.argtypes = [P, P, ctypes.c_float] + [P] * 4 + [I32, I32] + [P] * 12 + tail
     lib.sfb_max_avg_forward_static.restype = ctypes.c_int
     lib.sfb_max_avg_forward_static.argtypes = [P, P, P, P, SH, P]
     lib.sfb_static_scratch_bytes.restype = SZ

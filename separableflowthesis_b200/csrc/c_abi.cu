@@ -862,8 +862,22 @@ static PixView cf_channels(const void* base, int Ktot, int c0, int D, int N1) {
                  (uint32_t)N1, (uint32_t)(D * N1)};
 }
 
+// Where a level's (2+Kc)-channel volumes live: channels c0 .. c0+2+Kc-1 of tensors with Ktot channels (the
+// concatenated outputs of all pyramid levels); {0, 0} = tensors of their own.
+struct Placement { int Ktot, c0; };
+static int check_placement(const Dims& d, Placement* pl) {
+  const int Kt = 2 + d.Kc;
+  if (pl->Ktot == 0 && pl->c0 == 0) pl->Ktot = Kt;
+  if (pl->c0 < 0 || pl->c0 + Kt > pl->Ktot)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "channels %d..%d do not fit in %d channels", pl->c0, pl->c0 + Kt, pl->Ktot);
+  const long long n1p = ((long long)d.N1() + TILE_M - 1) / TILE_M * TILE_M;
+  if (n1p * pl->Ktot * (d.H2 > d.W2 ? d.H2 : d.W2) >= (1ll << 32))
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "H1*W1*max(H2,W2)*channels exceeds 2^32 elements per sample");
+  return SFB_OK;
+}
+
 // fmaps != 0: F1 / F2 are the model's feature maps (B, C, H, W); F1 is multiplied by scale1 on the way in.
-static int level_forward(const float* F1, const float* F2, int fmaps, float scale1, const float* weight_u,
+static int level_forward(Placement pl, const float* F1, const float* F2, int fmaps, float scale1, const float* weight_u,
                          const float* bias_u, const float* weight_v, const float* bias_v, float* SEP_u, float* SEP_v,
                          int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape,
                          void* workspace, size_t workspace_bytes, void* stream) {
@@ -874,6 +888,7 @@ static int level_forward(const float* F1, const float* F2, int fmaps, float scal
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(SEP_u); SFB_CHECK_PTR(SEP_v); SFB_CHECK_PTR(A_u); SFB_CHECK_PTR(A_v);
   if (weight_u == nullptr || bias_u == nullptr || weight_v == nullptr || bias_v == nullptr)
     return fail(SFB_ERR_INVALID_ARGUMENT, "attention weights and biases must not be NULL");
+  SFB_TRY(check_placement(d, &pl));
   const bool with_argmax = AM_u != nullptr || AM_v != nullptr;
   if (with_argmax) { SFB_CHECK_PTR(AM_u); SFB_CHECK_PTR(AM_v); }
   Workspace w;
@@ -887,45 +902,48 @@ static int level_forward(const float* F1, const float* F2, int fmaps, float scal
     return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, w.aux, w.status, st)
                  : launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st);
   }));
-  const int N1 = d.N1(), K = d.Kc, Kt = 2 + d.Kc;
+  const int N1 = d.N1(), K = d.Kc, Kt = pl.Ktot, c0 = pl.c0;
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
   a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
   a.n_valid = N1;
-  a.pu = cf_channels(SEP_v, Kt, 0, d.H2, N1);  // per-u channels live in the tensor the call site calls sep_v
-  a.pv = cf_channels(SEP_u, Kt, 0, d.W2, N1);
+  a.pu = cf_channels(SEP_v, Kt, c0, d.H2, N1);  // per-u channels live in the tensor the call site calls sep_v
+  a.pv = cf_channels(SEP_u, Kt, c0, d.W2, N1);
   a.pu_arg = cf_view(AM_u, 1, d.H2, N1);
   a.pv_arg = cf_view(AM_v, 1, d.W2, N1);
   a.status = w.status;
   SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
   const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
   SFB_CUDA(timed(KID_ATTENTION_FWD, 2 * ((K + 3) / 4), st, [&] {
-    launch_attention_forward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u, sb_u, weight_u, bias_u, A_u, st);
-    return launch_attention_forward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v, sb_v, weight_v, bias_v, A_v, st);
+    launch_attention_forward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u + (size_t)c0 * d.W2 * N1, sb_u, weight_u,
+                             bias_u, A_u, st);
+    return launch_attention_forward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v + (size_t)c0 * d.H2 * N1, sb_v,
+                                    weight_v, bias_v, A_v, st);
   }));
   // C_u (per u, weights A_u per v) -> SEP_v channels 2.., C_v -> SEP_u channels 2..
   return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(A_v, K, d.H2, N1), cf_view(A_u, K, d.W2, N1), 0, 0, 1,
-                             cf_channels(SEP_v, Kt, 2, d.H2, N1), cf_channels(SEP_u, Kt, 2, d.W2, N1), N1, st);
+                             cf_channels(SEP_v, Kt, c0 + 2, d.H2, N1), cf_channels(SEP_u, Kt, c0 + 2, d.W2, N1), N1, st);
 }
 
 int sfb_separation_level_forward(const float* F1, const float* F2, const float* weight_u, const float* bias_u,
                                  const float* weight_v, const float* bias_v, float* SEP_u, float* SEP_v,
                                  int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape,
                                  void* workspace, size_t workspace_bytes, void* stream) {
-  return level_forward(F1, F2, 0, 1.f, weight_u, bias_u, weight_v, bias_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v, shape,
-                       workspace, workspace_bytes, stream);
+  return level_forward(Placement{0, 0}, F1, F2, 0, 1.f, weight_u, bias_u, weight_v, bias_v, SEP_u, SEP_v, AM_u, AM_v, A_u,
+                       A_v, shape, workspace, workspace_bytes, stream);
 }
 
 int sfb_separation_level_forward_fmaps(const float* fmap1, const float* fmap2, float scale1, const float* weight_u,
                                        const float* bias_u, const float* weight_v, const float* bias_v, float* SEP_u,
-                                       float* SEP_v, int32_t* AM_u, int32_t* AM_v, float* A_u, float* A_v,
-                                       const sfb_shape* shape, void* workspace, size_t workspace_bytes, void* stream) {
-  return level_forward(fmap1, fmap2, 1, scale1, weight_u, bias_u, weight_v, bias_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v,
-                       shape, workspace, workspace_bytes, stream);
+                                       float* SEP_v, int32_t sep_channels, int32_t sep_channel0, int32_t* AM_u,
+                                       int32_t* AM_v, float* A_u, float* A_v, const sfb_shape* shape, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  return level_forward(Placement{sep_channels, sep_channel0}, fmap1, fmap2, 1, scale1, weight_u, bias_u, weight_v, bias_v,
+                       SEP_u, SEP_v, AM_u, AM_v, A_u, A_v, shape, workspace, workspace_bytes, stream);
 }
 
-static int level_backward(const float* F1, const float* F2, int fmaps, float scale1, const float* weight_u,
+static int level_backward(Placement pl, const float* F1, const float* F2, int fmaps, float scale1, const float* weight_u,
                           const float* weight_v, const float* SEP_u, const float* SEP_v, const int32_t* AM_u,
                           const int32_t* AM_v, const float* A_u, const float* A_v, const float* gSEP_u,
                           const float* gSEP_v, float* gF1, float* gF2, float* gweight_u, float* gbias_u,
@@ -940,6 +958,7 @@ static int level_backward(const float* F1, const float* F2, int fmaps, float sca
   if (weight_u == nullptr || weight_v == nullptr || gweight_u == nullptr || gbias_u == nullptr || gweight_v == nullptr ||
       gbias_v == nullptr)
     return fail(SFB_ERR_INVALID_ARGUMENT, "attention weights and their gradient buffers must not be NULL");
+  SFB_TRY(check_placement(d, &pl));
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_LEVEL_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -950,21 +969,22 @@ static int level_backward(const float* F1, const float* F2, int fmaps, float sca
     return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, nullptr, w.status, st)
                  : launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st);
   }));
-  const int N1 = d.N1(), K = d.Kc, Kt = 2 + d.Kc;
+  const int N1 = d.N1(), K = d.Kc, Kt = pl.Ktot, c0 = pl.c0;
   // attention gradients: gA_v(b,k,u,p) = sum_v S * gC_v(b,k,v,p), gA_u(b,k,v,p) = sum_u S * gC_u(b,k,u,p), with
   // gC_u = gSEP_v[:, 2:] (per u) and gC_v = gSEP_u[:, 2:] (per v) in the role of the weights
-  SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_channels(gSEP_v, Kt, 2, d.H2, N1),
-                              cf_channels(gSEP_u, Kt, 2, d.W2, N1), 0, 0, 1, cf_view(w.ga_v, K, d.H2, N1),
+  SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_channels(gSEP_v, Kt, c0 + 2, d.H2, N1),
+                              cf_channels(gSEP_u, Kt, c0 + 2, d.W2, N1), 0, 0, 1, cf_view(w.ga_v, K, d.H2, N1),
                               cf_view(w.ga_u, K, d.W2, N1), N1, st));
   // through softmax and Conv3d: parameter gradients, and the total gradients of the max/avg channels
   const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
   SFB_CUDA(timed(KID_ATTENTION_BWD, 2 * attention_backward_launches(K), st, [&] {
-    launch_attention_backward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u, sb_u, weight_u, A_u, w.ga_u, gSEP_u, sb_u,
-                              w.gm_u, gweight_u, gbias_u, w.at_partial, st);
-    return launch_attention_backward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v, sb_v, weight_v, A_v, w.ga_v, gSEP_v,
-                                     sb_v, w.gm_v, gweight_v, gbias_v, w.at_partial, st);
+    const size_t ou = (size_t)c0 * d.W2 * N1, ov = (size_t)c0 * d.H2 * N1;  // first channel of this level
+    launch_attention_backward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u + ou, sb_u, weight_u, A_u, w.ga_u,
+                              gSEP_u + ou, sb_u, w.gm_u, gweight_u, gbias_u, w.at_partial, st);
+    return launch_attention_backward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v + ov, sb_v, weight_v, A_v, w.ga_v,
+                                     gSEP_v + ov, sb_v, w.gm_v, gweight_v, gbias_v, w.at_partial, st);
   }));
-  return run_fused_feature_grads_cf(d, w, AM_u, AM_v, w.gm_v, w.gm_u, A_u, A_v, gSEP_v, gSEP_u, Kt, 2, gF1, gF2, st,
+  return run_fused_feature_grads_cf(d, w, AM_u, AM_v, w.gm_v, w.gm_u, A_u, A_v, gSEP_v, gSEP_u, Kt, c0 + 2, gF1, gF2, st,
                                     fmaps, fmaps ? scale1 : 1.f);
 }
 
@@ -974,20 +994,20 @@ int sfb_separation_level_backward(const float* F1, const float* F2, const float*
                                   float* gF1, float* gF2, float* gweight_u, float* gbias_u, float* gweight_v,
                                   float* gbias_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
                                   void* stream) {
-  return level_backward(F1, F2, 0, 1.f, weight_u, weight_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v, gSEP_u, gSEP_v, gF1, gF2,
-                        gweight_u, gbias_u, gweight_v, gbias_v, shape, workspace, workspace_bytes, stream);
+  return level_backward(Placement{0, 0}, F1, F2, 0, 1.f, weight_u, weight_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v, gSEP_u,
+                        gSEP_v, gF1, gF2, gweight_u, gbias_u, gweight_v, gbias_v, shape, workspace, workspace_bytes, stream);
 }
 
 int sfb_separation_level_backward_fmaps(const float* fmap1, const float* fmap2, float scale1, const float* weight_u,
                                         const float* weight_v, const float* SEP_u, const float* SEP_v,
-                                        const int32_t* AM_u, const int32_t* AM_v, const float* A_u, const float* A_v,
-                                        const float* gSEP_u, const float* gSEP_v, float* gfmap1, float* gfmap2,
-                                        float* gweight_u, float* gbias_u, float* gweight_v, float* gbias_v,
-                                        const sfb_shape* shape, void* workspace, size_t workspace_bytes,
-                                        void* stream) {
-  return level_backward(fmap1, fmap2, 1, scale1, weight_u, weight_v, SEP_u, SEP_v, AM_u, AM_v, A_u, A_v, gSEP_u, gSEP_v,
-                        gfmap1, gfmap2, gweight_u, gbias_u, gweight_v, gbias_v, shape, workspace, workspace_bytes,
-                        stream);
+                                        int32_t sep_channels, int32_t sep_channel0, const int32_t* AM_u,
+                                        const int32_t* AM_v, const float* A_u, const float* A_v, const float* gSEP_u,
+                                        const float* gSEP_v, float* gfmap1, float* gfmap2, float* gweight_u,
+                                        float* gbias_u, float* gweight_v, float* gbias_v, const sfb_shape* shape,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  return level_backward(Placement{sep_channels, sep_channel0}, fmap1, fmap2, 1, scale1, weight_u, weight_v, SEP_u, SEP_v,
+                        AM_u, AM_v, A_u, A_v, gSEP_u, gSEP_v, gfmap1, gfmap2, gweight_u, gbias_u, gweight_v, gbias_v, shape,
+                        workspace, workspace_bytes, stream);
 }
 
 

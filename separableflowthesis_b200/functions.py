@@ -263,14 +263,21 @@ class SeparationPyramidFunction(Function):
             sep_u = torch.empty(B, Kt * L, W1, H1, W1, dtype=fmap1.dtype, device=fmap1.device)
             sep_v = torch.empty(B, Kt * L, H1, H1, W1, dtype=fmap1.dtype, device=fmap1.device)
             for l, fmap2 in enumerate(fmap2_levels):
-                su, sv, am_u, am_v, a_u, a_v = MemorySaver.separation_level_forward(fmap1, fmap2, *params, with_argmax,
-                                                                                    True, scale1)
-                MemorySaver.upsample_displacement_into(su, sep_u, l * Kt)
-                MemorySaver.upsample_displacement_into(sv, sep_v, l * Kt)
-                saved += [su, sv, am_u, am_v, a_u, a_v]
+                if tuple(fmap2.shape[2:]) == (H1, W1):   # displacement range of the output: written in place
+                    su, sv, am_u, am_v, a_u, a_v = MemorySaver.separation_level_forward(
+                        fmap1, fmap2, *params, with_argmax, True, scale1, (sep_u, sep_v, l * Kt))
+                else:
+                    su, sv, am_u, am_v, a_u, a_v = MemorySaver.separation_level_forward(fmap1, fmap2, *params,
+                                                                                        with_argmax, True, scale1)
+                    MemorySaver.upsample_displacement_into(su, sep_u, l * Kt)
+                    MemorySaver.upsample_displacement_into(sv, sep_v, l * Kt)
+                saved.append((su, sv, am_u, am_v, a_u, a_v))
         ctx.with_argmax, ctx.scale1, ctx.levels = with_argmax, scale1, L
         if with_argmax:
-            ctx.save_for_backward(fmap1, weight_u, weight_v, *fmap2_levels, *saved)
+            # volumes written in place are saved as the outputs themselves
+            ctx.in_place = [t[0] is None for t in saved]
+            flat = [x for t in saved for x in t if x is not None]
+            ctx.save_for_backward(fmap1, weight_u, weight_v, sep_u, sep_v, *fmap2_levels, *flat)
         return sep_u, sep_v
 
     @staticmethod
@@ -279,9 +286,9 @@ class SeparationPyramidFunction(Function):
         if not ctx.with_argmax:
             raise NotImplementedError("max avg backward pass is not implemented: use max argmax avg")
         L = ctx.levels
-        fmap1, weight_u, weight_v = ctx.saved_tensors[:3]
-        fmap2_levels = ctx.saved_tensors[3:3 + L]
-        saved = ctx.saved_tensors[3 + L:]
+        fmap1, weight_u, weight_v, sep_u, sep_v = ctx.saved_tensors[:5]
+        fmap2_levels = ctx.saved_tensors[5:5 + L]
+        flat = list(ctx.saved_tensors[5 + L:])
         wu, wv = weight_u.contiguous(), weight_v.contiguous()
         gu, gv = grad_sep_u.contiguous(), grad_sep_v.contiguous()
         Kt = 2 + weight_u.shape[0]
@@ -289,11 +296,18 @@ class SeparationPyramidFunction(Function):
         g2 = []
         with torch.cuda.device_of(gu):
             for l in range(L):
-                su, sv, am_u, am_v, a_u, a_v = saved[6 * l:6 * l + 6]
-                gsu = MemorySaver.upsample_displacement_backward(gu, l * Kt, Kt, su.shape[2])
-                gsv = MemorySaver.upsample_displacement_backward(gv, l * Kt, Kt, sv.shape[2])
-                out = MemorySaver.separation_level_backward(fmap1, fmap2_levels[l], wu, wv, su, sv, am_u, am_v, a_u, a_v,
-                                                            gsu, gsv, True, ctx.scale1)
+                if ctx.in_place[l]:
+                    am_u, am_v, a_u, a_v = flat[:4]
+                    del flat[:4]
+                    out = MemorySaver.separation_level_backward(fmap1, fmap2_levels[l], wu, wv, sep_u, sep_v, am_u, am_v,
+                                                                a_u, a_v, gu, gv, True, ctx.scale1, l * Kt)
+                else:
+                    su, sv, am_u, am_v, a_u, a_v = flat[:6]
+                    del flat[:6]
+                    gsu = MemorySaver.upsample_displacement_backward(gu, l * Kt, Kt, su.shape[2])
+                    gsv = MemorySaver.upsample_displacement_backward(gv, l * Kt, Kt, sv.shape[2])
+                    out = MemorySaver.separation_level_backward(fmap1, fmap2_levels[l], wu, wv, su, sv, am_u, am_v, a_u,
+                                                                a_v, gsu, gsv, True, ctx.scale1)
                 g2.append(out[1])
                 if l == 0:
                     g1, gw_u, gb_u, gw_v, gb_v = out[0], out[2], out[3], out[4], out[5]

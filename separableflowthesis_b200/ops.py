@@ -62,6 +62,8 @@ def _workspace(nbytes: int, device: torch.device, stream: int) -> torch.Tensor:
 def _ptr(t):
     if isinstance(t, float):
         return ctypes.c_float(t)
+    if isinstance(t, int):
+        return ctypes.c_int32(t)
     return ctypes.c_void_p(t.data_ptr() if t is not None else None)
 
 
@@ -377,12 +379,14 @@ def _check_fmaps(fmap1: torch.Tensor, fmap2: torch.Tensor) -> _lib.SfbShape:
 
 
 def separation_level_forward(img1_features_l0, img2_features_lk, weight_u, bias_u, weight_v, bias_v,
-                             with_argmax=True, fmaps=False, scale1=1.0) -> List[torch.Tensor]:
+                             with_argmax=True, fmaps=False, scale1=1.0, place=None) -> List[torch.Tensor]:
     """One pyramid level of the call site (core/corr.py:419-457 up to the upsampling):
     [sep_u (B,2+Kc,W2,H1,W1), sep_v (B,2+Kc,H2,H1,W1), am_u, am_v, a_u (B,Kc,W2,H1,W1), a_v (B,Kc,H2,H1,W1)];
     (weight_u, bias_u) are the parameters of the reference's ``attention1``, which acts on sep_u.
     With ``fmaps`` the two feature arguments are the model's maps (B,C,H,W) and image 1's is multiplied by
-    ``scale1`` inside the library (the permute + division of core/corr.py:419-422)."""
+    ``scale1`` inside the library (the permute + division of core/corr.py:419-422).  ``place`` = (sep_u_all,
+    sep_v_all, c0) (fmaps only) writes the volumes into channels c0.. of those larger contiguous tensors (the
+    concatenation over pyramid levels, core/corr.py:473-475) and returns None in their place."""
     F1, F2 = img1_features_l0, img2_features_lk
     s = _check_fmaps(F1, F2) if fmaps else _check_pair(F1, F2)
     dev = F1.device
@@ -390,25 +394,47 @@ def separation_level_forward(img1_features_l0, img2_features_lk, weight_u, bias_
     if _check_attention_params(weight_v, bias_v, "attention2", dev) != s.Kc:
         raise RuntimeError("attention1 and attention2 must have the same number of output channels")
     f32 = dict(dtype=torch.float32, device=dev)
-    sep_u = torch.empty(s.B, 2 + s.Kc, s.W2, s.H1, s.W1, **f32)
-    sep_v = torch.empty(s.B, 2 + s.Kc, s.H2, s.H1, s.W1, **f32)
+    Ktot = c0 = 0
+    if place is not None:
+        if not fmaps:
+            raise RuntimeError("place needs fmaps=True")
+        sep_u, sep_v, c0 = place
+        Ktot = _check_placed(s, sep_u, sep_v, c0, dev, "sep")
+    else:
+        sep_u = torch.empty(s.B, 2 + s.Kc, s.W2, s.H1, s.W1, **f32)
+        sep_v = torch.empty(s.B, 2 + s.Kc, s.H2, s.H1, s.W1, **f32)
     am_u = torch.empty(s.B, s.H2, s.H1, s.W1, dtype=torch.int32, device=dev) if with_argmax else None
     am_v = torch.empty(s.B, s.W2, s.H1, s.W1, dtype=torch.int32, device=dev) if with_argmax else None
     a_u = torch.empty(s.B, s.Kc, s.W2, s.H1, s.W1, **f32)
     a_v = torch.empty(s.B, s.Kc, s.H2, s.H1, s.W1, **f32)
     if fmaps:
         _call("sfb_separation_level_forward_fmaps", _lib.OP_SEPARATION_LEVEL_FORWARD, s, dev,
-              (F1, F2, float(scale1), weight_u, bias_u, weight_v, bias_v, sep_u, sep_v, am_u, am_v, a_u, a_v))
+              (F1, F2, float(scale1), weight_u, bias_u, weight_v, bias_v, sep_u, sep_v, int(Ktot), int(c0), am_u, am_v,
+               a_u, a_v))
+        if place is not None:
+            return [None, None, am_u, am_v, a_u, a_v]
     else:
         _call("sfb_separation_level_forward", _lib.OP_SEPARATION_LEVEL_FORWARD, s, dev,
               (F1, F2, weight_u, bias_u, weight_v, bias_v, sep_u, sep_v, am_u, am_v, a_u, a_v))
     return [sep_u, sep_v, am_u, am_v, a_u, a_v]
 
 
+def _check_placed(s, t_u, t_v, c0, dev, name):
+    """Larger tensors (B,Ktot,D,H1,W1) holding this level's 2+Kc channels from channel c0; returns Ktot."""
+    _check(t_u, name + "_u", torch.float32, 5)
+    Ktot = t_u.shape[1]
+    _check_like(t_u, name + "_u", (s.B, Ktot, s.W2, s.H1, s.W1), torch.float32, dev)
+    _check_like(t_v, name + "_v", (s.B, Ktot, s.H2, s.H1, s.W1), torch.float32, dev)
+    if c0 < 0 or c0 + 2 + s.Kc > Ktot:
+        raise RuntimeError(f"channels {c0}..{c0 + 2 + s.Kc} do not fit in {Ktot}")
+    return Ktot
+
+
 def separation_level_backward(img1_features_l0, img2_features_lk, weight_u, weight_v, sep_u, sep_v, am_u, am_v,
-                              a_u, a_v, g_sep_u, g_sep_v, fmaps=False, scale1=1.0) -> List[torch.Tensor]:
+                              a_u, a_v, g_sep_u, g_sep_v, fmaps=False, scale1=1.0, c0=None) -> List[torch.Tensor]:
     """[gF1, gF2, gweight_u, gbias_u, gweight_v, gbias_v] of ``separation_level_forward`` (feature gradients in the
-    layout of the feature arguments)."""
+    layout of the feature arguments).  With ``c0`` (fmaps only) sep_u, sep_v, g_sep_u, g_sep_v are the larger
+    tensors of a forward with ``place`` and the level occupies their channels c0.. ."""
     F1, F2 = img1_features_l0, img2_features_lk
     s = _check_fmaps(F1, F2) if fmaps else _check_pair(F1, F2)
     dev = F1.device
@@ -417,9 +443,17 @@ def separation_level_backward(img1_features_l0, img2_features_lk, weight_u, weig
     _check_like(weight_v, "attention2.weight", (s.Kc, 2, 3, 3, 3), torch.float32, dev)
     _check_like(am_u, "argmax_u", (s.B, s.H2, s.H1, s.W1), torch.int32, dev)
     _check_like(am_v, "argmax_v", (s.B, s.W2, s.H1, s.W1), torch.int32, dev)
-    for t, name, D in ((sep_u, "sep_u", s.W2), (sep_v, "sep_v", s.H2), (g_sep_u, "grad_sep_u", s.W2),
-                       (g_sep_v, "grad_sep_v", s.H2)):
-        _check_like(t, name, (s.B, 2 + s.Kc, D, s.H1, s.W1), torch.float32, dev)
+    Ktot = 0
+    if c0 is not None:
+        if not fmaps:
+            raise RuntimeError("c0 needs fmaps=True")
+        Ktot = _check_placed(s, sep_u, sep_v, c0, dev, "sep")
+        if _check_placed(s, g_sep_u, g_sep_v, c0, dev, "grad_sep") != Ktot:
+            raise RuntimeError("sep and grad_sep have different channel counts")
+    else:
+        for t, name, D in ((sep_u, "sep_u", s.W2), (sep_v, "sep_v", s.H2), (g_sep_u, "grad_sep_u", s.W2),
+                           (g_sep_v, "grad_sep_v", s.H2)):
+            _check_like(t, name, (s.B, 2 + s.Kc, D, s.H1, s.W1), torch.float32, dev)
     gF1 = torch.empty_like(F1)
     gF2 = torch.empty_like(F2)
     gw_u, gw_v = torch.empty_like(weight_u), torch.empty_like(weight_v)
@@ -427,9 +461,10 @@ def separation_level_backward(img1_features_l0, img2_features_lk, weight_u, weig
     gb_v = torch.empty(s.Kc, dtype=torch.float32, device=dev)
     name = "sfb_separation_level_backward_fmaps" if fmaps else "sfb_separation_level_backward"
     head = (F1, F2, float(scale1)) if fmaps else (F1, F2)
+    place = (int(Ktot), int(c0 or 0)) if fmaps else ()
     _call(name, _lib.OP_SEPARATION_LEVEL_BACKWARD, s, dev,
-          head + (weight_u, weight_v, sep_u, sep_v, am_u, am_v, a_u, a_v, g_sep_u, g_sep_v, gF1, gF2, gw_u, gb_u,
-                  gw_v, gb_v))
+          head + (weight_u, weight_v, sep_u, sep_v) + place + (am_u, am_v, a_u, a_v, g_sep_u, g_sep_v, gF1, gF2, gw_u,
+                                                               gb_u, gw_v, gb_v))
     return [gF1, gF2, gw_u, gb_u, gw_v, gb_v]
 
 

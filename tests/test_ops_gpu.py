@@ -283,6 +283,22 @@ def test_separation_level(shape, cuda_device):
     assert outm[0].shape == fmap1.shape and outm[1].shape == fmap2.shape
     assert relerr(outm[0], rm[0]) < TOL and relerr(outm[1], rm[1]) < TOL
     assert relerr(outm[2], rm[2]) < TOL and relerr(outm[4], rm[4]) < TOL
+    # ... and written into / read from channels 3.. of larger tensors (the concatenation over pyramid levels)
+    Kt, Ktot, c0 = 2 + Kc, 2 + Kc + 4, 3
+    big_u = torch.full((B, Ktot, W2, H1, W1), 5.0, device=dev)
+    big_v = torch.full((B, Ktot, H2, H1, W1), 5.0, device=dev)
+    fp = ops.separation_level_forward(fmap1.to(dev), fmap2.to(dev), wu, bu, wv, bv, fmaps=True, scale1=scale,
+                                      place=(big_u, big_v, c0))
+    assert fp[0] is None and torch.equal(big_u[:, c0:c0 + Kt], fw[0]) and torch.equal(big_v[:, c0:c0 + Kt], fw[1])
+    assert (big_u[:, :c0] == 5.0).all() and (big_u[:, c0 + Kt:] == 5.0).all()
+    gbig_u = torch.zeros_like(big_u)
+    gbig_v = torch.zeros_like(big_v)
+    gbig_u[:, c0:c0 + Kt] = g_sep_u.to(dev)
+    gbig_v[:, c0:c0 + Kt] = g_sep_v.to(dev)
+    outp = ops.separation_level_backward(fmap1.to(dev), fmap2.to(dev), wu, wv, big_u, big_v, fp[2], fp[3], fp[4], fp[5],
+                                         gbig_u, gbig_v, fmaps=True, scale1=scale, c0=c0)
+    for x, y in zip(outp, outm):
+        assert torch.equal(x, y)
 
 
 # positions pass through grid_sample's normalisation and back in float32, as in the reference's own float32 run:
