@@ -187,17 +187,28 @@ def run_ops(ms, cfg, job, fused=True):
     return out
 
 
-def launches_per_step(cfg) -> int:
-    """Kernels of this library launched by one step (the prepare step is 2 rounding copies, plus the
-    F2 mean rows for the max/avg forward)."""
-    n = 3 + 1                                   # max/avg forward: prepare(3) + sweep
+def launches_per_step(cfg, path="ops") -> int:
+    """Kernels of this library launched by one step, from the op list (used only when the library's own count
+    from the timing pass is not available)."""
     sweeps = (cfg["Kc"] + 3) // 4
+    if path == "level":
+        # forward: prepare 3, max/avg sweep, 2 attention modules x chunks, compression sweeps
+        n = 3 + 1 + 2 * sweeps + sweeps
+        if cfg["bwd"]:
+            # prepare 2, attention-gradient sweeps, 2 x (logit chunks + input-grad chunks + weight grad + 2 reductions),
+            # 4 interleave packs, 2 gradient GEMMs (+ 2 packs and 2 GEMMs per further chunk of 4 channels)
+            n += 2 + sweeps + 2 * (2 * sweeps + 3) + 4 + 2 + 4 * (sweeps - 1)
+        return n
+    n = 3 + 1 + 2                               # max/avg forward: prepare(3) + sweep + unpack(2)
+    if cfg["bwd"]:
+        n += 2                                  # argmax unpack
     if cfg["Kc"] > 0:
-        n += 2 + sweeps                         # compression forward
+        n += 2 + 2 + sweeps + 2                 # compression forward: prepare, pack, sweep(s), unpack
     if cfg["bwd"]:
         if cfg["Kc"] > 0:
-            n += 2 + sweeps + 2                 # compression backward: prepare, sweep(s), 2 gradient GEMMs
-        n += 2 + 2                              # max/avg backward: prepare, 2 gradient GEMMs
+            n += 2 + 2 + sweeps + 2 + 4 + 2     # one-call backward: prepare, pack, sweeps, unpack, interleave, 2 GEMMs
+        else:
+            n += 2 + 2 + 2                      # max/avg backward: prepare, interleave, 2 GEMMs
     return n
 
 
@@ -564,7 +575,7 @@ def main():
         _lib.kernel_timing(False)
     roofline, kernels = None, []
     # kernels of this library per step: counted by the library when the timing pass ran, else from the op list
-    launches = (sum(r[2] for r in report) // min(args.steps, 3)) if report else launches_per_step(cfg)
+    launches = (sum(r[2] for r in report) // min(args.steps, 3)) if report else launches_per_step(cfg, path)
     if rank == 0 and report:
         tot = sum(r[1] for r in report)
         kernels = [{"kernel": n, "launches": l, "ms_per_launch": t / l, "share": t / tot} for n, t, l in report]
