@@ -122,9 +122,12 @@ def make_job(cfg, shard, device, path="ops"):
     g = torch.Generator().manual_seed(SEED)
     f1 = torch.randn(B, C_FEAT, H, W, generator=g)
     f2 = torch.randn(B, C_FEAT, H, W, generator=g)
+    from separableflowthesis_b200 import sharding as _sh
+    e0, e1, _, _ = _sh.halo_range(shard, H)     # row shards: plus one halo row per side for the attention stencil
+    f1_ext = f1[shard.b0:shard.b1, :, e0:e1].contiguous()
     f1 = f1[shard.b0:shard.b1, :, shard.r0:shard.r1].contiguous()
     f2 = f2[shard.b0:shard.b1].contiguous()
-    job = {"f1_nchw": f1, "f2_nchw": f2}
+    job = {"f1_nchw": f1_ext, "f2_nchw": f2}
     F1 = (f1.permute(0, 2, 3, 1).contiguous() / C_FEAT ** 0.5).to(device)
     F2 = f2.permute(0, 2, 3, 1).contiguous().to(device)
     b, h = F1.shape[0], F1.shape[1]
@@ -287,11 +290,12 @@ class E2E:
     AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
     gradients -> loss-sized results back on the host."""
 
-    def __init__(self, cfg, job, device, chunks=1, levels=1):
+    def __init__(self, cfg, job, device, chunks=1, levels=1, shard=None, row_group=None):
         import separableflowthesis_b200 as sfb
         self.sfb, self.cfg, self.device = sfb, cfg, device
-        self.chunks = chunks
+        self.chunks = chunks if shard is None or shard.g_rows == 1 else 1
         self.levels = levels
+        self.shard, self.row_group = shard, row_group
         self.copy_stream = torch.cuda.Stream(device=device)
         self.h1 = job["f1_nchw"].pin_memory()
         self.h2 = job["f2_nchw"].pin_memory()
@@ -340,6 +344,11 @@ class E2E:
             blk = self.sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=self.levels, support_backward=cfg["bwd"])
             with torch.set_grad_enabled(cfg["bwd"]):
                 sep_u, sep_v = blk(None, sep=True, attention_weights=tuple(self.att) if self.att else None)
+            sharded_rows = self.shard is not None and self.shard.g_rows > 1
+            if sharded_rows:   # computed on the block plus halo rows: keep this rank's own image-1 rows
+                from separableflowthesis_b200 import sharding
+                sep_u = sharding.interior(sep_u, self.shard, cfg["H"], 3)
+                sep_v = sharding.interior(sep_v, self.shard, cfg["H"], 3)
             if cfg["bwd"]:
                 if self.up is None:
                     gd = torch.Generator(device=dev).manual_seed(SEED + 7)
@@ -348,7 +357,11 @@ class E2E:
                     self.up = (torch.randn(shape_u, generator=gd, device=dev),
                                torch.randn(shape_v, generator=gd, device=dev))
                 torch.autograd.backward([sep_u, sep_v], [self.up[0][b0:b1], self.up[1][b0:b1]])
-                pieces += [f1.grad.sum().reshape(1), f2.grad.sum().reshape(1)]
+                g1, g2 = f1.grad, f2.grad
+                if sharded_rows:   # halo rows of gF1 go to the neighbouring shards, gF2 is summed over the row group
+                    g1 = sharding.exchange_halo_grads(g1, self.shard, cfg["H"], self.row_group, dim=2)
+                    g2 = sharding.reduce_row_partial(g2, self.row_group)
+                pieces += [g1.sum().reshape(1), g2.sum().reshape(1)]
             else:
                 pieces += [sep_u.sum().reshape(1), sep_v.sum().reshape(1)]
             keep.append((f1, f2))
@@ -513,6 +526,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     shard = sharding.make_shard(cfg["B"], cfg["H"], world, rank)
+    row_group = sharding.new_row_groups(world, shard.g_rows) if world > 1 else None
     path = args.path
     if path == "lookup":   # the lookup on the aggregated volumes (next component after the separation), one GPU
         if rank == 0:
@@ -600,7 +614,7 @@ def main():
     # ---- end to end through the public API with host buffers ----
     e2e = None
     if not args.no_e2e:
-        runner = E2E(cfg, job, device, chunks=args.e2e_chunks, levels=args.levels)
+        runner = E2E(cfg, job, device, chunks=args.e2e_chunks, levels=args.levels, shard=shard, row_group=row_group)
         for _ in range(min(args.warmup, 3)):
             runner.step()
         barrier()

@@ -106,6 +106,7 @@ class AlternateCorrBlockSepflow:
         """All levels, each trilinearly resampled to the level-0 displacement range and concatenated
         over channels: sep_u (B, K*levels, W, H, W), sep_v (B, K*levels, H, H, W) (core/corr.py:384-477)."""
         batch, fdim, h1, w1 = self.fmap1_l0.shape
+        h2, w2 = self.pyramid[0].shape[2:]
         if self._one_node_per_level(attention_weights) and self.num_levels > 1:
             # one node for the whole pyramid: levels are resampled along the displacement axis and written into
             # their channel slices of the outputs by the library (no F.interpolate, no torch.cat)
@@ -119,11 +120,13 @@ class AlternateCorrBlockSepflow:
         sep_u_lvls, sep_v_lvls = [], []
         for level in range(self.num_levels):
             sep_u, sep_v = self.separate_level(F1, level, attention_weights)
-            # align_corners resampling to the size a tensor already has copies it: skip
-            if sep_u.shape[2] != w1:
-                sep_u = F.interpolate(sep_u, [w1, h1, w1], mode="trilinear", align_corners=True)
-            if sep_v.shape[2] != h1:
-                sep_v = F.interpolate(sep_v, [h1, h1, w1], mode="trilinear", align_corners=True)
+            # align_corners resampling to the size a tensor already has copies it: skip.  The target displacement
+            # ranges are those of level 0 of image 2 (the reference writes [w1, h1, w1] / [h1, h1, w1], the same
+            # thing for its equally sized images; with image-1 rows sharded over ranks only image 2 has them all).
+            if sep_u.shape[2] != w2:
+                sep_u = F.interpolate(sep_u, [w2, h1, w1], mode="trilinear", align_corners=True)
+            if sep_v.shape[2] != h2:
+                sep_v = F.interpolate(sep_v, [h2, h1, w1], mode="trilinear", align_corners=True)
             sep_u_lvls.append(sep_u)
             sep_v_lvls.append(sep_v)
         if self.num_levels == 1:

@@ -257,13 +257,14 @@ class SeparationPyramidFunction(Function):
         assert fmap1.is_contiguous() and all(f.is_contiguous() for f in fmap2_levels)
         params = [t.contiguous() for t in (weight_u, bias_u, weight_v, bias_v)]
         B, _, H1, W1 = fmap1.shape
+        H2, W2 = fmap2_levels[0].shape[2:]     # displacement ranges of the outputs (= H1, W1 unless image-1 rows are sharded)
         L, Kt = len(fmap2_levels), 2 + weight_u.shape[0]
         saved = []
         with torch.cuda.device_of(fmap1):
-            sep_u = torch.empty(B, Kt * L, W1, H1, W1, dtype=fmap1.dtype, device=fmap1.device)
-            sep_v = torch.empty(B, Kt * L, H1, H1, W1, dtype=fmap1.dtype, device=fmap1.device)
+            sep_u = torch.empty(B, Kt * L, W2, H1, W1, dtype=fmap1.dtype, device=fmap1.device)
+            sep_v = torch.empty(B, Kt * L, H2, H1, W1, dtype=fmap1.dtype, device=fmap1.device)
             for l, fmap2 in enumerate(fmap2_levels):
-                if tuple(fmap2.shape[2:]) == (H1, W1):   # displacement range of the output: written in place
+                if tuple(fmap2.shape[2:]) == (H2, W2):   # displacement range of the output: written in place
                     su, sv, am_u, am_v, a_u, a_v = MemorySaver.separation_level_forward(
                         fmap1, fmap2, *params, with_argmax, True, scale1, (sep_u, sep_v, l * Kt))
                 else:

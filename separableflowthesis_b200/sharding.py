@@ -9,7 +9,13 @@ So a job of B samples with H1 image-1 rows is split into ``G_batch x G_rows`` sh
 * the parameters of the two attention Conv3d modules are shared by everything, so their gradients
   are summed over all ranks (what DistributedDataParallel does in the reference, train.py:397).
 
-Only these two reductions use the process group (NCCL on GPUs, gloo in the CPU tests).
+* the attention modules are 3x3x3 convolutions over (displacement, h1, w1), so a row shard needs the max/avg
+  channels of one image-1 row above and below its block.  They are recomputed, not exchanged: a row shard runs
+  on its block extended by one halo row per side (``halo_range``) and keeps the interior of the outputs; in the
+  backward the halo rows of its feature gradient belong to the neighbouring shards and are handed over
+  (``exchange_halo_grads``).
+
+Only these reductions / exchanges use the process group (NCCL on GPUs, gloo in the CPU tests).
 """
 from __future__ import annotations
 
@@ -97,3 +103,41 @@ def reduce_parameter_grads(params: Iterable[torch.nn.Parameter], group=None) -> 
         p.grad.copy_(flat[off:off + n].view_as(p.grad))
         off += n
     return flat
+
+
+def halo_range(shard: Shard, H1: int):
+    """Image-1 rows a row shard computes on: its block plus one row per side (inside the image), so that the
+    attention stencil sees true neighbours at the shard borders.  Returns (e0, e1, i0, i1): rows [e0, e1) of the
+    image, and the shard's own rows as [i0, i1) inside that extended block.  Without row sharding nothing is added."""
+    if shard.g_rows == 1:
+        return shard.r0, shard.r1, 0, shard.r1 - shard.r0
+    e0, e1 = max(shard.r0 - 1, 0), min(shard.r1 + 1, H1)
+    return e0, e1, shard.r0 - e0, shard.r1 - e0
+
+
+def interior(t: torch.Tensor, shard: Shard, H1: int, dim: int) -> torch.Tensor:
+    """The shard's own image-1 rows of a tensor computed on the extended block (rows along ``dim``)."""
+    _, _, i0, i1 = halo_range(shard, H1)
+    return t.narrow(dim, i0, i1 - i0)
+
+
+def exchange_halo_grads(g_ext: torch.Tensor, shard: Shard, H1: int, row_group, dim: int = 2) -> torch.Tensor:
+    """Feature gradient of the shard's own rows from the gradient on its extended block ``g_ext`` (image-1 rows
+    along ``dim``): the interior, plus what the neighbouring shards computed for this shard's first and last row in
+    their halos.  One small all-gather (two rows per rank) inside the row group."""
+    e0, e1, i0, i1 = halo_range(shard, H1)
+    own = g_ext.narrow(dim, i0, i1 - i0).clone()
+    if shard.g_rows == 1:
+        return own
+    zero_row = torch.zeros_like(g_ext.narrow(dim, 0, 1))
+    top = g_ext.narrow(dim, 0, 1) if i0 > 0 else zero_row                       # belongs to the shard above
+    bottom = g_ext.narrow(dim, g_ext.shape[dim] - 1, 1) if e1 > shard.r1 else zero_row   # ... below
+    mine = torch.cat((top, bottom), dim=dim).contiguous()
+    gathered = [torch.empty_like(mine) for _ in range(shard.g_rows)]
+    dist.all_gather(gathered, mine, group=row_group)
+    ri = shard.rank % shard.g_rows
+    if ri > 0:             # the shard above sent its bottom halo row = my first row
+        own.narrow(dim, 0, 1).add_(gathered[ri - 1].narrow(dim, 1, 1))
+    if ri < shard.g_rows - 1:   # the shard below sent its top halo row = my last row
+        own.narrow(dim, own.shape[dim] - 1, 1).add_(gathered[ri + 1].narrow(dim, 0, 1))
+    return own

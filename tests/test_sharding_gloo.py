@@ -85,3 +85,71 @@ def test_two_rank_sharded_backward_matches_unsharded(B):
         p.join(120)
         assert p.exitcode == 0
     assert all(results.get(r) for r in range(world)), dict(results)
+
+
+def _halo_worker(rank, world, port, results):
+    """Row-sharded call site with halo rows against the unsharded one: outputs of the shard's rows, feature
+    gradients (halo rows handed to the neighbour, gF2 summed over the row group) and attention-parameter gradients."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import separableflowthesis_b200 as sfb
+        from separableflowthesis_b200 import functions
+        functions.MemorySaver = orc                      # the oracle stands in for the CUDA ops
+        torch.manual_seed(5)
+        B, C, H, W, Kc = 1, 8, 7, 6, 2
+        g = torch.Generator().manual_seed(3)
+        f1 = torch.randn(B, C, H, W, generator=g, dtype=torch.float64)
+        f2 = torch.randn(B, C, H, W, generator=g, dtype=torch.float64)
+        convs = [torch.nn.Conv3d(2, Kc, 3, padding=1).double() for _ in range(2)]
+        up_u = torch.randn(B, (2 + Kc) * 2, W, H, W, generator=g, dtype=torch.float64)
+        up_v = torch.randn(B, (2 + Kc) * 2, H, H, W, generator=g, dtype=torch.float64)
+
+        def run(f1_rows, f2_all, rows):
+            a = f1_rows.clone().requires_grad_(True)
+            b = f2_all.clone().requires_grad_(True)
+            for c in convs:
+                c.zero_grad()
+            blk = sfb.AlternateCorrBlockSepflow(a, b, None, num_levels=2, support_backward=True)
+            su, sv = blk(None, sep=True, attention_weights=tuple(convs))
+            return a, b, su, sv
+
+        # unsharded reference
+        a, b, su, sv = run(f1, f2, slice(0, H))
+        ((su * up_u).sum() + (sv * up_v).sum()).backward()
+        ref = dict(su=su.detach(), sv=sv.detach(), g1=a.grad.clone(), g2=b.grad.clone(),
+                   gw=[c.weight.grad.clone() for c in convs])
+
+        sh = sharding.make_shard(B, H, world, rank)
+        grp = sharding.new_row_groups(world, sh.g_rows)
+        e0, e1, i0, i1 = sharding.halo_range(sh, H)
+        a, b, su, sv = run(f1[:, :, e0:e1].contiguous(), f2, None)
+        su_own = sharding.interior(su, sh, H, 3)
+        sv_own = sharding.interior(sv, sh, H, 3)
+        ok = torch.allclose(su_own, ref["su"][:, :, :, sh.r0:sh.r1], atol=1e-12)
+        ok = ok and torch.allclose(sv_own, ref["sv"][:, :, :, sh.r0:sh.r1], atol=1e-12)
+        ((su_own * up_u[:, :, :, sh.r0:sh.r1]).sum() + (sv_own * up_v[:, :, :, sh.r0:sh.r1]).sum()).backward()
+        g1 = sharding.exchange_halo_grads(a.grad, sh, H, grp, dim=2)
+        g2 = sharding.reduce_row_partial(b.grad, grp)
+        sharding.reduce_parameter_grads([p for c in convs for p in c.parameters()])
+        ok = ok and torch.allclose(g1, ref["g1"][:, :, sh.r0:sh.r1], atol=1e-11)
+        ok = ok and torch.allclose(g2, ref["g2"], atol=1e-11)
+        ok = ok and all(torch.allclose(c.weight.grad, w, atol=1e-11) for c, w in zip(convs, ref["gw"]))
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_row_shards_with_halo_rows_match_the_unsharded_call_site(world):
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_halo_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert all(results.get(r) for r in range(world)), dict(results)
