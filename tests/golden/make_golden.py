@@ -179,4 +179,6 @@ def lookup_vectors():
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/SeparableFlowThesis")
+    main(sys.argv[1])
