@@ -128,17 +128,25 @@ def make_job(cfg, shard, device, path="ops"):
     f1 = f1[shard.b0:shard.b1, :, shard.r0:shard.r1].contiguous()
     f2 = f2[shard.b0:shard.b1].contiguous()
     job = {"f1_nchw": f1_ext, "f2_nchw": f2}
+    if path == "level":
+        f1 = f1_ext      # the level calls of a row shard run on the block plus its halo rows
     F1 = (f1.permute(0, 2, 3, 1).contiguous() / C_FEAT ** 0.5).to(device)
     F2 = f2.permute(0, 2, 3, 1).contiguous().to(device)
     b, h = F1.shape[0], F1.shape[1]
     gd = torch.Generator(device=device).manual_seed(SEED + 1 + shard.rank)
     job.update(F1=F1, F2=F2)
-    job["cells"] = b * h * W * H * W
+    job["cells"] = b * (shard.r1 - shard.r0) * W * H * W
     if path == "level":
         job["att"] = attention_parameters(Kc, device)
         if cfg["bwd"]:
             job["gSEP_u"] = torch.randn(b, 2 + Kc, W, h, W, generator=gd, device=device)
             job["gSEP_v"] = torch.randn(b, 2 + Kc, H, h, W, generator=gd, device=device)
+            if shard.g_rows > 1:   # the outputs of halo rows are not used: no upstream gradient there
+                _, _, i0, i1 = _sh.halo_range(shard, H)
+                for t in (job["gSEP_u"], job["gSEP_v"]):
+                    t[:, :, :, :i0] = 0
+                    t[:, :, :, i1:] = 0
+        job["shard"] = shard
         return job
     if Kc > 0:
         job["A_u"] = torch.randn(b, h, W, Kc, W, generator=gd, device=device).softmax(-1)
@@ -152,25 +160,32 @@ def make_job(cfg, shard, device, path="ops"):
     return job
 
 
-def run_level(ms, cfg, job):
+def run_level(ms, cfg, job, row_group=None):
     """The hot path on device-resident inputs as the call site runs it: one library call for the level's
-    forward (max/avg sweep, attention weights, compression sweep) and one for its backward."""
+    forward (max/avg sweep, attention weights, compression sweep) and one for its backward.  Row shards then sum
+    gF2 over their group and hand the halo rows of gF1 to their neighbours."""
     F1, F2 = job["F1"], job["F2"]
     wu, bu, wv, bv = job["att"]
     out = ms.separation_level_forward(F1, F2, wu, bu, wv, bv, with_argmax=cfg["bwd"])
     if cfg["bwd"]:
         sep_u, sep_v, am_u, am_v, a_u, a_v = out
-        out = out + ms.separation_level_backward(F1, F2, wu, wv, sep_u, sep_v, am_u, am_v, a_u, a_v, job["gSEP_u"],
-                                                 job["gSEP_v"])
+        grads = ms.separation_level_backward(F1, F2, wu, wv, sep_u, sep_v, am_u, am_v, a_u, a_v, job["gSEP_u"],
+                                              job["gSEP_v"])
+        shard = job["shard"]
+        if shard.g_rows > 1:
+            from separableflowthesis_b200 import sharding
+            grads[0] = sharding.exchange_halo_grads(grads[0], shard, cfg["H"], row_group, dim=1)
+            grads[1] = sharding.reduce_row_partial(grads[1], row_group)
+        out = out + grads
     return out
 
 
-def run_ops(ms, cfg, job, fused=True):
+def run_ops(ms, cfg, job, fused=True, row_group=None):
     """The hot path on device-resident inputs through the five ops of the reference's module (random softmaxed
     attention weights stand in for the Conv3d modules the call site runs between them).  With `fused` the two
     backward ops run as the library's one-call backward (same outputs; feature gradients arrive summed)."""
     if "att" in job:
-        return run_level(ms, cfg, job)
+        return run_level(ms, cfg, job, row_group)
     F1, F2 = job["F1"], job["F2"]
     if cfg["bwd"]:
         MA_u, MA_v, AM_u, AM_v = ms.max_argmax_avg_forward(F1, F2)
@@ -488,6 +503,10 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=2,
                     help="micro-batches per end-to-end step (the host->device copy of one overlaps the compute of the "
                          "previous one); 1 = copy everything, then compute")
+    ap.add_argument("--shard", default="batch", choices=["batch", "rows"],
+                    help="batch: samples first, image-1 rows for what is left (no data-path exchange when the batch "
+                         "is a multiple of the GPUs); rows: every rank gets all samples and a block of image-1 rows "
+                         "plus a halo row per side, gF2 is summed and halo-row gradients exchanged over NCCL")
     ap.add_argument("--levels", type=int, default=1,
                     help="pyramid levels of the end-to-end block (the metric counts level-0 cells; the reference's "
                          "model uses 4 levels = 1.33x the cells)")
@@ -525,7 +544,7 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    shard = sharding.make_shard(cfg["B"], cfg["H"], world, rank)
+    shard = sharding.make_shard(cfg["B"], cfg["H"], world, rank, prefer=args.shard)
     row_group = sharding.new_row_groups(world, shard.g_rows) if world > 1 else None
     path = args.path
     if path == "lookup":   # the lookup on the aggregated volumes (next component after the separation), one GPU
@@ -536,10 +555,9 @@ def main():
             dist.destroy_process_group()
         return
     if path == "auto":
-        path = "level" if cfg["Kc"] > 0 and shard.g_rows == 1 and not args.unfused else "ops"
-    if path == "level" and (cfg["Kc"] == 0 or shard.g_rows > 1):
-        raise SystemExit("--path level needs attention channels and whole image-1 rows per rank (the 3x3x3 "
-                         "attention stencil crosses row shards)")
+        path = "level" if cfg["Kc"] > 0 and not args.unfused else "ops"
+    if path == "level" and cfg["Kc"] == 0:
+        raise SystemExit("--path level needs attention channels")
     job = make_job(cfg, shard, device, path)
 
     def barrier():
@@ -563,14 +581,14 @@ def main():
 
     # ---- device-resident throughput ("value") ----
     for _ in range(args.warmup):
-        run_ops(ms, cfg, job, not args.unfused)
+        run_ops(ms, cfg, job, not args.unfused, row_group)
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     for _ in range(args.steps):
-        run_ops(ms, cfg, job, not args.unfused)
+        run_ops(ms, cfg, job, not args.unfused, row_group)
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
@@ -583,7 +601,7 @@ def main():
     if not args.no_roofline:
         _lib.kernel_timing(True)
         for _ in range(min(args.steps, 3)):
-            run_ops(ms, cfg, job, not args.unfused)
+            run_ops(ms, cfg, job, not args.unfused, row_group)
         torch.cuda.synchronize()
         report = _lib.kernel_timing_report()
         _lib.kernel_timing(False)

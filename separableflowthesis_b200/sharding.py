@@ -51,11 +51,16 @@ def split_range(n: int, parts: int, index: int):
     return start, start + base + (1 if index < extra else 0)
 
 
-def make_shard(B: int, H1: int, world_size: int, rank: int) -> Shard:
-    """Batch first, rows for what is left: G_batch = gcd(B, world_size), G_rows = world_size / G_batch."""
+def make_shard(B: int, H1: int, world_size: int, rank: int, prefer: str = "batch") -> Shard:
+    """``prefer="batch"``: batch first, rows for what is left (G_batch = gcd(B, world_size), G_rows = world_size /
+    G_batch) -- no exchange on the data path when B is a multiple of the world size.  ``prefer="rows"``: every rank
+    gets all samples and a block of image-1 rows (G_rows = world_size), the partition for batches smaller than the
+    machine; it costs a halo row per side, a sum of gF2 over the ranks and F2 replicated on every rank."""
     if not 0 <= rank < world_size:
         raise ValueError(f"rank {rank} outside world of {world_size}")
-    g_batch = math.gcd(B, world_size)
+    if prefer not in ("batch", "rows"):
+        raise ValueError(f"prefer must be 'batch' or 'rows', got {prefer!r}")
+    g_batch = math.gcd(B, world_size) if prefer == "batch" else 1
     g_rows = world_size // g_batch
     if g_rows > H1:
         raise ValueError(f"{g_rows} row shards for {H1} image-1 rows")

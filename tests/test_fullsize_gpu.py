@@ -135,3 +135,44 @@ def test_gF2_against_fp32_torch_full_sum(cuda_device):
     ref = orc.max_argmax_avg_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v)
     for x, r in zip(out, ref):
         assert relerr(x, r) < TOL
+
+
+def test_call_site_variants_agree_at_full_size(cuda_device):
+    """One sample of config 5 (135x240, C=256, Kc=4), two pyramid levels: the call site as one autograd node (library
+    stencil kernels for the attention modules, library resampling + concatenation) against the op-by-op call site
+    (torch's Conv3d / softmax / F.interpolate / torch.cat around the same sweeps).  Both use the same TF32 sweeps,
+    so they must agree far inside the TF32 tolerance: this checks the attention, resampling and placement kernels
+    and the one-call backward at the full image size."""
+    import separableflowthesis_b200 as sfb
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    H, W, C, Kc = 135, 240, 256, 4
+    g = torch.Generator().manual_seed(99)
+    f1 = torch.randn(1, C, H, W, generator=g).to(cuda_device)
+    f2 = torch.randn(1, C, H, W, generator=g).to(cuda_device)
+    convs = []
+    for _ in range(2):
+        conv = torch.nn.Conv3d(2, Kc, 3, padding=1)
+        with torch.no_grad():
+            conv.weight.copy_(torch.randn(conv.weight.shape, generator=g) * 0.1)
+            conv.bias.copy_(torch.randn(conv.bias.shape, generator=g) * 0.1)
+        convs.append(conv.to(cuda_device))
+    gd = torch.Generator(device=cuda_device).manual_seed(7)
+    results = []
+    for fuse_attention in (True, False):
+        a = f1.clone().requires_grad_(True)
+        b = f2.clone().requires_grad_(True)
+        for c in convs:
+            c.zero_grad()
+        blk = sfb.AlternateCorrBlockSepflow(a, b, None, num_levels=2, support_backward=True,
+                                            fuse_attention=fuse_attention)
+        su, sv = blk(None, sep=True, attention_weights=tuple(convs))
+        if not results:
+            up = (torch.randn(su.shape, generator=gd, device=cuda_device),
+                  torch.randn(sv.shape, generator=gd, device=cuda_device))
+        torch.autograd.backward([su, sv], list(up))
+        results.append([su.detach(), sv.detach(), a.grad, b.grad] + [c.weight.grad.clone() for c in convs])
+        del su, sv, blk
+    names = ("sep_u", "sep_v", "g_fmap1", "g_fmap2", "g_weight1", "g_weight2")
+    for name, x, y in zip(names, results[0], results[1]):
+        assert x.shape == y.shape and relerr(x, y) < 2e-4, (name, relerr(x, y))

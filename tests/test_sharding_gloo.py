@@ -27,6 +27,11 @@ def test_make_shard_partitions_cover_everything():
     assert (s.r0, s.r1) == (119, 135)  # 135 rows over 8 ranks = 17 x 7 + 16
     with pytest.raises(ValueError):
         sharding.make_shard(1, 3, 8, 0)
+    s = sharding.make_shard(8, 135, 4, 1, prefer="rows")     # all samples, a block of rows
+    assert (s.g_batch, s.g_rows, s.b0, s.b1, s.r0, s.r1) == (1, 4, 0, 8, 34, 68)
+    assert sharding.halo_range(s, 135) == (33, 69, 1, 35)
+    assert sharding.halo_range(sharding.make_shard(8, 135, 4, 0, prefer="rows"), 135) == (0, 35, 0, 34)
+    assert sharding.halo_range(sharding.make_shard(8, 135, 8, 3), 135) == (0, 135, 0, 135)
 
 
 def _free_port():
