@@ -59,3 +59,28 @@ def test_argument_validation(lib):
                                      1 << 20, None)
     assert rc == _lib.SFB_ERR_INVALID_ARGUMENT
     assert lib.sfb_status_string(_lib.SFB_ERR_DEVICE_TIMEOUT) == b"device-side wait timed out"
+
+
+def test_argument_validation_of_the_call_site_entry_points(lib):
+    """Attention, lookup, resampling and placed level calls reject bad sizes before any CUDA work."""
+    P = ctypes.c_void_p
+    buf = (ctypes.c_char * 4096)()
+    a16 = (ctypes.addressof(buf) + 255) // 256 * 256
+    p = P(a16)
+    assert lib.sfb_attention_forward(p, 0, p, p, p, 1, 0, 4, 4, 4, None) == _lib.SFB_ERR_INVALID_ARGUMENT
+    assert lib.sfb_attention_forward(p, 0, p, p, p, 1, 65, 4, 4, 4, None) == _lib.SFB_ERR_UNSUPPORTED_SHAPE
+    assert lib.sfb_attention_forward(None, 0, p, p, p, 1, 2, 4, 4, 4, None) == _lib.SFB_ERR_INVALID_ARGUMENT
+    assert lib.sfb_attention_backward_workspace_bytes(1, 2, 4, 4, 4) > 0
+    assert lib.sfb_attention_backward(p, 0, p, p, p, None, 0, p, p, p, 1, 2, 4, 4, 4, p, 16, None) \
+        == _lib.SFB_ERR_WORKSPACE_TOO_SMALL
+    assert lib.sfb_lookup_pyramid_bytes(2, 1, 16, 3, 5, 4) == 4 * 2 * (8 + 4 + 2) * 15
+    assert lib.sfb_lookup_pyramid_bytes(2, 1, 16, 3, 5, 5) == 0          # coarsest level would have one entry
+    assert lib.sfb_lookup_forward(p, p, p, 15, p, 2, 1, 1, 3, 5, 1, 4, 0, None) == _lib.SFB_ERR_INVALID_ARGUMENT
+    assert lib.sfb_lookup_forward(p, p, p, 15, p, 2, 1, 16, 3, 5, 9, 4, 0, None) == _lib.SFB_ERR_UNSUPPORTED_SHAPE
+    assert lib.sfb_upsample_displacement(p, p, 100, 1, 2, 8, 4, 3, 5, None) == _lib.SFB_ERR_UNSUPPORTED_SHAPE
+    assert b"upsampling" in lib.sfb_last_error()
+    assert lib.sfb_upsample_displacement(p, None, 100, 1, 2, 4, 8, 3, 5, None) == _lib.SFB_ERR_INVALID_ARGUMENT
+    s = _lib.SfbShape(1, 4, 4, 4, 4, 32, 2)
+    rc = lib.sfb_separation_level_forward_fmaps(p, p, ctypes.c_float(1.0), p, p, p, p, p, p, 5, 3, None, None, p, p,
+                                                ctypes.byref(s), p, 1 << 30, None)
+    assert rc == _lib.SFB_ERR_INVALID_ARGUMENT and b"do not fit" in lib.sfb_last_error()
