@@ -248,6 +248,17 @@ int sfb_lookup_backward(const float* gout, const float* coord, int64_t coord_bat
                         float* gpyramid, int32_t B, int32_t dim, int32_t D, int32_t H1, int32_t W1, int32_t levels,
                         int32_t radius, int32_t clamp_unit, void* stream);
 
+/* Operand type of the correlation sweeps inside the level calls (sfb_separation_level_forward / _backward and their
+ * _fmaps forms).  SFB_OPERANDS_TF32 (default): features rounded to TF32.  SFB_OPERANDS_BF16: features rounded to
+ * BF16 (round to nearest even), products exact in FP32, FP32 accumulation -- twice the tensor-core rate per
+ * instruction at about 8 mantissa bits (needs C % 8 == 0); the gradient GEMMs keep TF32 operands.  The setting is
+ * process-wide (a
+ * backward runs on another thread than the forward); sfb_set_sweep_operands returns the previous value, or -1 for
+ * an unknown one.  All other entry points always use TF32. */
+enum { SFB_OPERANDS_TF32 = 0, SFB_OPERANDS_BF16 = 1 };
+int sfb_set_sweep_operands(int operands);
+int sfb_get_sweep_operands(void);
+
 /* Test aid with no counterpart in the reference ops: writes the dense volume S (B,H1,W1,H2,W2) of a
  * SMALL problem through the same tensor-core pipeline (the reference builds it with torch.matmul,
  * core/corr.py:286-289). */

@@ -42,7 +42,8 @@ EXPORTED_SYMBOLS = (
     "sfb_separation_feature_backward_cf", "sfb_attention_forward", "sfb_attention_backward_workspace_bytes",
     "sfb_attention_backward", "sfb_separation_level_forward", "sfb_separation_level_backward",
     "sfb_separation_level_forward_fmaps", "sfb_separation_level_backward_fmaps",
-    "sfb_upsample_displacement", "sfb_upsample_displacement_backward", "sfb_lookup_pyramid_bytes", "sfb_lookup_build_pyramid", "sfb_lookup_forward", "sfb_lookup_backward",
+    "sfb_upsample_displacement", "sfb_upsample_displacement_backward", "sfb_lookup_pyramid_bytes",
+    "sfb_set_sweep_operands", "sfb_get_sweep_operands", "sfb_lookup_build_pyramid", "sfb_lookup_forward", "sfb_lookup_backward",
 )
 
 
@@ -85,6 +86,10 @@ def load() -> ctypes.CDLL:
     lib.sfb_attention_backward_workspace_bytes.argtypes = [I32] * 5
     lib.sfb_attention_backward.restype = ctypes.c_int
     lib.sfb_attention_backward.argtypes = [P, I64, P, P, P, P, I64, P, P, P, I32, I32, I32, I32, I32, P, SZ, P]
+    lib.sfb_set_sweep_operands.restype = ctypes.c_int
+    lib.sfb_set_sweep_operands.argtypes = [ctypes.c_int]
+    lib.sfb_get_sweep_operands.restype = ctypes.c_int
+    lib.sfb_get_sweep_operands.argtypes = []
     lib.sfb_upsample_displacement.restype = ctypes.c_int
     lib.sfb_upsample_displacement.argtypes = [P, P, I64] + [I32] * 6 + [P]
     lib.sfb_upsample_displacement_backward.restype = ctypes.c_int

@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -44,8 +45,8 @@ EncodeTiledFn encode_fn() {
 
 // Tiled fp32 tensor map, 128-byte swizzle, innermost box = 32 channels (128 bytes), zero fill out of bounds.
 // dims/box are innermost-first; strides are implied by a contiguous tensor.
-int make_map(CUtensorMap* tm, const float* base, int rank, const uint64_t* dims, const uint32_t* box,
-             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+int make_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, const uint32_t* box,
+             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, bool bf16 = false) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
   // The driver call needs a context that is current to this thread.  A thread that has made no runtime call yet
@@ -58,7 +59,7 @@ int make_map(CUtensorMap* tm, const float* base, int rank, const uint64_t* dims,
   }
   cuuint64_t gdim[5], gstride[5];
   cuuint32_t bdim[5], estride[5];
-  uint64_t stride = sizeof(float);
+  uint64_t stride = bf16 ? 2 : sizeof(float);
   for (int i = 0; i < rank; ++i) {
     gdim[i] = dims[i];
     bdim[i] = box[i];
@@ -66,7 +67,8 @@ int make_map(CUtensorMap* tm, const float* base, int rank, const uint64_t* dims,
     stride *= dims[i];
     if (i < rank - 1) gstride[i] = stride;  // byte stride of dimension i+1
   }
-  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), gdim, gstride,
+  CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank,
+                  const_cast<void*>(base), gdim, gstride,
                   bdim, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -135,11 +137,18 @@ void drain_timing_locked() {
   g_timing_pending.clear();
 }
 
+// Operand type of the correlation sweeps of the level calls: 0 = TF32 (default), 1 = BF16.  Process-wide, because
+// a backward runs on an autograd worker thread, not on the thread that chose the precision.
+std::atomic<int> g_sweep_operands{0};
+
 struct Workspace {
   int* status;
   float* F1r;
   float* F2r;
   float* aux;
+  uint16_t* F1h;  // BF16 copies of the three arrays above (operands of the BF16 sweeps)
+  uint16_t* F2h;
+  uint16_t* auxh;
   float* xu;   // packed inputs indexed by (u, slot, pixel): (B, H2, Rx, n1p)
   float* xv;   // packed inputs indexed by (v, slot, pixel): (B, W2, Rx, n1p)
   float* ou;   // packed outputs, (B, H2, Ro, n1p)
@@ -167,24 +176,24 @@ PixView cf_view(const void* base, int slots, int D, int N1) {
 }
 
 // What an op keeps in the workspace: the mean rows of F2, Rx packed input slots, Ro packed output slots.
-struct WsPlan { bool aux; int Rx; int Ro; int Rg; bool level_bwd; };
+struct WsPlan { bool aux; int Rx; int Ro; int Rg; bool level_bwd; bool bf16; };
 constexpr int MAXAVG_SLOTS = 3;  // max, mean, argmax bits
 int chunk_channels(int Kc) { return Kc < KC_MAX_PER_SWEEP ? Kc : KC_MAX_PER_SWEEP; }
 int grad_slots(int kc) { return 2 * kc <= 4 ? 4 : 8; }  // two slots per channel, rounded up to a multiple of 4
 
 WsPlan plan_for(int op, const Dims& d) {
   switch (op) {
-    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS, 0, false};
-    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc, 0, false};
-    case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, 0, 0, 4, false};
-    case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc)), false};
-    case SFB_OP_SEPARATION_BACKWARD: return {false, d.Kc, d.Kc, 4 + grad_slots(chunk_channels(d.Kc)), false};
-    case SFB_OP_MAX_AVG_FORWARD_CF: return {true, 0, 0, 0, false};
-    case SFB_OP_COMPRESSION_CF: return {false, 0, 0, 0, false};
-    case SFB_OP_SEPARATION_FEATURE_BACKWARD_CF: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc)), false};
-    case SFB_OP_SEPARATION_LEVEL_FORWARD: return {true, 0, 0, 0, false};
-    case SFB_OP_SEPARATION_LEVEL_BACKWARD: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc)), true};
-    default: return {false, 0, 0, 0, false};
+    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS, 0, false, false};
+    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc, 0, false, false};
+    case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, 0, 0, 4, false, false};
+    case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc)), false, false};
+    case SFB_OP_SEPARATION_BACKWARD: return {false, d.Kc, d.Kc, 4 + grad_slots(chunk_channels(d.Kc)), false, false};
+    case SFB_OP_MAX_AVG_FORWARD_CF: return {true, 0, 0, 0, false, false};
+    case SFB_OP_COMPRESSION_CF: return {false, 0, 0, 0, false, false};
+    case SFB_OP_SEPARATION_FEATURE_BACKWARD_CF: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc)), false, false};
+    case SFB_OP_SEPARATION_LEVEL_FORWARD: return {true, 0, 0, 0, false, true};
+    case SFB_OP_SEPARATION_LEVEL_BACKWARD: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc)), true, true};
+    default: return {false, 0, 0, 0, false, false};
   }
 }
 
@@ -203,6 +212,12 @@ Workspace carve(const Dims& d, void* base, const WsPlan& plan) {
   w.F1r = take((size_t)d.B * d.N1() * d.C);
   w.F2r = take((size_t)d.B * d.N2() * d.C);
   w.aux = plan.aux ? take((size_t)d.B * d.aux_rows() * d.C) : nullptr;
+  w.F1h = w.F2h = w.auxh = nullptr;
+  if (plan.bf16) {   // half the floats of the fp32 copies
+    w.F1h = reinterpret_cast<uint16_t*>(take(((size_t)d.B * d.N1() * d.C + 1) / 2));
+    w.F2h = reinterpret_cast<uint16_t*>(take(((size_t)d.B * d.N2() * d.C + 1) / 2));
+    w.auxh = reinterpret_cast<uint16_t*>(take(((size_t)d.B * d.aux_rows() * d.C + 1) / 2));
+  }
   w.xu = plan.Rx ? take((size_t)d.B * d.H2 * plan.Rx * w.n1p) : nullptr;
   w.xv = plan.Rx ? take((size_t)d.B * d.W2 * plan.Rx * w.n1p) : nullptr;
   w.ou = plan.Ro ? take((size_t)d.B * d.H2 * plan.Ro * w.n1p) : nullptr;
@@ -278,17 +293,17 @@ int check_workspace(const Dims& d, void* ws, size_t ws_bytes, int op, Workspace*
 // Tensor maps over the rounded copies.
 // `swizzle` is the 16-byte-atom 128B swizzle for K-major operands (rows = pixels of the tile) and the
 // 32-byte-atom variant for MN-major TF32 operands (the only layout tcgen05.mma accepts for those).
-int map_f1_rows(CUtensorMap* tm, const Dims& d, const float* F1r, uint32_t rows,
-                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {  // (C, N1, B)
+int map_f1_rows(CUtensorMap* tm, const Dims& d, const void* F1r, uint32_t rows,
+                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, bool bf16 = false) {  // (C, N1, B)
   const uint64_t dims[3] = {(uint64_t)d.C, (uint64_t)d.N1(), (uint64_t)d.B};
-  const uint32_t box[3] = {KBLK, rows, 1};
-  return make_map(tm, F1r, 3, dims, box, swizzle);
+  const uint32_t box[3] = {bf16 ? 2u * KBLK : (uint32_t)KBLK, rows, 1};   // one 128-byte row of channels
+  return make_map(tm, F1r, 3, dims, box, swizzle, bf16);
 }
-int map_f2_tile(CUtensorMap* tm, const Dims& d, const float* F2r, uint32_t ut, uint32_t vt,
-                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {  // (C, W2, H2, B)
+int map_f2_tile(CUtensorMap* tm, const Dims& d, const void* F2r, uint32_t ut, uint32_t vt,
+                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, bool bf16 = false) {  // (C, W2, H2, B)
   const uint64_t dims[4] = {(uint64_t)d.C, (uint64_t)d.W2, (uint64_t)d.H2, (uint64_t)d.B};
-  const uint32_t box[4] = {KBLK, vt, ut, 1};
-  return make_map(tm, F2r, 4, dims, box, swizzle);
+  const uint32_t box[4] = {bf16 ? 2u * KBLK : (uint32_t)KBLK, vt, ut, 1};
+  return make_map(tm, F2r, 4, dims, box, swizzle, bf16);
 }
 // Interleaved gradient operands (B, D, Q, n1p, 4), seen by TMA as (4*n1p, Q, D, B) so that the innermost box
 // dimension is a long contiguous run (`pixels` * 16 bytes): box = (4*pixels, Q groups, `disps` displacements, 1).
@@ -297,10 +312,10 @@ int map_operands(CUtensorMap* tm, const float* x, int B, int D, int Q, int n1p, 
   const uint32_t box[4] = {4 * pixels, (uint32_t)Q, disps, 1};
   return make_map(tm, x, 4, dims, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
-int map_aux(CUtensorMap* tm, const Dims& d, const float* aux) {  // (C, H2+W2, B)
+int map_aux(CUtensorMap* tm, const Dims& d, const void* aux, bool bf16 = false) {  // (C, H2+W2, B)
   const uint64_t dims[3] = {(uint64_t)d.C, (uint64_t)d.aux_rows(), (uint64_t)d.B};
-  const uint32_t box[3] = {KBLK, (uint32_t)(SWEEP_UT * SWEEP_VT), 1};
-  return make_map(tm, aux, 3, dims, box);
+  const uint32_t box[3] = {bf16 ? 2u * KBLK : (uint32_t)KBLK, (uint32_t)(SWEEP_UT * SWEEP_VT), 1};
+  return make_map(tm, aux, 3, dims, box, CU_TENSOR_MAP_SWIZZLE_128B, bf16);
 }
 
 int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u, int32_t* AM_v,
@@ -346,7 +361,7 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
 // channels per sweep.  Weight k is slot (slot0 + k*stride) of the views xu (per u: w_v) / xv (per v: w_u).
 int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2, PixView xu,
                         PixView xv, int wu_slot0, int wv_slot0, int w_stride, PixView ou, PixView ov, int n_valid,
-                        cudaStream_t st) {
+                        cudaStream_t st, int bf16 = 0) {
   for (int k0 = 0; k0 < d.Kc; k0 += KC_MAX_PER_SWEEP) {
     SweepArgs a;
     memset(&a, 0, sizeof(a));
@@ -358,6 +373,7 @@ int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, co
     a.xu = xu; a.xv = xv;
     a.wu_slot0 = wu_slot0; a.wv_slot0 = wv_slot0; a.w_stride = w_stride;
     a.ou = ou; a.ov = ov;
+    a.bf16 = bf16;
     a.status = status;
     SFB_CUDA(timed(KID_SWEEP_COMPRESS, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));
   }
@@ -894,13 +910,25 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_LEVEL_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int bf16 = g_sweep_operands.load() == 1 ? 1 : 0;
+  if (bf16 && d.C % 8 != 0)
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "BF16 sweep operands need a feature dimension that is a multiple of 8 (C=%d)", d.C);
   CUtensorMap tm_f1, tm_f2, tm_aux;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_TRY(map_aux(&tm_aux, d, w.aux));
+  if (bf16) {
+    SFB_TRY(map_f1_rows(&tm_f1, d, w.F1h, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, true));
+    SFB_TRY(map_f2_tile(&tm_f2, d, w.F2h, SWEEP_UT, SWEEP_VT, CU_TENSOR_MAP_SWIZZLE_128B, true));
+    SFB_TRY(map_aux(&tm_aux, d, w.auxh, true));
+  } else {
+    SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+    SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+    SFB_TRY(map_aux(&tm_aux, d, w.aux));
+  }
+  uint16_t* const F1h = bf16 ? w.F1h : nullptr;
+  uint16_t* const F2h = bf16 ? w.F2h : nullptr;
+  uint16_t* const auxh = bf16 ? w.auxh : nullptr;
   SFB_CUDA(timed(KID_PREPARE, 3, st, [&] {
-    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, w.aux, w.status, st)
-                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st);
+    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, w.aux, w.status, st, F1h, F2h, auxh)
+                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st, F1h, F2h, auxh);
   }));
   const int N1 = d.N1(), K = d.Kc, Kt = pl.Ktot, c0 = pl.c0;
   SweepArgs a;
@@ -912,6 +940,7 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   a.pv = cf_channels(SEP_u, Kt, c0, d.W2, N1);
   a.pu_arg = cf_view(AM_u, 1, d.H2, N1);
   a.pv_arg = cf_view(AM_v, 1, d.W2, N1);
+  a.bf16 = bf16;
   a.status = w.status;
   SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
   const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
@@ -923,7 +952,8 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   }));
   // C_u (per u, weights A_u per v) -> SEP_v channels 2.., C_v -> SEP_u channels 2..
   return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(A_v, K, d.H2, N1), cf_view(A_u, K, d.W2, N1), 0, 0, 1,
-                             cf_channels(SEP_v, Kt, c0 + 2, d.H2, N1), cf_channels(SEP_u, Kt, c0 + 2, d.W2, N1), N1, st);
+                             cf_channels(SEP_v, Kt, c0 + 2, d.H2, N1), cf_channels(SEP_u, Kt, c0 + 2, d.W2, N1), N1, st,
+                             bf16);
 }
 
 int sfb_separation_level_forward(const float* F1, const float* F2, const float* weight_u, const float* bias_u,
@@ -962,19 +992,30 @@ static int level_backward(Placement pl, const float* F1, const float* F2, int fm
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_LEVEL_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the attention-gradient sweep follows the chosen operand type; the gradient GEMMs always use the TF32 copies
+  const int bf16 = g_sweep_operands.load() == 1 ? 1 : 0;
+  if (bf16 && d.C % 8 != 0)
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "BF16 sweep operands need a feature dimension that is a multiple of 8 (C=%d)", d.C);
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  if (bf16) {
+    SFB_TRY(map_f1_rows(&tm_f1, d, w.F1h, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, true));
+    SFB_TRY(map_f2_tile(&tm_f2, d, w.F2h, SWEEP_UT, SWEEP_VT, CU_TENSOR_MAP_SWIZZLE_128B, true));
+  } else {
+    SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
+    SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  }
+  uint16_t* const F1h = bf16 ? w.F1h : nullptr;
+  uint16_t* const F2h = bf16 ? w.F2h : nullptr;
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] {
-    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, nullptr, w.status, st)
-                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st);
+    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, nullptr, w.status, st, F1h, F2h, nullptr)
+                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st, F1h, F2h, nullptr);
   }));
   const int N1 = d.N1(), K = d.Kc, Kt = pl.Ktot, c0 = pl.c0;
   // attention gradients: gA_v(b,k,u,p) = sum_v S * gC_v(b,k,v,p), gA_u(b,k,v,p) = sum_u S * gC_u(b,k,u,p), with
   // gC_u = gSEP_v[:, 2:] (per u) and gC_v = gSEP_u[:, 2:] (per v) in the role of the weights
   SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_channels(gSEP_v, Kt, c0 + 2, d.H2, N1),
                               cf_channels(gSEP_u, Kt, c0 + 2, d.W2, N1), 0, 0, 1, cf_view(w.ga_v, K, d.H2, N1),
-                              cf_view(w.ga_u, K, d.W2, N1), N1, st));
+                              cf_view(w.ga_u, K, d.W2, N1), N1, st, bf16));
   // through softmax and Conv3d: parameter gradients, and the total gradients of the max/avg channels
   const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
   SFB_CUDA(timed(KID_ATTENTION_BWD, 2 * attention_backward_launches(K), st, [&] {
@@ -1101,6 +1142,12 @@ int sfb_lookup_backward(const float* gout, const float* coord, int64_t coord_bat
   }));
   return SFB_OK;
 }
+
+int sfb_set_sweep_operands(int operands) {
+  if (operands != SFB_OPERANDS_TF32 && operands != SFB_OPERANDS_BF16) return -1;
+  return g_sweep_operands.exchange(operands);
+}
+int sfb_get_sweep_operands(void) { return g_sweep_operands.load(); }
 
 int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape* shape, void* workspace,
                     size_t workspace_bytes, void* stream) {

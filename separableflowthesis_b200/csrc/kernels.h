@@ -60,6 +60,7 @@ struct SweepArgs {
   PixView xu, xv;
   int wu_slot0, wv_slot0, w_stride;
   PixView ou, ov;
+  int bf16;              // operands are BF16 copies (64 channels per 128-byte row, tcgen05.mma kind::f16) instead of TF32
   float* dump;           // SWEEP_DUMP: dense S (B,N1,H2,W2), test use only
   int* status;           // device status word
 };
@@ -110,13 +111,17 @@ cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, i
 
 // Rounds F1/F2 to TF32 (round-to-nearest) into the workspace copies, optionally builds the
 // row/column mean rows of F2, and clears the status word.
+// F1h / F2h / auxh (optional): the same three arrays rounded to BF16 from the unrounded values, the operands of the
+// BF16 form of the sweeps.
 cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
-                           int* status, cudaStream_t stream);
+                           int* status, cudaStream_t stream, uint16_t* F1h = nullptr, uint16_t* F2h = nullptr,
+                           uint16_t* auxh = nullptr);
 // The same from the model's feature maps fmap1 (B, C, H1, W1), fmap2 (B, C, H2, W2): F1r = round(scale1 * fmap1)
 // transposed to (B, H1, W1, C), F2r = round(fmap2) transposed (core/corr.py:419-422 does this with
 // permute().contiguous() and a division).
 cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
-                              float* F2r, float* aux, int* status, cudaStream_t stream);
+                              float* F2r, float* aux, int* status, cudaStream_t stream, uint16_t* F1h = nullptr,
+                              uint16_t* F2h = nullptr, uint16_t* auxh = nullptr);
 // Pack: dst[b][d][r0 + k*rstride][p] = scale * src[b][p][ksrc0 + k][d] for k < K (raw 32-bit copy when
 // scale == 0), zero for N1 <= p < n1p.  src is (B, N1, Ksrc, D), dst is (B, D, R, n1p).
 cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,

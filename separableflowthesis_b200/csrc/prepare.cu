@@ -7,22 +7,31 @@
 //    reference accumulates cell by cell, MemorySaver_kernel_forward.cu:286-290).
 #include <algorithm>
 
+#include <cuda_bf16.h>
+
 #include "kernels.h"
 #include "sm100_primitives.cuh"
 
 namespace sfb {
 
-__global__ void round_copy_kernel(const float4* __restrict__ in, float4* __restrict__ out, size_t n4) {
+// `outh` (optional): the same values rounded to BF16 instead (operands of the BF16 sweeps).
+__global__ void round_copy_kernel(const float4* __restrict__ in, float4* __restrict__ out, size_t n4,
+                                  uint2* __restrict__ outh) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
     float4 v = __ldg(in + i);
+    if (outh != nullptr) {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      outh[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
     v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w);
     out[i] = v;
   }
 }
 
 // grid (H2 + W2, B), block = min(C, 256) threads over channels.
-__global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict__ aux, int H2, int W2, int C) {
+__global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict__ aux, int H2, int W2, int C,
+                                __nv_bfloat16* __restrict__ auxh) {
   const int r = blockIdx.x, b = blockIdx.y;
   const float* base = F2 + (size_t)b * H2 * W2 * C;
   float* dst = aux + ((size_t)b * (H2 + W2) + r) * C;
@@ -38,6 +47,7 @@ __global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict_
       acc /= (float)H2;
     }
     dst[c] = round_tf32(acc);
+    if (auxh != nullptr) auxh[((size_t)b * (H2 + W2) + r) * C + c] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -204,7 +214,7 @@ cudaError_t launch_unpack(const float* src, void* dst, int B, int N1, int n1p, i
 // (B, C, N) -> (B, N, C), scaled and rounded to TF32.  32 x 32 tiles through shared memory; grid
 // (ceil(N/32), ceil(C/32), B), block (32, 8).
 __global__ void transpose_round_kernel(const float* __restrict__ in, float* __restrict__ out, int C, int N,
-                                       float scale) {
+                                       float scale, __nv_bfloat16* __restrict__ outh) {
   __shared__ float tile[32][33];
   const int b = blockIdx.z, p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
   const int tx = threadIdx.x, ty = threadIdx.y;
@@ -217,40 +227,49 @@ __global__ void transpose_round_kernel(const float* __restrict__ in, float* __re
 #pragma unroll
   for (int j = ty; j < 32; j += 8) {
     const int p = p0 + j, c = c0 + tx;
-    if (p < N && c < C) out[((size_t)b * N + p) * C + c] = round_tf32(tile[tx][j] * scale);
+    if (p < N && c < C) {
+      const float v = tile[tx][j] * scale;
+      out[((size_t)b * N + p) * C + c] = round_tf32(v);
+      if (outh != nullptr) outh[((size_t)b * N + p) * C + c] = __float2bfloat16_rn(v);
+    }
   }
 }
 
 cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
-                              float* F2r, float* aux, int* status, cudaStream_t stream) {
+                              float* F2r, float* aux, int* status, cudaStream_t stream, uint16_t* F1h, uint16_t* F2h,
+                              uint16_t* auxh) {
   cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), stream);
   if (err != cudaSuccess) return err;
   const dim3 block(32, 8);
-  transpose_round_kernel<<<dim3((d.N1() + 31) / 32, (d.C + 31) / 32, d.B), block, 0, stream>>>(fmap1, F1r, d.C, d.N1(),
-                                                                                               scale1);
-  transpose_round_kernel<<<dim3((d.N2() + 31) / 32, (d.C + 31) / 32, d.B), block, 0, stream>>>(fmap2, F2r, d.C, d.N2(),
-                                                                                               1.f);
+  transpose_round_kernel<<<dim3((d.N1() + 31) / 32, (d.C + 31) / 32, d.B), block, 0, stream>>>(
+      fmap1, F1r, d.C, d.N1(), scale1, reinterpret_cast<__nv_bfloat16*>(F1h));
+  transpose_round_kernel<<<dim3((d.N2() + 31) / 32, (d.C + 31) / 32, d.B), block, 0, stream>>>(
+      fmap2, F2r, d.C, d.N2(), 1.f, reinterpret_cast<__nv_bfloat16*>(F2h));
   if (aux != nullptr) {  // mean rows from the transposed copy (already rounded: the means differ by < 2^-12 relative)
     const dim3 grid(d.H2 + d.W2, d.B);
-    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2r, aux, d.H2, d.W2, d.C);
+    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2r, aux, d.H2, d.W2, d.C,
+                                                             reinterpret_cast<__nv_bfloat16*>(auxh));
   }
   return cudaGetLastError();
 }
 
 cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
-                           int* status, cudaStream_t stream) {
+                           int* status, cudaStream_t stream, uint16_t* F1h, uint16_t* F2h, uint16_t* auxh) {
   cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), stream);
   if (err != cudaSuccess) return err;
   const size_t n1 = (size_t)d.B * d.N1() * d.C / 4, n2 = (size_t)d.B * d.N2() * d.C / 4;  // C % 4 == 0
   const int threads = 256;
   auto blocks = [&](size_t n) { return (unsigned)std::min<size_t>((n + threads - 1) / threads, 148 * 16); };
   round_copy_kernel<<<blocks(n1), threads, 0, stream>>>(reinterpret_cast<const float4*>(F1),
-                                                        reinterpret_cast<float4*>(F1r), n1);
+                                                        reinterpret_cast<float4*>(F1r), n1,
+                                                        reinterpret_cast<uint2*>(F1h));
   round_copy_kernel<<<blocks(n2), threads, 0, stream>>>(reinterpret_cast<const float4*>(F2),
-                                                        reinterpret_cast<float4*>(F2r), n2);
+                                                        reinterpret_cast<float4*>(F2r), n2,
+                                                        reinterpret_cast<uint2*>(F2h));
   if (aux != nullptr) {
     const dim3 grid(d.H2 + d.W2, d.B);
-    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2, aux, d.H2, d.W2, d.C);
+    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2, aux, d.H2, d.W2, d.C,
+                                                             reinterpret_cast<__nv_bfloat16*>(auxh));
   }
   return cudaGetLastError();
 }

@@ -66,8 +66,9 @@ struct SweepSched {
 // ---------------------------------------------------------------------------------- producer
 __device__ void sweep_producer(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const CUtensorMap* tm_f1,
                                const CUtensorMap* tm_f2, const CUtensorMap* tm_aux) {
+  const int kel = a.bf16 ? 2 * KBLK : KBLK;  // channels in one 128-byte row
   mbar_expect_tx(&sm.f1_full, sc.nkb * SW_F1_BLOCK_BYTES);
-  for (int kb = 0; kb < sc.nkb; ++kb) tma_load_3d(sm.f1[kb], tm_f1, &sm.f1_full, kb * KBLK, sc.m0, sc.b);
+  for (int kb = 0; kb < sc.nkb; ++kb) tma_load_3d(sm.f1[kb], tm_f1, &sm.f1_full, kb * kel, sc.m0, sc.b);
   uint32_t it = 0;
   int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_total; ++t) {
@@ -77,9 +78,9 @@ __device__ void sweep_producer(SweepSmem& sm, const SweepArgs& a, const SweepSch
       if (!mbar_wait(&sm.empty[s], ph ^ 1u, &sm.abort_flag, a.status, DEV_TIMEOUT_PRODUCER)) return;
       mbar_expect_tx(&sm.full[s], SW_STAGE_BYTES);
       if (main_tile)
-        tma_load_4d(sm.f2[s], tm_f2, &sm.full[s], kb * KBLK, vb * SWEEP_VT, ub * SWEEP_UT, sc.b);
+        tma_load_4d(sm.f2[s], tm_f2, &sm.full[s], kb * kel, vb * SWEEP_VT, ub * SWEEP_UT, sc.b);
       else
-        tma_load_3d(sm.f2[s], tm_aux, &sm.full[s], kb * KBLK, (t - sc.t_main) * SW_TILE_N, sc.b);
+        tma_load_3d(sm.f2[s], tm_aux, &sm.full[s], kb * kel, (t - sc.t_main) * SW_TILE_N, sc.b);
     }
     if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
@@ -87,7 +88,9 @@ __device__ void sweep_producer(SweepSmem& sm, const SweepArgs& a, const SweepSch
 
 // ---------------------------------------------------------------------------------- MMA issuer
 __device__ void sweep_mma(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc) {
-  constexpr uint32_t idesc = make_idesc_tf32(TILE_M, SW_TILE_N, false, false);
+  constexpr uint32_t idesc_tf32 = make_idesc_tf32(TILE_M, SW_TILE_N, false, false);
+  constexpr uint32_t idesc_bf16 = make_idesc_bf16(TILE_M, SW_TILE_N);
+  const bool bf16 = a.bf16 != 0;
   if (!mbar_wait(&sm.f1_full, 0, &sm.abort_flag, a.status, DEV_TIMEOUT_MMA)) return;
   tc_fence_after();
   uint32_t it = 0;
@@ -102,9 +105,15 @@ __device__ void sweep_mma(SweepSmem& sm, const SweepArgs& a, const SweepSched& s
       tc_fence_after();
       const uint64_t adesc = make_smem_desc_sw128(smem_u32(sm.f1[kb]), 16, 1024);
       const uint64_t bdesc = make_smem_desc_sw128(smem_u32(sm.f2[s]), 16, 1024);
+      if (bf16) {
 #pragma unroll
-      for (int k = 0; k < KBLK / 8; ++k)  // one instruction consumes K = 8 TF32 values = 32 bytes of each row
-        umma_tf32(d_tmem, desc_advance(adesc, k * 32), desc_advance(bdesc, k * 32), idesc, (kb | k) != 0);
+        for (int k = 0; k < 4; ++k)  // one instruction consumes K = 16 BF16 values = 32 bytes of each row
+          umma_bf16(d_tmem, desc_advance(adesc, k * 32), desc_advance(bdesc, k * 32), idesc_bf16, (kb | k) != 0);
+      } else {
+#pragma unroll
+        for (int k = 0; k < KBLK / 8; ++k)  // one instruction consumes K = 8 TF32 values = 32 bytes of each row
+          umma_tf32(d_tmem, desc_advance(adesc, k * 32), desc_advance(bdesc, k * 32), idesc_tf32, (kb | k) != 0);
+      }
       umma_commit(&sm.empty[s]);  // stage reusable once these MMAs have read it
     }
     umma_commit(&sm.acc_full[acc]);
@@ -397,7 +406,7 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
   SweepSched sc;
   sc.b = blockIdx.x / tiles_per_sample;
   sc.m0 = (blockIdx.x - sc.b * tiles_per_sample) * TILE_M;
-  sc.nkb = (a.d.C + KBLK - 1) / KBLK;
+  sc.nkb = a.bf16 ? (a.d.C + 2 * KBLK - 1) / (2 * KBLK) : (a.d.C + KBLK - 1) / KBLK;
   sc.n_ub = (a.d.H2 + SWEEP_UT - 1) / SWEEP_UT;
   sc.n_vb = (a.d.W2 + SWEEP_VT - 1) / SWEEP_VT;
   sc.t_main = sc.n_ub * sc.n_vb;

@@ -564,6 +564,24 @@ def lookup_backward(corr_shape, coord, grad_out, levels=4, radius=4, clamp_unit=
     return gcorr
 
 
+class sweep_operands:
+    """Context manager / setter for the operand type of the correlation sweeps inside the level calls:
+    ``with ops.sweep_operands("bf16"): ...`` (process-wide; "tf32" is the default)."""
+    _codes = {"tf32": 0, "bf16": 1}
+
+    def __init__(self, kind: str):
+        if kind not in self._codes:
+            raise ValueError(f"operand type must be 'tf32' or 'bf16', got {kind!r}")
+        self.prev = _lib.load().sfb_set_sweep_operands(self._codes[kind])
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        _lib.load().sfb_set_sweep_operands(self.prev)
+        return False
+
+
 def corr_volume(img1_features_l0, img2_features_lk) -> torch.Tensor:
     """Test aid: the dense volume S (B,H1,W1,H2,W2) of a small problem, through the tensor-core pipeline."""
     F1, F2 = img1_features_l0, img2_features_lk

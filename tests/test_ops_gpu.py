@@ -401,6 +401,50 @@ def test_ops_from_a_fresh_thread(cuda_device):
         assert torch.equal(x, y)
 
 
+@pytest.mark.parametrize("shape", [(2, 11, 19, 9, 21, 104, 3), (1, 24, 40, 24, 40, 256, 2)])
+def test_separation_level_with_bf16_sweep_operands(shape, cuda_device):
+    """BF16 operands in the sweeps of the level calls (BASELINE's bf16 configuration): products of BF16 values are
+    exact in FP32, so the max channel must match the float64 oracle evaluated on the BF16-rounded features to
+    accumulation-order accuracy; the mean rows of F2 are rounded once more (BF16), which the mean, attention and
+    compression channels inherit; the backward (TF32 gradient GEMMs on the unrounded features, BF16 attention-
+    gradient sweep) stays within BF16 accuracy of the TF32 path."""
+    B, H1, W1, H2, W2, C, Kc = shape
+    F1, F2, _, _, g = make_inputs(shape, 23)
+    params = [torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(Kc, generator=g) * 0.1,
+              torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(Kc, generator=g) * 0.1]
+    dev = cuda_device
+    F1d, F2d = F1.to(dev), F2.to(dev)
+    wu, bu, wv, bv = [t.to(dev) for t in params]
+    with ops.sweep_operands("bf16"):
+        fw = ops.separation_level_forward(F1d, F2d, wu, bu, wv, bv)
+        g_sep_u = torch.randn(fw[0].shape, generator=g).to(dev)
+        g_sep_v = torch.randn(fw[1].shape, generator=g).to(dev)
+        bw = ops.separation_level_backward(F1d, F2d, wu, wv, *fw, g_sep_u, g_sep_v)
+    assert _lib_operands() == 0                                   # restored
+    F1b, F2b = F1.bfloat16().double(), F2.bfloat16().double()
+    ref = orc.separation_level_forward(F1b, F2b, *[t.double() for t in params])
+    assert relerr(fw[0][:, 0], ref[0][:, 0]) < 2e-5 and relerr(fw[1][:, 0], ref[1][:, 0]) < 2e-5
+    assert relerr(fw[0], ref[0]) < 4e-3 and relerr(fw[1], ref[1]) < 4e-3
+    gap_u, gap_v = orc.top2_margins(F1b.float(), F2b.float())
+    assert ((fw[2].cpu() == ref[2]) | (gap_u.permute(0, 3, 1, 2) <= 1e-4)).all()
+    assert ((fw[3].cpu() == ref[3]) | (gap_v.permute(0, 3, 1, 2) <= 1e-4)).all()
+    # against the unrounded float64 oracle the BF16 path is a BF16-accuracy result
+    ref32 = orc.separation_level_forward(F1.double(), F2.double(), *[t.double() for t in params])
+    assert relerr(fw[0], ref32[0]) < 1e-2 and relerr(fw[1], ref32[1]) < 1e-2
+    # backward with the BF16 forward's own argmax / attention weights: BF16 accuracy against the float64 oracle
+    rb = orc.separation_level_backward(F1.double(), F2.double(), params[0].double(), params[2].double(),
+                                       fw[0].double().cpu(), fw[1].double().cpu(), fw[2].cpu(), fw[3].cpu(),
+                                       fw[4].double().cpu(), fw[5].double().cpu(), g_sep_u.double().cpu(),
+                                       g_sep_v.double().cpu())
+    for i in (0, 1, 2, 4):
+        assert relerr(bw[i], rb[i]) < 1e-2, i
+
+
+def _lib_operands():
+    from separableflowthesis_b200 import _lib
+    return _lib.load().sfb_get_sweep_operands()
+
+
 def test_backward_is_deterministic(cuda_device):
     """Gradients accumulate in TMEM, not with atomics: two runs are bit-identical."""
     shape = (2, 24, 40, 24, 40, 128, 2)
