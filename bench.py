@@ -507,6 +507,9 @@ def main():
                     help="batch: samples first, image-1 rows for what is left (no data-path exchange when the batch "
                          "is a multiple of the GPUs); rows: every rank gets all samples and a block of image-1 rows "
                          "plus a halo row per side, gF2 is summed and halo-row gradients exchanged over NCCL")
+    ap.add_argument("--operands", default="tf32", choices=["tf32", "bf16"],
+                    help="operand type of the correlation sweeps of the level calls (bf16: BASELINE's bf16 configuration; "
+                         "lower precision than the default, so not the headline)")
     ap.add_argument("--levels", type=int, default=1,
                     help="pyramid levels of the end-to-end block (the metric counts level-0 cells; the reference's "
                          "model uses 4 levels = 1.33x the cells)")
@@ -559,6 +562,10 @@ def main():
     if path == "level" and cfg["Kc"] == 0:
         raise SystemExit("--path level needs attention channels")
     job = make_job(cfg, shard, device, path)
+    if args.operands == "bf16":
+        if path != "level":
+            raise SystemExit("--operands bf16 applies to the level calls (--path level)")
+        _lib.load().sfb_set_sweep_operands(1)
 
     def barrier():
         if world > 1:
@@ -664,7 +671,9 @@ def main():
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "tf32 operands (fp32 in HBM), fp32 accumulate", "data": "synthetic",
+        "dtype": ("tf32 operands (fp32 in HBM), fp32 accumulate" if args.operands == "tf32" else
+                  "bf16 operands in the sweeps, tf32 in the gradient GEMMs (fp32 in HBM), fp32 accumulate"),
+        "data": "synthetic",
         "config": {"workload": cfg["name"], "path": path, "cells_per_step": total_cells,
                    "flop_per_cell": flops_per_cell(cfg),
                    "sharding": f"batch x rows = {shard.g_batch} x {shard.g_rows}",
