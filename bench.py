@@ -19,6 +19,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 import torch
@@ -58,48 +59,101 @@ def flops_per_cell(cfg) -> int:
 
 # --------------------------------------------------------------------------------------- clocks
 class ClockSampler:
+    """Samples the SM clock and the clock-event reasons of one GPU while a timed region runs.
+
+    Reads NVML from a thread of this process every 10 ms (a timed region of a few tens of milliseconds still
+    gets samples); when NVML cannot be loaded it falls back to an `nvidia-smi -lms 200` child process.
+    Nothing is set: both only read."""
+
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.out = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-        self.proc = None
+        self.sm, self.smax, self.reasons = [], [], set()
+        self.proc = self.out = self.thread = None
+        self.source = None
+        self._stop = threading.Event()
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = self._handle(pynvml, gpu_index)
+            self.smax.append(float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+            masks = ((pynvml.nvmlClocksEventReasonHwSlowdown, "hw_slowdown"),
+                     (pynvml.nvmlClocksEventReasonHwThermalSlowdown, "hw_thermal_slowdown"),
+                     (pynvml.nvmlClocksEventReasonSwThermalSlowdown, "sw_thermal_slowdown"),
+                     (pynvml.nvmlClocksEventReasonSwPowerCap, "sw_power_cap"))
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                        bits = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                        for mask, name in masks:
+                            if bits & mask:
+                                self.reasons.add(name)
+                    except pynvml.NVMLError:
+                        pass
+                    self._stop.wait(0.010)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            self.source = "nvml"
+            return
+        except Exception:
+            self.thread = None
+        try:
+            self.out = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
                  "-i", str(gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+            self.source = "nvidia-smi"
         except OSError:
             self.proc = None
 
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+    @staticmethod
+    def _handle(pynvml, gpu_index):
+        """NVML handle of CUDA device `gpu_index`, matched by PCI address so that a CUDA_VISIBLE_DEVICES
+        remapping cannot pick another GPU's clocks."""
         try:
-            self.proc.wait(5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        self.out.flush()
-        self.out.seek(0)
-        sm, smax, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.out.read().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
+            p = torch.cuda.get_device_properties(gpu_index)
+            bus = f"{p.pci_domain_id:08x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+            return pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:
+            return pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+
+    def stop(self):
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(2)
+        elif self.proc is not None:
+            self.proc.terminate()
             try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        self.out.close()
-        os.unlink(self.out.name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                self.proc.wait(5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.out.flush()
+            self.out.seek(0)
+            for line in self.out.read().splitlines():
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    self.sm.append(float(parts[0]))
+                    self.smax.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(self.NAMES, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        self.reasons.add(n)
+            self.out.close()
+            os.unlink(self.out.name)
+        else:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+                "sm_max_mhz": max(self.smax) if self.smax else None,
+                "samples": len(self.sm), "source": self.source, "reasons": sorted(self.reasons)}
 
 
 # --------------------------------------------------------------------------------------- workload
