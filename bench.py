@@ -354,6 +354,76 @@ def run_lookup_bench(args, cfg, device, emit):
                        "traffic": None, "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650"}})
 
 
+def run_lookup4d_bench(args, cfg, device, emit):
+    """`--path lookup4d`: one refinement iteration of the 4D lookup without the stored volume (the branch
+    core/corr.py:491-510 leaves unimplemented; result of core/corr.py:192-247): 4 levels, radius 4, at every image-1
+    pixel, forward and (training configs) backward, on the config's feature maps.  The stored volume would be
+    B*N^2*4/3 floats (45 GB at config 5); here each value is recomputed from the feature rows."""
+    import separableflowthesis_b200 as sfb
+    B, H, W = cfg["B"], cfg["H"], cfg["W"]
+    levels, radius = 4, 4
+    gd = torch.Generator(device=device).manual_seed(SEED + 12)
+    f1 = torch.randn(B, C_FEAT, H, W, generator=gd, device=device, requires_grad=cfg["bwd"])
+    f2 = torch.randn(B, C_FEAT, H, W, generator=gd, device=device, requires_grad=cfg["bwd"])
+    ys, xs = torch.meshgrid(torch.arange(H, device=device), torch.arange(W, device=device), indexing="ij")
+    yy, xx = ys.float() / H, xs.float() / W
+    # piecewise-smooth stand-in for a flow estimate: two low-frequency waves plus sub-pixel noise
+    flow = torch.stack((8.0 * torch.sin(6.28 * (xx + 0.5 * yy)), 6.0 * torch.cos(6.28 * (yy - 0.3 * xx))))
+    coords = (torch.stack((xs, ys)).float() + flow)[None].repeat(B, 1, 1, 1)
+    coords = coords + 0.25 * torch.randn(B, 2, H, W, generator=gd, device=device)
+    win = (2 * radius + 1) ** 2
+    gout = torch.randn(B, levels * win, H, W, generator=gd, device=device)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=levels, radius=radius, support_backward=cfg["bwd"])
+    blk(coords)   # channels-last copies of the feature pyramid: once per pair of images, not per iteration
+
+    def step():
+        out = blk(coords)
+        if cfg["bwd"]:
+            f1.grad = f2.grad = None
+            # the graph of the block's pooled, channels-last copies is shared by all iterations (in the model one
+            # backward runs through all of them), so it must survive this iteration's backward
+            out.backward(gout, retain_graph=True)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    e0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    e1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    sampler = ClockSampler(device.index or 0)
+    torch.cuda.synchronize()
+    for i in range(args.steps):
+        flush.zero_()
+        e0[i].record()
+        step()
+        e1[i].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = sum(a.elapsed_time(b) for a, b in zip(e0, e1)) / args.steps
+    samples = float(B) * H * W * levels * win
+    # algorithmic HBM bytes of one iteration: features read once, outputs written once (backward: output gradients
+    # read, feature gradients written); the gathers of image-2 rows are served by L1/L2
+    feats = 4.0 * B * C_FEAT * H * W * (1 + sum(1.0 / 4 ** l for l in range(levels)))
+    nbytes = (feats + samples * 4) * (2 if cfg["bwd"] else 1)
+    flops = float(B) * H * W * levels * (2 * radius + 2) ** 2 * 2 * C_FEAT * (3 if cfg["bwd"] else 1)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    emit({"metric": "4D cost-volume lookups/sec without the stored volume" + (" (fwd+bwd)" if cfg["bwd"] else " (fwd)"),
+          "value": samples / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": args.steps,
+          "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+          "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+          "config": {"workload": cfg["name"] + ": 4D lookup, 4 levels, radius 4, C=256", "path": "lookup4d",
+                     "l2": "L2 flushed between iterations", "fp32_tflops": flops / (ms * 1e-3) / 1e12},
+          "clocks": clocks, "gpu_launches": (1 + (1 if cfg["bwd"] else 0)) * args.steps,
+          "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                       "traffic": None, "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650",
+                       "note": "gather of image-2 feature rows through L1/L2; HBM traffic is not the limiter"}})
+
+
 class E2E:
     """The call a user of the reference makes: channels-first feature maps in host memory ->
     AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
@@ -549,11 +619,12 @@ def main():
     ap.add_argument("--no-roofline", action="store_true", help="skip the per-kernel timing pass and the TF32 peak run")
     ap.add_argument("--unfused", action="store_true",
                     help="run the two backward ops as the reference's two separate calls instead of the one-call backward")
-    ap.add_argument("--path", default="auto", choices=["auto", "level", "ops", "lookup"],
+    ap.add_argument("--path", default="auto", choices=["auto", "level", "ops", "lookup", "lookup4d"],
                     help="level: one library call per pyramid-level forward / backward, as the call site runs it "
                          "(attention Conv3d + softmax included); ops: the five ops of the reference's module with "
                          "random attention weights; auto: level when the config has attention channels; lookup: "
-                         "the CorrBlock1D lookup on the aggregated volumes instead of the separation")
+                         "the CorrBlock1D lookup on the aggregated volumes instead of the separation; lookup4d: the 4D lookup "
+                         "without the stored volume")
     ap.add_argument("--e2e-chunks", type=int, default=2,
                     help="micro-batches per end-to-end step (the host->device copy of one overlaps the compute of the "
                          "previous one); 1 = copy everything, then compute")
@@ -604,9 +675,9 @@ def main():
     shard = sharding.make_shard(cfg["B"], cfg["H"], world, rank, prefer=args.shard)
     row_group = sharding.new_row_groups(world, shard.g_rows) if world > 1 else None
     path = args.path
-    if path == "lookup":   # the lookup on the aggregated volumes (next component after the separation), one GPU
+    if path in ("lookup", "lookup4d"):   # the lookups that follow the separation in the model, one GPU
         if rank == 0:
-            run_lookup_bench(args, cfg, device, emit)
+            (run_lookup_bench if path == "lookup" else run_lookup4d_bench)(args, cfg, device, emit)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()

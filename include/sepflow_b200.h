@@ -248,6 +248,32 @@ int sfb_lookup_backward(const float* gout, const float* coord, int64_t coord_bat
                         float* gpyramid, int32_t B, int32_t dim, int32_t D, int32_t H1, int32_t W1, int32_t levels,
                         int32_t radius, int32_t clamp_unit, void* stream);
 
+/* Lookup on the 4D correlation volume without storing it: the call the reference's memory-saving block leaves
+ * unimplemented (core/corr.py:491-510 raises NotImplementedError, then sketches
+ * alt_cuda_corr.forward(fmap1, fmap2_l, coords / 2^l, radius) per level; alt_cuda_corr is RAFT's extension and is not
+ * part of the reference checkout).  The result equals the dense block's lookup (core/corr.py:192-247): for every
+ * image-1 pixel and level l, a (2r+1)x(2r+1) window of the level-l volume around coords / 2^l, bilinear with zero
+ * padding (F.grid_sample, align_corners=True, core/utils/utils.py:110-118).
+ *   F1 (B,H1,W1,C) and F2_levels[l] (B,H2[l],W2[l],C): features with channels innermost, as that call takes them
+ *   (core/corr.py:500-501); level l of image 2 is avg_pool2d of level l-1 (core/corr.py:377-382);
+ *   coords (B,2,H1,W1): (x, y) position in image 2 per image-1 pixel (core/sepflow.py:201);
+ *   out (B, levels*(2r+1)^2, H1, W1), channel l*(2r+1)^2 + a*(2r+1) + b sampled at (x + a - r, y + b - r) -- the
+ *   dense block's order (core/corr.py:214-231); every value times `scale` (the reference's 1/sqrt(C),
+ *   core/corr.py:286,510).
+ * F2_levels, H2, W2 are HOST arrays of `levels` entries.  C % 4 == 0, C <= 512, radius <= 4, H2[l], W2[l] >= 2;
+ * feature and feature-gradient pointers 16-byte aligned.
+ * FP32 arithmetic on unrounded features. */
+int sfb_lookup4d_forward(const float* F1, const float* const* F2_levels, const int32_t* H2, const int32_t* W2,
+                         int32_t levels, const float* coords, float* out, int32_t B, int32_t H1, int32_t W1, int32_t C,
+                         int32_t radius, float scale, void* stream);
+/* Gradients of the features for upstream gradient gout (shape of out): gF1 (shape of F1) is overwritten;
+ * gF2_levels[l] (shape of F2_levels[l]) is zeroed and then accumulated with floating-point reductions, so its low
+ * bits vary from run to run.  No gradient for coords: the model detaches them (core/sepflow.py:193). */
+int sfb_lookup4d_backward(const float* F1, const float* const* F2_levels, const int32_t* H2, const int32_t* W2,
+                          int32_t levels, const float* coords, const float* gout, float* gF1,
+                          float* const* gF2_levels, int32_t B, int32_t H1, int32_t W1, int32_t C, int32_t radius,
+                          float scale, void* stream);
+
 /* Operand type of the correlation sweeps inside the level calls (sfb_separation_level_forward / _backward and their
  * _fmaps forms).  SFB_OPERANDS_TF32 (default): features rounded to TF32.  SFB_OPERANDS_BF16: features rounded to
  * BF16 (round to nearest even), products exact in FP32, FP32 accumulation -- twice the tensor-core rate per

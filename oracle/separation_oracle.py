@@ -367,6 +367,76 @@ def lookup_backward(corr_shape, coord, gout, levels=4, radius=4, clamp_unit=Fals
     return corr.grad
 
 
+def lookup4d_dense_forward(fmap1, fmap2, coords, levels=4, radius=4):
+    """Lookup on the stored 4D correlation volume pyramid, the dense block's chain of operations: volume
+    fmap1 . fmap2 / sqrt(C) (core/corr.py:286-296), pyramid by 2x2 average pooling over the image-2 axes
+    (core/corr.py:32-39), per level a (2r+1)^2 window around coords / 2^l sampled with grid_sample
+    (core/corr.py:200-247, core/utils/utils.py:110-118).  fmap1, fmap2 (B,C,H,W); coords (B,2,H1,W1) ->
+    (B, levels*(2r+1)^2, H1, W1).  This is what the memory-saving block's unimplemented branch
+    (core/corr.py:491-510) has to return."""
+    B, C, H1, W1 = fmap1.shape
+    H2, W2 = fmap2.shape[2:]
+    corr = torch.einsum("bcij,bcuv->bijuv", fmap1, fmap2) / torch.sqrt(torch.tensor(float(C), dtype=fmap1.dtype))
+    corr = corr.reshape(B * H1 * W1, 1, H2, W2)
+    r = radius
+    pos = coords.permute(0, 2, 3, 1)
+    outs = []
+    for l in range(levels):
+        if l > 0:
+            corr = torch.nn.functional.avg_pool2d(corr, 2, stride=2)
+        d = torch.linspace(-r, r, 2 * r + 1, dtype=coords.dtype, device=coords.device)
+        delta = torch.stack(torch.meshgrid(d, d, indexing="ij"), dim=-1)
+        at = pos.reshape(B * H1 * W1, 1, 1, 2) / 2 ** l + delta.view(1, 2 * r + 1, 2 * r + 1, 2)
+        Hl, Wl = corr.shape[-2:]
+        xgrid, ygrid = at.split([1, 1], dim=-1)
+        grid = torch.cat([2 * xgrid / (Wl - 1) - 1, 2 * ygrid / (Hl - 1) - 1], dim=-1)
+        smp = torch.nn.functional.grid_sample(corr, grid.to(corr.dtype), align_corners=True)
+        outs.append(smp.view(B, H1, W1, -1))
+    return torch.cat(outs, dim=-1).permute(0, 3, 1, 2).contiguous()
+
+
+def lookup4d_dense_backward(fmap1, fmap2, coords, gout, levels=4, radius=4):
+    """(gfmap1, gfmap2) of lookup4d_dense_forward for upstream gradient gout, by autograd through the dense chain."""
+    with torch.enable_grad():
+        a = fmap1.detach().clone().requires_grad_(True)
+        b = fmap2.detach().clone().requires_grad_(True)
+        lookup4d_dense_forward(a, b, coords, levels, radius).backward(gout)
+    return a.grad, b.grad
+
+
+def lookup4d_forward(F1, F2_levels, coords, radius=4, scale=1.0):
+    """The same lookup in the memory-saving formulation, with the interface of the call the reference sketches
+    (core/corr.py:497-510): channels-last F1 (B,H1,W1,C) and one channels-last image-2 feature map per level
+    (B,H2_l,W2_l,C), level l being the 2x2 average pooling of level l-1 (core/corr.py:377-382).  Averaging the
+    volume over image-2 blocks equals correlating with the averaged features, so this returns what
+    lookup4d_dense_forward returns when scale = 1/sqrt(C)."""
+    B, H1, W1, C = F1.shape
+    r = radius
+    pos = coords.permute(0, 2, 3, 1)
+    outs = []
+    for l, F2 in enumerate(F2_levels):
+        Hl, Wl = F2.shape[1:3]
+        corr = (torch.einsum("bijc,buvc->bijuv", F1, F2) * scale).reshape(B * H1 * W1, 1, Hl, Wl)
+        d = torch.linspace(-r, r, 2 * r + 1, dtype=coords.dtype, device=coords.device)
+        delta = torch.stack(torch.meshgrid(d, d, indexing="ij"), dim=-1)
+        at = pos.reshape(B * H1 * W1, 1, 1, 2) / 2 ** l + delta.view(1, 2 * r + 1, 2 * r + 1, 2)
+        xgrid, ygrid = at.split([1, 1], dim=-1)
+        grid = torch.cat([2 * xgrid / (Wl - 1) - 1, 2 * ygrid / (Hl - 1) - 1], dim=-1)
+        smp = torch.nn.functional.grid_sample(corr, grid.to(corr.dtype), align_corners=True)
+        outs.append(smp.view(B, H1, W1, -1))
+    return torch.cat(outs, dim=-1).permute(0, 3, 1, 2).contiguous()
+
+
+def lookup4d_backward(F1, F2_levels, coords, gout, radius=4, scale=1.0):
+    """(gF1, [gF2_l]) of lookup4d_forward: the gradient of every level's feature map separately, as the
+    device path returns them (the pooling between levels is the caller's)."""
+    with torch.enable_grad():
+        a = F1.detach().clone().requires_grad_(True)
+        bs = [f.detach().clone().requires_grad_(True) for f in F2_levels]
+        lookup4d_forward(a, bs, coords, radius, scale).backward(gout)
+    return a.grad, [b.grad for b in bs]
+
+
 def top2_margins(F1: torch.Tensor, F2: torch.Tensor):
     """Gap between the largest and second-largest entry of S along v (per (p,u)) and
     along u (per (p,v)), computed in float64.  An argmax is required to be bit-exact only

@@ -44,6 +44,7 @@ EXPORTED_SYMBOLS = (
     "sfb_separation_level_forward_fmaps", "sfb_separation_level_backward_fmaps",
     "sfb_upsample_displacement", "sfb_upsample_displacement_backward", "sfb_lookup_pyramid_bytes",
     "sfb_set_sweep_operands", "sfb_get_sweep_operands", "sfb_lookup_build_pyramid", "sfb_lookup_forward", "sfb_lookup_backward",
+    "sfb_lookup4d_forward", "sfb_lookup4d_backward",
 )
 
 
@@ -102,6 +103,10 @@ def load() -> ctypes.CDLL:
     lib.sfb_lookup_forward.argtypes = [P, P, P, I64, P] + [I32] * 8 + [P]
     lib.sfb_lookup_backward.restype = ctypes.c_int
     lib.sfb_lookup_backward.argtypes = [P, P, I64, P, P] + [I32] * 8 + [P]
+    lib.sfb_lookup4d_forward.restype = ctypes.c_int
+    lib.sfb_lookup4d_forward.argtypes = [P, P, P, P, I32, P, P] + [I32] * 5 + [ctypes.c_float, P]
+    lib.sfb_lookup4d_backward.restype = ctypes.c_int
+    lib.sfb_lookup4d_backward.argtypes = [P, P, P, P, I32, P, P, P, P] + [I32] * 5 + [ctypes.c_float, P]
     lib.sfb_separation_level_forward_fmaps.restype = ctypes.c_int
     lib.sfb_separation_level_forward_fmaps.argtypes = [P, P, ctypes.c_float] + [P] * 6 + [I32, I32] + [P] * 4 + tail
     lib.sfb_separation_level_backward_fmaps.restype = ctypes.c_int

@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(CSRC, "libsepflow_b200.so")
-SOURCES = ["prepare.cu", "sweep.cu", "grad_gemm.cu", "attention.cu", "lookup.cu", "resample.cu", "c_abi.cu"]
+SOURCES = ["prepare.cu", "sweep.cu", "grad_gemm.cu", "attention.cu", "lookup.cu", "lookup4d.cu", "resample.cu", "c_abi.cu"]
 HEADERS = ["kernels.h", "sm100_primitives.cuh", os.path.join("..", "..", "include", "sepflow_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -24,7 +24,7 @@ import torch.nn.functional as F
 
 from .functions import (ComputeMaxArgmaxAvgFunction, ComputeMaxAvgFunction, ComputeSelfCompressionFunction,
                         FusedMaxArgmaxAvgFunction, FusedSelfCompressionFunction, SeparationCompressionCF,
-                        LookupFunction, SeparationLevelFunction, SeparationMaxAvgCF, SeparationPyramidFunction,
+                        Lookup4dFunction, LookupFunction, SeparationLevelFunction, SeparationMaxAvgCF, SeparationPyramidFunction,
                         SeparationState)
 from . import ops as _ops
 
@@ -57,6 +57,7 @@ class AlternateCorrBlockSepflow:
         for _ in range(num_levels - 1):
             fmap2 = F.avg_pool2d(fmap2, 2, stride=2)
             self.pyramid.append(fmap2)
+        self._channels_last = None
 
     def _one_node_per_level(self, attention_weights) -> bool:
         return (self.channels_first and self.fuse_backward and self.fuse_attention and attention_weights is not None
@@ -136,7 +137,18 @@ class AlternateCorrBlockSepflow:
     def __call__(self, coords, sep=False, attention_weights=None):
         if sep:
             return self.separate(attention_weights)
-        raise NotImplementedError("Missing the cpp/cuda part for lookup of the 4d correlation volume without storing it")
+        return self.lookup(coords)
+
+    def lookup(self, coords):
+        """Lookup on the 4D correlation volume pyramid without storing it: the branch the reference leaves as
+        NotImplementedError (core/corr.py:491-510).  coords (B,2,H1,W1) -> (B, levels*(2r+1)^2, H1, W1), equal to
+        the dense block's lookup (core/corr.py:192-247).  The channels-last copies that the reference's sketch makes
+        on every call (core/corr.py:500-501) are made once per block."""
+        if self._channels_last is None:
+            self._channels_last = [t.permute(0, 2, 3, 1).contiguous() for t in [self.fmap1_l0] + self.pyramid]
+        F1, *F2_levels = self._channels_last
+        scale = 1.0 / math.sqrt(self.fmap1_l0.shape[1])
+        return Lookup4dFunction.apply(coords.to(F1.dtype).contiguous(), self.radius, scale, F1, *F2_levels)
 
 
 class CorrBlock1D:

@@ -81,7 +81,7 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 enum KernelId : int {
   KID_PREPARE = 0, KID_PACK, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
   KID_GRAD_COMPRESS_IMG1, KID_GRAD_COMPRESS_IMG2, KID_GRAD_FUSED_IMG1, KID_GRAD_FUSED_IMG2, KID_ATTENTION_FWD,
-  KID_ATTENTION_BWD, KID_LOOKUP, KID_RESAMPLE, KID_COUNT
+  KID_ATTENTION_BWD, KID_LOOKUP, KID_RESAMPLE, KID_LOOKUP4D, KID_COUNT
 };
 const char* const kKernelNames[KID_COUNT] = {
     "prepare(round_copy+f2_means)", "pack_kernel/unpack_kernel", "sweep_kernel<maxavg>", "sweep_kernel<compress>", "sweep_kernel<dump>",
@@ -89,7 +89,8 @@ const char* const kKernelNames[KID_COUNT] = {
     "grad_gemm_kernel<compress,image1-major>", "grad_gemm_kernel<compress,image2-major>",
     "grad_gemm_kernel<fused,image1-major>", "grad_gemm_kernel<fused,image2-major>",
     "attention_forward_kernel", "attention backward (logit, input, weight grads)",
-    "lookup kernels (pyramid, forward, backward)", "upsample_displacement kernels"};
+    "lookup kernels (pyramid, forward, backward)", "upsample_displacement kernels",
+    "lookup4d kernels (forward, backward)"};
 struct TimingRec { cudaEvent_t e0, e1; int id; int launches; };
 std::mutex g_timing_mu;
 bool g_timing_on = false;
@@ -1139,6 +1140,68 @@ int sfb_lookup_backward(const float* gout, const float* coord, int64_t coord_bat
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SFB_CUDA(timed(KID_LOOKUP, levels > 1 ? 2 : 1, st, [&] {
     return launch_lookup_backward(ld, gout, coord, coord_batch_stride, gcorr, gpyramid, clamp_unit, st);
+  }));
+  return SFB_OK;
+}
+
+namespace {
+int check_lookup4d(const void* F1, const void* const* F2, const int32_t* H2, const int32_t* W2, int32_t levels,
+                   const void* coords, int32_t B, int32_t H1, int32_t W1, int32_t C, int32_t radius,
+                   Lookup4dDims* out) {
+  if (B < 1 || H1 < 1 || W1 < 1 || C < 1) return fail(SFB_ERR_INVALID_ARGUMENT, "B, H1, W1 and C must be positive");
+  if (C % 4 != 0 || C > 512)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "the 4D lookup needs C % 4 == 0 and C <= 512");
+  if (levels < 1 || levels > LOOKUP_MAX_LEVELS) return fail(SFB_ERR_INVALID_ARGUMENT, "levels must be in [1, 8]");
+  if (radius < 0 || radius > 4) return fail(SFB_ERR_INVALID_ARGUMENT, "radius must be in [0, 4]");
+  if (F1 == nullptr || F2 == nullptr || H2 == nullptr || W2 == nullptr || coords == nullptr)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "F1, F2_levels, H2, W2 and coords must not be NULL");
+  if ((long long)H1 * W1 > INT32_MAX / 4) return fail(SFB_ERR_INVALID_ARGUMENT, "H1*W1 too large");
+  if (reinterpret_cast<uintptr_t>(F1) % 16 != 0)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "feature pointers of the 4D lookup must be 16-byte aligned");
+  out->B = B; out->H1 = H1; out->W1 = W1; out->C = C; out->levels = levels; out->radius = radius;
+  for (int l = 0; l < levels; ++l) {
+    // grid_sample's normalisation divides by size - 1 (core/utils/utils.py:114-115)
+    if (H2[l] < 2 || W2[l] < 2)
+      return fail(SFB_ERR_INVALID_ARGUMENT, "every pyramid level needs H2 >= 2 and W2 >= 2");
+    if (F2[l] == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "F2_levels holds a NULL pointer");
+    if (reinterpret_cast<uintptr_t>(F2[l]) % 16 != 0)
+      return fail(SFB_ERR_INVALID_ARGUMENT, "feature pointers of the 4D lookup must be 16-byte aligned");
+    if ((long long)H2[l] * W2[l] > INT32_MAX / 4) return fail(SFB_ERR_INVALID_ARGUMENT, "H2*W2 too large");
+    out->H2[l] = H2[l]; out->W2[l] = W2[l];
+  }
+  return SFB_OK;
+}
+}  // namespace
+
+int sfb_lookup4d_forward(const float* F1, const float* const* F2_levels, const int32_t* H2, const int32_t* W2,
+                         int32_t levels, const float* coords, float* out, int32_t B, int32_t H1, int32_t W1, int32_t C,
+                         int32_t radius, float scale, void* stream) {
+  Lookup4dDims ld;
+  SFB_TRY(check_lookup4d(F1, reinterpret_cast<const void* const*>(F2_levels), H2, W2, levels, coords, B, H1, W1, C,
+                         radius, &ld));
+  if (out == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "out must not be NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_LOOKUP4D, 1, st, [&] { return launch_lookup4d_forward(ld, F1, F2_levels, coords, out, scale, st); }));
+  return SFB_OK;
+}
+
+int sfb_lookup4d_backward(const float* F1, const float* const* F2_levels, const int32_t* H2, const int32_t* W2,
+                          int32_t levels, const float* coords, const float* gout, float* gF1,
+                          float* const* gF2_levels, int32_t B, int32_t H1, int32_t W1, int32_t C, int32_t radius,
+                          float scale, void* stream) {
+  Lookup4dDims ld;
+  SFB_TRY(check_lookup4d(F1, reinterpret_cast<const void* const*>(F2_levels), H2, W2, levels, coords, B, H1, W1, C,
+                         radius, &ld));
+  if (gout == nullptr || gF1 == nullptr || gF2_levels == nullptr)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "gout, gF1 and gF2_levels must not be NULL");
+  for (int l = 0; l < levels; ++l)
+    if (gF2_levels[l] == nullptr || reinterpret_cast<uintptr_t>(gF2_levels[l]) % 16 != 0)
+      return fail(SFB_ERR_INVALID_ARGUMENT, "gF2_levels holds a NULL or not 16-byte aligned pointer");
+  if (reinterpret_cast<uintptr_t>(gF1) % 16 != 0)
+    return fail(SFB_ERR_INVALID_ARGUMENT, "gF1 must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SFB_CUDA(timed(KID_LOOKUP4D, 1, st, [&] {
+    return launch_lookup4d_backward(ld, F1, F2_levels, coords, gout, gF1, gF2_levels, scale, st);
   }));
   return SFB_OK;
 }

@@ -178,4 +178,19 @@ cudaError_t launch_lookup_forward(const LookupDims& d, const float* corr, const 
 cudaError_t launch_lookup_backward(const LookupDims& d, const float* gout, const float* coord, long long coord_sb,
                                    float* gcorr, float* gpyramid, int clamp_unit, cudaStream_t stream);
 
+// Lookup on the 4D correlation volume without storing it (the call core/corr.py:491-510 leaves unimplemented; its
+// result is the dense block's lookup, core/corr.py:192-247).  F1 (B, H1, W1, C) and the image-2 feature pyramid
+// F2[l] (B, H2[l], W2[l], C), channels innermost; coords (B, 2, H1, W1) = (x, y) per pixel;
+// out (B, levels*(2*radius+1)^2, H1, W1), every product times `scale`.  C % 4 == 0, C <= 512, radius <= 4.
+struct Lookup4dDims {
+  int B, H1, W1, C, levels, radius;
+  int H2[LOOKUP_MAX_LEVELS], W2[LOOKUP_MAX_LEVELS];
+};
+cudaError_t launch_lookup4d_forward(const Lookup4dDims& d, const float* F1, const float* const* F2,
+                                    const float* coords, float* out, float scale, cudaStream_t stream);
+// gF1 (shape of F1) is overwritten; gF2[l] (shape of F2[l]) is zeroed and then accumulated with float reductions.
+cudaError_t launch_lookup4d_backward(const Lookup4dDims& d, const float* F1, const float* const* F2,
+                                     const float* coords, const float* gout, float* gF1, float* const* gF2,
+                                     float scale, cudaStream_t stream);
+
 }  // namespace sfb

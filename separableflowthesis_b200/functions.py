@@ -338,3 +338,26 @@ class LookupFunction(Function):
         with torch.cuda.device_of(grad_out):
             gcorr = MemorySaver.lookup_backward(shape, coord, grad_out.contiguous(), levels, radius, clamp_unit)
         return gcorr, None, None, None, None, None
+
+
+class Lookup4dFunction(Function):
+    """Lookup on the 4D correlation volume without storing it.  ``apply(coords, radius, scale, F1, *F2_levels)`` with
+    channels-last features -> (B, levels*(2r+1)^2, H1, W1); gradients for the features only (the model detaches
+    the coordinates, core/sepflow.py:193)."""
+
+    @staticmethod
+    def forward(ctx, coords, radius, scale, F1, *F2_levels):
+        with torch.cuda.device_of(F1):
+            out = MemorySaver.lookup4d_forward(F1, list(F2_levels), coords, radius, scale)
+        ctx.save_for_backward(coords, F1, *F2_levels)
+        ctx.cfg = (radius, scale)
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_out):
+        coords, F1, *F2_levels = ctx.saved_tensors
+        radius, scale = ctx.cfg
+        with torch.cuda.device_of(grad_out):
+            gF1, gF2 = MemorySaver.lookup4d_backward(F1, F2_levels, coords, grad_out.contiguous(), radius, scale)
+        return (None, None, None, gF1, *gF2)

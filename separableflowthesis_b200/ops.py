@@ -589,3 +589,70 @@ def corr_volume(img1_features_l0, img2_features_lk) -> torch.Tensor:
     S = torch.empty(s.B, s.H1, s.W1, s.H2, s.W2, dtype=torch.float32, device=F1.device)
     _call("sfb_corr_volume", _lib.OP_CORR_VOLUME, s, F1.device, (F1, F2, S))
     return S
+
+
+def _check_lookup4d(F1, F2_levels, coords, radius):
+    if not (isinstance(F1, torch.Tensor) and F1.is_cuda and F1.dtype == torch.float32 and F1.dim() == 4
+            and F1.is_contiguous()):
+        raise RuntimeError("F1 must be a contiguous CUDA float32 tensor of shape (B, H1, W1, C)")
+    B, H1, W1, C = F1.shape
+    if C % 4 != 0 or C > 512:
+        raise RuntimeError("the 4D lookup needs C % 4 == 0 and C <= 512")
+    if not 0 <= radius <= 4:
+        raise RuntimeError("radius must be in [0, 4]")
+    if not 1 <= len(F2_levels) <= 8:
+        raise RuntimeError("between 1 and 8 pyramid levels")
+    for l, f2 in enumerate(F2_levels):
+        if not (isinstance(f2, torch.Tensor) and f2.device == F1.device and f2.dtype == torch.float32 and f2.dim() == 4
+                and f2.is_contiguous() and f2.shape[0] == B and f2.shape[3] == C):
+            raise RuntimeError(f"F2_levels[{l}] must be a contiguous float32 tensor of shape (B, H2, W2, C) on {F1.device}")
+        if f2.shape[1] < 2 or f2.shape[2] < 2:
+            raise RuntimeError("every pyramid level needs H2 >= 2 and W2 >= 2")
+    _check_like(coords, "coords", (B, 2, H1, W1), torch.float32, F1.device)
+    if not coords.is_contiguous():
+        raise RuntimeError("coords must be contiguous")
+    return B, H1, W1, C
+
+
+def _level_arrays(tensors):
+    n = len(tensors)
+    ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in tensors])
+    H2 = (ctypes.c_int32 * n)(*[t.shape[1] for t in tensors])
+    W2 = (ctypes.c_int32 * n)(*[t.shape[2] for t in tensors])
+    return ptrs, H2, W2
+
+
+def lookup4d_forward(F1, F2_levels, coords, radius=4, scale=1.0) -> torch.Tensor:
+    """Lookup on the 4D correlation volume without storing it (the call core/corr.py:491-510 leaves
+    unimplemented; same result as the dense block's lookup, core/corr.py:192-247).  F1 (B,H1,W1,C),
+    F2_levels[l] (B,H2_l,W2_l,C) channels-last, coords (B,2,H1,W1) -> (B, levels*(2r+1)^2, H1, W1)."""
+    B, H1, W1, C = _check_lookup4d(F1, F2_levels, coords, radius)
+    n = len(F2_levels)
+    out = torch.empty(B, n * (2 * radius + 1) ** 2, H1, W1, dtype=torch.float32, device=F1.device)
+    ptrs, H2, W2 = _level_arrays(F2_levels)
+    lib = _lib.load()
+    with torch.cuda.device(F1.device):
+        stream = torch.cuda.current_stream(F1.device).cuda_stream
+        _raise_on(lib.sfb_lookup4d_forward(_ptr(F1), ptrs, H2, W2, n, _ptr(coords), _ptr(out), B, H1, W1, C, radius,
+                                           float(scale), ctypes.c_void_p(stream)), "sfb_lookup4d_forward")
+    return out
+
+
+def lookup4d_backward(F1, F2_levels, coords, grad_out, radius=4, scale=1.0):
+    """(gF1, [gF2_l]) for upstream gradient grad_out of lookup4d_forward."""
+    B, H1, W1, C = _check_lookup4d(F1, F2_levels, coords, radius)
+    n = len(F2_levels)
+    _check_like(grad_out, "grad_out", (B, n * (2 * radius + 1) ** 2, H1, W1), torch.float32, F1.device)
+    if not grad_out.is_contiguous():
+        raise RuntimeError("grad_out must be contiguous")
+    gF1 = torch.empty_like(F1)
+    gF2 = [torch.empty_like(f2) for f2 in F2_levels]
+    ptrs, H2, W2 = _level_arrays(F2_levels)
+    gptrs, _, _ = _level_arrays(gF2)
+    lib = _lib.load()
+    with torch.cuda.device(F1.device):
+        stream = torch.cuda.current_stream(F1.device).cuda_stream
+        _raise_on(lib.sfb_lookup4d_backward(_ptr(F1), ptrs, H2, W2, n, _ptr(coords), _ptr(grad_out), _ptr(gF1), gptrs,
+                                            B, H1, W1, C, radius, float(scale), ctypes.c_void_p(stream)),
+                  "sfb_lookup4d_backward")
+    return gF1, gF2

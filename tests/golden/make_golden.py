@@ -140,6 +140,7 @@ def main(ref_root: str):
         })
     np.savez_compressed(os.path.join(HERE, "ops_b2_c12_8x12_k3.npz"), **store)
     lookup_vectors()
+    lookup4d_vectors()
     print("golden vectors written to", HERE)
 
 
@@ -176,6 +177,37 @@ def lookup_vectors():
     # the reference returns float32 (core/corr.py:602,623: ``.float()``), so its outputs and the gradients that
     # pass through that cast carry float32 rounding; the float64 oracle agrees to that rounding
     assert max(e1, e2, e3, e4) < 1e-6
+
+
+
+
+def lookup4d_vectors():
+    """The reference's dense block (core/corr.py:15-247, pure torch with guid=None) looked up at seeded coordinates
+    that reach inside, across and beyond the image: the result the memory-saving block's unimplemented branch
+    (core/corr.py:491-510) would have to return, and the gradients of both feature maps."""
+    from core.corr import CorrBlock  # reference code
+    B, C, H, W, levels, radius = 1, 8, 12, 16, 3, 4
+    g = torch.Generator().manual_seed(1357)
+    f1 = torch.randn(B, C, H, W, generator=g, dtype=torch.float64).requires_grad_(True)
+    f2 = torch.randn(B, C, H, W, generator=g, dtype=torch.float64).requires_grad_(True)
+    coords = torch.stack((torch.rand(B, H, W, generator=g, dtype=torch.float64) * (W + 8) - 4,
+                          torch.rand(B, H, W, generator=g, dtype=torch.float64) * (H + 8) - 4), dim=1)
+    coords[0, :, 0, 0] = torch.tensor([3.0, 7.0], dtype=torch.float64)      # exact integers
+    coords[0, :, 0, 1] = torch.tensor([-0.5, float(H - 1)], dtype=torch.float64)
+    coords[0, :, 0, 2] = torch.tensor([float(W - 1), 0.0], dtype=torch.float64)
+    coords[0, :, 0, 3] = torch.tensor([-40.0, 55.0], dtype=torch.float64)   # window entirely in the padding
+    out = CorrBlock(f1, f2, None, num_levels=levels, radius=radius)(coords)
+    w = torch.randn(out.shape, generator=g, dtype=torch.float64)
+    (out.double() * w).sum().backward()
+    np.savez_compressed(os.path.join(HERE, "lookup4d_b1_c8_12x16.npz"),
+                        f1=f1.detach().numpy(), f2=f2.detach().numpy(), coords=coords.numpy(),
+                        out=out.detach().numpy(), w=w.float().numpy(),
+                        g_f1=f1.grad.float().numpy(), g_f2=f2.grad.float().numpy(),
+                        levels=np.int64(levels), radius=np.int64(radius))
+    o = oracle.lookup4d_dense_forward(f1.detach(), f2.detach(), coords, levels, radius)
+    g1, g2 = oracle.lookup4d_dense_backward(f1.detach(), f2.detach(), coords, w, levels, radius)
+    print(f"oracle lookup4d vs reference CorrBlock: out {(o - out.detach()).abs().max().item():.2e} "
+          f"g_f1 {(g1 - f1.grad).abs().max().item():.2e} g_f2 {(g2 - f2.grad).abs().max().item():.2e}")
 
 
 if __name__ == "__main__":

@@ -77,6 +77,19 @@ def test_argument_validation_of_the_call_site_entry_points(lib):
     assert lib.sfb_lookup_pyramid_bytes(2, 1, 16, 3, 5, 5) == 0          # coarsest level would have one entry
     assert lib.sfb_lookup_forward(p, p, p, 15, p, 2, 1, 1, 3, 5, 1, 4, 0, None) == _lib.SFB_ERR_INVALID_ARGUMENT
     assert lib.sfb_lookup_forward(p, p, p, 15, p, 2, 1, 16, 3, 5, 9, 4, 0, None) == _lib.SFB_ERR_UNSUPPORTED_SHAPE
+    levels = (P * 2)(a16, a16)
+    H2, W2 = (ctypes.c_int32 * 2)(8, 4), (ctypes.c_int32 * 2)(8, 4)
+    f = ctypes.c_float(1.0)
+    assert lib.sfb_lookup4d_forward(p, levels, H2, W2, 2, p, p, 1, 8, 8, 30, 4, f, None) == _lib.SFB_ERR_INVALID_ARGUMENT
+    assert b"C % 4" in lib.sfb_last_error()
+    assert lib.sfb_lookup4d_forward(p, levels, H2, W2, 2, p, p, 1, 8, 8, 32, 5, f, None) == _lib.SFB_ERR_INVALID_ARGUMENT
+    assert lib.sfb_lookup4d_forward(p, levels, H2, W2, 9, p, p, 1, 8, 8, 32, 4, f, None) == _lib.SFB_ERR_INVALID_ARGUMENT
+    one = (ctypes.c_int32 * 2)(8, 1)
+    assert lib.sfb_lookup4d_forward(p, levels, H2, one, 2, p, p, 1, 8, 8, 32, 4, f, None) == _lib.SFB_ERR_INVALID_ARGUMENT
+    assert b"H2 >= 2" in lib.sfb_last_error()
+    holes = (P * 2)(a16, None)
+    assert lib.sfb_lookup4d_backward(p, levels, H2, W2, 2, p, p, p, holes, 1, 8, 8, 32, 4, f, None) \
+        == _lib.SFB_ERR_INVALID_ARGUMENT
     assert lib.sfb_upsample_displacement(p, p, 100, 1, 2, 8, 4, 3, 5, None) == _lib.SFB_ERR_UNSUPPORTED_SHAPE
     assert b"upsampling" in lib.sfb_last_error()
     assert lib.sfb_upsample_displacement(p, None, 100, 1, 2, 4, 8, 3, 5, None) == _lib.SFB_ERR_INVALID_ARGUMENT

@@ -67,9 +67,21 @@ def test_block_error_behaviour(oracle_backend):
     f = torch.randn(1, 8, 4, 6)
     with pytest.raises(Exception, match="NLF"):
         sfb.AlternateCorrBlockSepflow(f, f, guid=torch.zeros(1))
-    blk = sfb.AlternateCorrBlockSepflow(f, f, None, num_levels=2)
-    with pytest.raises(NotImplementedError):
-        blk(None, sep=False)
+
+
+def test_block_lookup_matches_reference_dense_block(golden_dir, oracle_backend):
+    """sep=False: the branch the reference leaves unimplemented (core/corr.py:491-510) returns the dense block's
+    lookup (core/corr.py:192-247), and its gradients reach both feature maps through the pooling pyramid."""
+    g = np.load(os.path.join(golden_dir, "lookup4d_b1_c8_12x16.npz"))
+    f1 = _t(g["f1"]).requires_grad_(True)
+    f2 = _t(g["f2"]).requires_grad_(True)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=int(g["levels"]), radius=int(g["radius"]),
+                                        support_backward=True)
+    monkey_out = blk(_t(g["coords"]), sep=False)
+    assert (monkey_out - _t(g["out"]).double()).abs().max().item() < 1e-6
+    (monkey_out * _t(g["w"]).double()).sum().backward()
+    assert (f1.grad - _t(g["g_f1"]).double()).abs().max().item() < 1e-5
+    assert (f2.grad - _t(g["g_f2"]).double()).abs().max().item() < 1e-5
 
 
 def test_ops_reject_cpu_and_malformed_tensors():

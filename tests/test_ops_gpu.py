@@ -369,6 +369,83 @@ def test_corrblock1d_against_reference_vectors(golden_dir, cuda_device):
     assert relerr(corr2.grad, torch.from_numpy(gold["g_corr2"])) < LOOKUP_TOL
 
 
+def _lookup4d_coords(kind, B, H1, W1, H2, W2, gen):
+    """(B,2,H1,W1) positions in image 2: 'smooth' = the pixel grid plus a slowly varying displacement (neighbouring
+    windows overlap, four pixels per pass), 'random' = anywhere inside and around the image (one pixel per pass),
+    'mixed' = smooth with a block of random ones, exact integers and far-away positions."""
+    ys, xs = torch.meshgrid(torch.arange(H1, dtype=torch.float32), torch.arange(W1, dtype=torch.float32), indexing="ij")
+    sx, sy = (W2 - 1) / max(W1 - 1, 1), (H2 - 1) / max(H1 - 1, 1)
+    smooth = torch.stack((xs * sx + 2.5 * torch.sin(ys / 3.0) + 0.3, ys * sy + 1.5 * torch.cos(xs / 4.0) - 0.2))
+    smooth = smooth.unsqueeze(0).repeat(B, 1, 1, 1)
+    rnd = torch.stack((torch.rand(B, H1, W1, generator=gen) * (W2 + 12) - 6,
+                       torch.rand(B, H1, W1, generator=gen) * (H2 + 12) - 6), dim=1)
+    if kind == "smooth":
+        return smooth
+    if kind == "random":
+        return rnd
+    out = smooth.clone()
+    out[:, :, : max(H1 // 3, 1)] = rnd[:, :, : max(H1 // 3, 1)]
+    out[0, :, -1, 0] = torch.tensor([3.0, 2.0])
+    out[0, :, -1, -1] = torch.tensor([-500.0, 1.0e7])
+    return out
+
+
+# (B, C, H1, W1, H2, W2, levels, radius, coordinates)
+LOOKUP4D_CASES = [
+    (1, 4, 1, 1, 2, 2, 1, 0, "random"),
+    (1, 8, 12, 16, 12, 16, 3, 4, "mixed"),
+    (2, 256, 20, 28, 20, 28, 3, 4, "smooth"),
+    (2, 256, 9, 13, 9, 13, 2, 4, "random"),
+    (1, 100, 9, 13, 16, 11, 2, 2, "mixed"),       # C not a multiple of 128, N1 not a multiple of 32, H2 != H1
+    (1, 384, 8, 12, 8, 12, 2, 3, "smooth"),
+    (1, 512, 5, 7, 17, 33, 4, 1, "mixed"),
+]
+
+
+@pytest.mark.parametrize("case", LOOKUP4D_CASES)
+def test_lookup4d_forward_backward(case, cuda_device):
+    """4D lookup without the stored volume, and its feature gradients, against the oracle's restatement of the
+    dense block's einsum / avg_pool2d / grid_sample chain (core/corr.py:286-296, 32-39, 200-247) in float64."""
+    B, C, H1, W1, H2, W2, levels, radius, kind = case
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(4242 + C + H1)
+    f1 = torch.randn(B, H1, W1, C, generator=gen)
+    f2 = torch.randn(B, C, H2, W2, generator=gen)
+    pyr = [f2]
+    for _ in range(levels - 1):
+        pyr.append(F.avg_pool2d(pyr[-1], 2, stride=2))
+    F2s = [t.permute(0, 2, 3, 1).contiguous() for t in pyr]
+    coords = _lookup4d_coords(kind, B, H1, W1, H2, W2, gen)
+    scale = 1.0 / C ** 0.5
+    out = ops.lookup4d_forward(f1.to(dev), [t.to(dev) for t in F2s], coords.to(dev), radius, scale)
+    ref = orc.lookup4d_forward(f1.double(), [t.double() for t in F2s], coords.double(), radius, scale)
+    assert out.shape == ref.shape and relerr(out, ref) < LOOKUP_TOL
+    gout = torch.randn(out.shape, generator=gen)
+    gF1, gF2 = ops.lookup4d_backward(f1.to(dev), [t.to(dev) for t in F2s], coords.to(dev), gout.to(dev), radius, scale)
+    rF1, rF2 = orc.lookup4d_backward(f1.double(), [t.double() for t in F2s], coords.double(), gout.double(), radius, scale)
+    assert relerr(gF1, rF1) < LOOKUP_TOL
+    for a, b in zip(gF2, rF2):
+        assert relerr(a, b) < LOOKUP_TOL
+
+
+def test_block_lookup_against_reference_vectors(golden_dir, cuda_device):
+    """AlternateCorrBlockSepflow(...)(coords): the branch the reference leaves unimplemented (core/corr.py:491-510),
+    against the output and feature gradients of the reference's own dense CorrBlock (core/corr.py:192-247)."""
+    gold = np.load(os.path.join(golden_dir, "lookup4d_b1_c8_12x16.npz"))
+    dev = cuda_device
+    f1 = torch.from_numpy(gold["f1"]).float().to(dev).requires_grad_(True)
+    f2 = torch.from_numpy(gold["f2"]).float().to(dev).requires_grad_(True)
+    blk = sfb.AlternateCorrBlockSepflow(f1, f2, None, num_levels=int(gold["levels"]), radius=int(gold["radius"]),
+                                        support_backward=True)
+    coords = torch.from_numpy(gold["coords"]).float().to(dev)
+    out = blk(coords)
+    assert relerr(out, torch.from_numpy(gold["out"])) < LOOKUP_TOL
+    assert torch.equal(out, blk(coords))
+    (out * torch.from_numpy(gold["w"]).to(dev)).sum().backward()
+    assert relerr(f1.grad, torch.from_numpy(gold["g_f1"])) < LOOKUP_TOL
+    assert relerr(f2.grad, torch.from_numpy(gold["g_f2"])) < LOOKUP_TOL
+
+
 def test_ops_from_a_fresh_thread(cuda_device):
     """A thread that has not touched CUDA yet (an autograd worker whose first node is one of these ops) can call
     every entry point: the library binds the device context itself before it builds tensor maps."""

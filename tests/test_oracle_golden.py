@@ -106,3 +106,36 @@ def test_lookup_matches_reference_corrblock1d(golden_dir):
         assert out.shape == ref.shape and (out - ref).abs().max().item() < 1e-6
         gc = orc.lookup_backward(corr.shape, coords[:, i - 1], torch.from_numpy(g[f"w{i}"]).double(), levels, radius, clamp)
         assert (gc - torch.from_numpy(g[f"g_corr{i}"]).double()).abs().max().item() < 1e-6
+
+
+def test_lookup4d_matches_reference_dense_block(golden_dir):
+    """The oracle's 4D lookup (stored-volume form and memory-saving form) against the output and feature gradients
+    of the reference's own dense CorrBlock (core/corr.py:192-247), generated by tests/golden/make_golden.py."""
+    g = np.load(os.path.join(golden_dir, "lookup4d_b1_c8_12x16.npz"))
+    levels, radius = int(g["levels"]), int(g["radius"])
+    f1, f2 = torch.from_numpy(g["f1"]), torch.from_numpy(g["f2"])
+    coords, w = torch.from_numpy(g["coords"]), torch.from_numpy(g["w"]).double()
+    out = orc.lookup4d_dense_forward(f1, f2, coords, levels, radius)
+    assert (out - torch.from_numpy(g["out"]).double()).abs().max().item() < 1e-6
+    g1, g2 = orc.lookup4d_dense_backward(f1, f2, coords, w, levels, radius)
+    assert (g1 - torch.from_numpy(g["g_f1"]).double()).abs().max().item() < 1e-5
+    assert (g2 - torch.from_numpy(g["g_f2"]).double()).abs().max().item() < 1e-5
+
+    # memory-saving form: pooled features instead of a pooled volume
+    pyr = [f2]
+    for _ in range(levels - 1):
+        pyr.append(torch.nn.functional.avg_pool2d(pyr[-1], 2, stride=2))
+    F1 = f1.permute(0, 2, 3, 1).contiguous()
+    F2s = [t.permute(0, 2, 3, 1).contiguous() for t in pyr]
+    scale = 1.0 / f1.shape[1] ** 0.5
+    out2 = orc.lookup4d_forward(F1, F2s, coords, radius, scale)
+    assert (out2 - out).abs().max().item() < 1e-12
+    gF1, gF2s = orc.lookup4d_backward(F1, F2s, coords, w, radius, scale)
+    assert (gF1.permute(0, 3, 1, 2) - g1).abs().max().item() < 1e-12
+    with torch.enable_grad():
+        x = f2.clone().requires_grad_(True)
+        p = [x]
+        for _ in range(levels - 1):
+            p.append(torch.nn.functional.avg_pool2d(p[-1], 2, stride=2))
+        torch.autograd.backward(p, [t.permute(0, 3, 1, 2) for t in gF2s])
+    assert (x.grad - g2).abs().max().item() < 1e-12
