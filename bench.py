@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the cost-volume separation hot path: cells/s of forward + backward.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 1..5] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 1..5] [--impl ours|reference|reference-cuda]
 
 One "step" is one pass of the four ops over one batch of synthetic feature maps:
 max/argmax/avg forward, compression forward, compression backward, max/avg backward (forward-only
@@ -424,6 +424,59 @@ def run_lookup4d_bench(args, cfg, device, emit):
                        "note": "gather of image-2 feature rows through L1/L2; HBM traffic is not the limiter"}})
 
 
+def run_reference_cuda(args, cfg, metric, unit, emit):
+    """`--impl reference-cuda`: the five ops of the reference's own CUDA extension (oracle/_ref/MemorySaver.so, built
+    unmodified from libs/MemorySaver/src) on one GPU, and this library's five ops on the same tensors, in the
+    reference's layouts with random softmaxed attention weights (the op sequence of the survey's metric).  One
+    line per implementation.  The reference needs seconds per step, so it runs `steps` capped at 3."""
+    import importlib.util
+    so = os.path.join(ROOT, "oracle", "_ref", "MemorySaver.so")
+    if not os.path.exists(so):
+        emit({"impl": "reference-cuda", "unavailable": "oracle/_ref/MemorySaver.so not built (oracle/build_ref_cuda.py)"})
+        return
+    if cfg["Kc"] != 2:
+        emit({"impl": "reference-cuda",
+              "unavailable": "the reference's forward kernel computes two attention channels only: use --config 2 or 4"})
+        return
+    from separableflowthesis_b200 import ops
+    spec = importlib.util.spec_from_file_location("MemorySaver", so)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    device = torch.device("cuda", 0)
+    B, H, W, Kc = cfg["B"], cfg["H"], cfg["W"], cfg["Kc"]
+    g = torch.Generator().manual_seed(SEED)
+    F1 = (torch.randn(B, H, W, C_FEAT, generator=g) / C_FEAT ** 0.5).to(device)
+    F2 = torch.randn(B, H, W, C_FEAT, generator=g).to(device)
+    A_u = torch.randn(B, H, W, Kc, W, generator=g).softmax(-1).to(device)
+    A_v = torch.randn(B, H, W, Kc, H, generator=g).softmax(-1).to(device)
+    gMu, gMv = torch.randn(B, H, W, 2, H, generator=g).to(device), torch.randn(B, H, W, 2, W, generator=g).to(device)
+    gCu, gCv = torch.randn(B, H, W, Kc, H, generator=g).to(device), torch.randn(B, H, W, Kc, W, generator=g).to(device)
+    cells = float(B) * (H * W) ** 2
+
+    def step(mod):
+        _, _, au, av = mod.max_argmax_avg_forward(F1, F2)
+        mod.compression_forward(F1, F2, A_u, A_v)
+        if cfg["bwd"]:
+            mod.compression_backward(F1, F2, A_u, A_v, gCu, gCv)
+            mod.max_argmax_avg_backward(F1, F2, au, av, gMu, gMv)
+
+    for name, mod, steps, warm in (("reference-cuda", ref, min(args.steps, 3), 1), ("ours", ops, args.steps, max(args.warmup, 3))):
+        for _ in range(warm):
+            step(mod)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step(mod)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        emit({"impl": name, "metric": metric, "value": cells / (ms * 1e-3), "unit": unit, "n_gpus": 1, "steps": steps,
+              "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+              "dtype": "f32" if name != "ours" else "tf32 operands, fp32 accumulate", "data": "synthetic",
+              "config": {"workload": cfg["name"], "path": "the five ops in the reference's layouts, device-resident"}})
+
+
 class E2E:
     """The call a user of the reference makes: channels-first feature maps in host memory ->
     AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
@@ -613,7 +666,11 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"],
+                    help="reference: the CPU port of the reference's dense path (the driver's reference arm); "
+                         "reference-cuda: the reference's own CUDA extension built by oracle/build_ref_cuda.py, timed on "
+                         "the five ops next to this library's five ops (configs with Kc = 2 only: the reference's forward "
+                         "kernel is compiled for two attention channels, MemorySaver_kernel_forward.cu:20)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-roofline", action="store_true", help="skip the per-kernel timing pass and the TF32 peak run")
@@ -664,6 +721,11 @@ def main():
                 "e2e": {"value": base["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
         emit(line)
+        return
+
+    if args.impl == "reference-cuda":
+        if rank == 0:
+            run_reference_cuda(args, cfg, metric, unit, emit)
         return
 
     import torch.distributed as dist

@@ -5,8 +5,8 @@ the bench can time it beside this library; nothing in the product imports it.  N
 
     python oracle/build_ref_cuda.py /path/to/SeparableFlowThesis
 
-The recipe is the four source files handed to nvcc with torch's include and library paths; the reference's
-setup.py is not run.  Compiled for sm_100a.
+The recipe is the four source files handed to nvcc (one process each) with torch's include and library paths; the
+reference's setup.py is not run.  Compiled for sm_100a; takes several minutes.
 """
 from __future__ import annotations
 
@@ -33,17 +33,28 @@ def build(ref_root: str, force: bool = False) -> str:
     import torch
     os.makedirs(OUT_DIR, exist_ok=True)
     lib_dir = os.path.join(os.path.dirname(torch.__file__), "lib")
-    cmd = [os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
-           "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w", "-Xcompiler", "-fPIC", "-shared",
-           "-DTORCH_EXTENSION_NAME=MemorySaver", "-DTORCH_API_INCLUDE_EXTENSION_H",
-           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w", "-Xcompiler", "-fPIC",
+             "-DTORCH_EXTENSION_NAME=MemorySaver", "-DTORCH_API_INCLUDE_EXTENSION_H",
+             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
     for inc in cpp_extension.include_paths("cuda") + [sysconfig.get_paths()["include"]]:
-        cmd += ["-I", inc]
-    cmd += ["-x", "cu", *srcs, "-L", lib_dir, "-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda",
+        flags += ["-I", inc]
+    # one nvcc per source file, side by side (torch's headers make each of them minutes long), then one link
+    objs = [os.path.join(OUT_DIR, os.path.splitext(f)[0] + ".o") for f in SOURCES]
+    procs = [subprocess.Popen([nvcc, *flags, "-x", "cu", "-c", src, "-o", obj], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for src, obj in zip(srcs, objs)]
+    for proc, src in zip(procs, srcs):
+        out, _ = proc.communicate()
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n{out[-4000:]}")
+    link = [nvcc, "-shared", *objs, "-L", lib_dir, "-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda",
             "-ltorch_cuda", "-Xlinker", "-rpath", "-Xlinker", lib_dir, "-o", OUT]
-    res = subprocess.run(cmd, capture_output=True, text=True)
+    res = subprocess.run(link, capture_output=True, text=True)
+    for obj in objs:
+        if os.path.exists(obj):
+            os.remove(obj)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed on the reference extension:\n" + " ".join(cmd) + "\n" + res.stderr[-4000:])
+        raise RuntimeError("linking the reference extension failed:\n" + res.stderr[-4000:])
     return OUT
 
 
