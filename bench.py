@@ -482,9 +482,10 @@ class E2E:
     AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
     gradients -> loss-sized results back on the host."""
 
-    def __init__(self, cfg, job, device, chunks=1, levels=1, shard=None, row_group=None):
+    def __init__(self, cfg, job, device, chunks=1, levels=1, shard=None, row_group=None, prefetch=False):
         import separableflowthesis_b200 as sfb
         self.sfb, self.cfg, self.device = sfb, cfg, device
+        self.prefetch, self.prefetched = prefetch, None
         self.chunks = chunks if shard is None or shard.g_rows == 1 else 1
         self.levels = levels
         self.shard, self.row_group = shard, row_group
@@ -510,20 +511,30 @@ class E2E:
         """One step: this step's features host -> device, separation forward + backward, results -> host.  The batch
         is processed as `self.chunks` micro-batches through the same public call; the copy of micro-batch i+1 runs on
         a second stream while micro-batch i computes (gradients of the shared attention parameters accumulate
-        across micro-batches as autograd does for any repeated use)."""
+        across micro-batches as autograd does for any repeated use).  With `prefetch` the copy of the NEXT step's
+        first micro-batch is issued while this step's last one computes, as an input pipeline does; every step still
+        copies all of its inputs from pinned host memory inside the timed region (the step after the last timed one
+        gets its first micro-batch copied there too, unused)."""
         cfg, dev = self.cfg, self.device
         n = self.h1.shape[0]
         chunks = max(1, min(self.chunks, n))
         bounds = [(i * n // chunks, (i + 1) * n // chunks) for i in range(chunks)]
         main = torch.cuda.current_stream()
-        staged = []
-        with torch.cuda.stream(self.copy_stream):
-            for b0, b1 in bounds:
+        def stage(b0, b1):
+            with torch.cuda.stream(self.copy_stream):
                 f1 = self.h1[b0:b1].to(dev, non_blocking=True)
                 f2 = self.h2[b0:b1].to(dev, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self.copy_stream)
-                staged.append((f1, f2, ev))
+            return f1, f2, ev
+
+        staged = []
+        for i, (b0, b1) in enumerate(bounds):
+            if i == 0 and self.prefetched is not None:
+                staged.append(self.prefetched)
+                self.prefetched = None
+            else:
+                staged.append(stage(b0, b1))
         params = [p for c in (self.att or []) for p in c.parameters()]
         for p in params:
             p.grad = None
@@ -565,6 +576,8 @@ class E2E:
         res = torch.cat(pieces)
         self.host_out[:res.numel()].copy_(res, non_blocking=True)
         self.d2h = res.numel() * 4
+        if self.prefetch:
+            self.prefetched = stage(*bounds[0])
         main.synchronize()
         return float(self.host_out[0])
 
@@ -685,6 +698,8 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=2,
                     help="micro-batches per end-to-end step (the host->device copy of one overlaps the compute of the "
                          "previous one); 1 = copy everything, then compute")
+    ap.add_argument("--no-e2e-prefetch", action="store_true",
+                    help="end to end: do not copy the next step's first micro-batch while this step computes")
     ap.add_argument("--shard", default="batch", choices=["batch", "rows"],
                     help="batch: samples first, image-1 rows for what is left (no data-path exchange when the batch "
                          "is a multiple of the GPUs); rows: every rank gets all samples and a block of image-1 rows "
@@ -826,13 +841,16 @@ def main():
     # ---- end to end through the public API with host buffers ----
     e2e = None
     if not args.no_e2e:
-        runner = E2E(cfg, job, device, chunks=args.e2e_chunks, levels=args.levels, shard=shard, row_group=row_group)
+        runner = E2E(cfg, job, device, chunks=args.e2e_chunks, levels=args.levels, shard=shard, row_group=row_group,
+                     prefetch=not args.no_e2e_prefetch)   # warm-up runs the same pipeline (allocator steady state)
         for _ in range(min(args.warmup, 3)):
             runner.step()
         barrier()
+        runner.prefetched = None   # nothing copied before the timed region is used inside it
         e0.record()
         n_e2e = max(2, min(args.steps, 5))
-        for _ in range(n_e2e):
+        for i in range(n_e2e):
+            runner.prefetch = (not args.no_e2e_prefetch) and i < n_e2e - 1   # the last step has no successor
             runner.step()
         e1.record()
         barrier()
@@ -843,7 +861,10 @@ def main():
                "pyramid_levels": args.levels,
                "path": f"pinned host f1,f2 (B,C,H,W) -> AlternateCorrBlockSepflow(num_levels={args.levels}).separate with "
                        "Conv3d attention -> autograd backward -> all-reduce of attention-parameter grads -> host; "
-                       f"{runner.chunks} micro-batch(es) per step, copy of one overlapping compute of the previous"}
+                       f"{runner.chunks} micro-batch(es) per step, copy of one overlapping compute of the previous"
+                       + ("" if args.no_e2e_prefetch else
+                          "; the first micro-batch of the next timed step is copied while this step computes "
+                          "(all copies of the timed steps run inside the timed region)")}
         del runner
 
     cpu = None
