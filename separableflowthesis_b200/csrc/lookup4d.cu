@@ -35,6 +35,9 @@ constexpr int L4_RMAX = 4;
 constexpr int L4_WIN = 2 * L4_RMAX + 1;        // window side
 constexpr int L4_BW = 16, L4_BH = 12;          // largest bounding box a four-pixel pass accepts
 constexpr int L4_BMAX = L4_BW * L4_BH;
+#ifndef L4_BWD_STEP
+#define L4_BWD_STEP 2
+#endif
 static_assert(L4_TILE == 32, "the output staging assumes 32 pixels per CTA");
 static_assert((2 * L4_RMAX + 2) * (2 * L4_RMAX + 2) <= L4_BMAX, "one pixel's positions must fit the buffer");
 
@@ -239,37 +242,53 @@ __device__ __forceinline__ void l4_box_gradients(const float4 (&f1)[L4_PX][NCH],
                                                  const float* __restrict__ F2b, float* __restrict__ G2b, int H2, int W2,
                                                  int C, int ox, int oy, int bw, int bh, float (*gS)[L4_BMAX], int px0,
                                                  int lane) {
-  const int nq = bw * bh;
-  int row = 0, col = 0;
-  for (int q = 0; q < nq; ++q, ++col) {
-    if (col == bw) { col = 0; ++row; }
-    const int x = ox + col, y = oy + row;
-    if (x < 0 || x >= W2 || y < 0 || y >= H2) continue;
-    float g[NPX];
-    bool any = false;
+  // L4_BWD_STEP positions of a row per step: their image-2 rows are all requested before any is used
+  constexpr int J = L4_BWD_STEP;
+  for (int row = 0; row < bh; ++row) {
+    const int y = oy + row;
+    if (y < 0 || y >= H2) continue;
+    for (int col = 0; col < bw; col += J) {
+      bool in[J];
+      float4 f2[J][NCH];
+      float g[J][NPX];
+      size_t at[J];
 #pragma unroll
-    for (int px = 0; px < NPX; ++px) {
-      g[px] = gS[px0 + px][q];
-      any |= g[px] != 0.f;
-    }
-    if (!any) continue;
+      for (int j = 0; j < J; ++j) {
+        const int x = ox + col + j;
+        in[j] = col + j < bw && x >= 0 && x < W2;
+        at[j] = ((size_t)y * W2 + (in[j] ? x : 0)) * C;
 #pragma unroll
-    for (int ch = 0; ch < NCH; ++ch) {
-      const int c = ch * 128 + lane * 4;
-      if (c >= C) continue;
-      const size_t at = ((size_t)y * W2 + x) * C + c;
-      const float4 f2 = __ldg(reinterpret_cast<const float4*>(F2b + at));
-      float4 g2 = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int px = 0; px < NPX; ++px) {
-        float4& a = gf1[px0 + px][ch];   // px0 is 0 for the four-pixel pass; a compile-time index either way below
-        a.x = fmaf(g[px], f2.x, a.x); a.y = fmaf(g[px], f2.y, a.y);
-        a.z = fmaf(g[px], f2.z, a.z); a.w = fmaf(g[px], f2.w, a.w);
-        const float4& s = f1[px0 + px][ch];
-        g2.x = fmaf(g[px], s.x, g2.x); g2.y = fmaf(g[px], s.y, g2.y);
-        g2.z = fmaf(g[px], s.z, g2.z); g2.w = fmaf(g[px], s.w, g2.w);
+        for (int ch = 0; ch < NCH; ++ch) {
+          const int c = ch * 128 + lane * 4;
+          f2[j][ch] = (in[j] && c < C) ? __ldg(reinterpret_cast<const float4*>(F2b + at[j] + c))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
       }
-      red_add_v4(G2b + at, g2);
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        bool any = false;
+#pragma unroll
+        for (int px = 0; px < NPX; ++px) {
+          g[j][px] = in[j] ? gS[px0 + px][row * bw + col + j] : 0.f;
+          any |= g[j][px] != 0.f;
+        }
+        if (!any) continue;   // outside the image, or no pixel of the pass has this position in its window
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          const int c = ch * 128 + lane * 4;
+          float4 g2 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int px = 0; px < NPX; ++px) {
+            float4& a = gf1[px0 + px][ch];   // a compile-time index once the caller's loop is unrolled
+            a.x = fmaf(g[j][px], f2[j][ch].x, a.x); a.y = fmaf(g[j][px], f2[j][ch].y, a.y);
+            a.z = fmaf(g[j][px], f2[j][ch].z, a.z); a.w = fmaf(g[j][px], f2[j][ch].w, a.w);
+            const float4& s = f1[px0 + px][ch];
+            g2.x = fmaf(g[j][px], s.x, g2.x); g2.y = fmaf(g[j][px], s.y, g2.y);
+            g2.z = fmaf(g[j][px], s.z, g2.z); g2.w = fmaf(g[j][px], s.w, g2.w);
+          }
+          if (c < C) red_add_v4(G2b + at[j] + c, g2);
+        }
+      }
     }
   }
 }
