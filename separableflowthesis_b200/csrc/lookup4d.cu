@@ -66,8 +66,8 @@ struct L4Pixel {     // geometry of one pixel at one level
   int bx, by;        // integer position under the window centre
 };
 
-__device__ __forceinline__ float dot4(const float4& a, const float4& b) {
-  return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
+__device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
+  return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, fmaf(a.w, b.w, acc))));
 }
 
 // v[i] of all lanes summed; lane i keeps the total of v[i].  31 shuffles for 32 values.
@@ -129,7 +129,7 @@ __device__ __forceinline__ void l4_box_products(const float4 (&f1)[L4_PX][NCH], 
       for (int px = 0; px < NPX; ++px) {
         float acc = 0.f;
 #pragma unroll
-        for (int ch = 0; ch < NCH; ++ch) acc += dot4(f1[px][ch], f2[ch]);
+        for (int ch = 0; ch < NCH; ++ch) acc = dot4(f1[px][ch], f2[ch], acc);
         v[qi * NPX + px] = acc;
       }
     }
