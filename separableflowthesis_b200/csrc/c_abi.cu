@@ -2,6 +2,7 @@
 // map encoding and the launch sequence of each op.  No torch types, no allocation.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <mutex>
@@ -141,6 +142,16 @@ void drain_timing_locked() {
 // Operand type of the correlation sweeps of the level calls: 0 = TF32 (default), 1 = BF16.  Process-wide, because
 // a backward runs on an autograd worker thread, not on the thread that chose the precision.
 std::atomic<int> g_sweep_operands{0};
+
+// Where the image-1-major gradient GEMM keeps its generated A blocks: 1 = tensor memory, 0 = shared memory (default).
+// SFB_GRAD_A_TMEM=0/1 in the environment overrides the default (read once).
+int grad_a_in_tmem() {
+  static const int v = [] {
+    const char* e = getenv("SFB_GRAD_A_TMEM");
+    return e != nullptr ? (e[0] != '0' ? 1 : 0) : 0;
+  }();
+  return v;
+}
 
 struct Workspace {
   int* status;
@@ -401,6 +412,7 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   SFB_TRY(map_f2_tile(&tm_y, d, w.F2r, GG_UT, GG_VT, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
   SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, TILE_M / 2, GG_UT));  // two 64-pixel boxes per block
   a.out_cf = out_cf;
+  a.a_in_tmem = grad_a_in_tmem();
   a.image2_major = 0;
   a.out = gF1;
   a.out_scale = scale1;
@@ -416,17 +428,20 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   return SFB_OK;
 }
 
-// Interleaved slots of the max/avg backward: 0 = mean-gradient / row length, 1 = max-gradient, 2 = argmax bits.
+// Interleaved slots of the max/avg backward (kernels.h): XU = (mean-gradient / W2, 1, max-gradient, argmax bits),
+// XV = (1, mean-gradient / H2, max-gradient, argmax bits); slots 0 and 1 of the two sides multiply to the mean terms.
 void maxavg_slot_sources(const Dims& d, const int32_t* AM_u, const int32_t* AM_v, const float* gMA_u,
                          const float* gMA_v, SlotSources* su, SlotSources* sv) {
   memset(su, 0, sizeof(*su));
   memset(sv, 0, sizeof(*sv));
   su->s[0] = {gMA_u, 2, 1, 1.f / (float)d.W2};
-  su->s[1] = {gMA_u, 2, 0, 0.f};
-  su->s[2] = {AM_u, 1, 0, 0.f};
-  sv->s[0] = {gMA_v, 2, 1, 1.f / (float)d.H2};
-  sv->s[1] = {gMA_v, 2, 0, 0.f};
-  sv->s[2] = {AM_v, 1, 0, 0.f};
+  su->s[1] = {nullptr, 0, 0, 1.f};
+  su->s[2] = {gMA_u, 2, 0, 0.f};
+  su->s[3] = {AM_u, 1, 0, 0.f};
+  sv->s[0] = {nullptr, 0, 0, 1.f};
+  sv->s[1] = {gMA_v, 2, 1, 1.f / (float)d.H2};
+  sv->s[2] = {gMA_v, 2, 0, 0.f};
+  sv->s[3] = {AM_v, 1, 0, 0.f};
 }
 // Interleaved slots of the compression backward for channels k0 .. k0+kc-1, local channel j:
 // XU 2j = gC_u, 2j+1 = A_v;  XV 2j = A_u, 2j+1 = gC_v, so that G[p,u,v] = sum_slots XU[u,p,slot] * XV[v,p,slot].

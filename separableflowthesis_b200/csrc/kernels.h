@@ -4,7 +4,27 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace sfb {
+
+// Host side.  Runs a per-device set-up step (cudaFuncSetAttribute and the like) once per device instead of before every launch.
+// Racing first calls may both run it, which is harmless for idempotent settings.
+struct DeviceOnce {
+  std::atomic<bool> done[64];
+  DeviceOnce() { for (auto& d : done) d.store(false); }
+  template <class F>
+  cudaError_t run(F&& f) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= 64) return f();
+    if (done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+    err = f();
+    if (err == cudaSuccess) done[dev].store(true, std::memory_order_release);
+    return err;
+  }
+};
 
 // Problem size of one op call (one pyramid level).  N1 = H1*W1 image-1 pixels, N2 = H2*W2.
 struct Dims {
@@ -72,8 +92,10 @@ struct SweepArgs {
 // One group of four slots of 32 consecutive pixels is 512 contiguous bytes: a 16-byte load per lane, or one
 // TMA box row, and conflict-free 16-byte shared-memory reads after a TMA copy.
 //   GRAD_COMPRESS: G[p,u,v] = sum_r XU[u,p,r] * XV[v,p,r]            (2 slots per channel, zero padded)
-//   GRAD_MAXAVG  : slots (mean-gradient already divided by the row length, max-gradient, argmax bits, 0):
-//                  G[p,u,v] = XU[u,p,0] + XV[v,p,0] + (XU[u,p,2]==v ? XU[u,p,1] : 0) + (XV[v,p,2]==u ? XV[v,p,1] : 0)
+//   GRAD_MAXAVG  : XU slots (mean-gradient / W2, 1, max-gradient, argmax bits), XV slots (1, mean-gradient / H2,
+//                  max-gradient, argmax bits), so that slots 0 and 1 multiply to the two mean terms:
+//                  G[p,u,v] = XU[u,p,0]*XV[v,p,0] + XU[u,p,1]*XV[v,p,1]
+//                             + (XU[u,p,3]==v ? XU[u,p,2] : 0) + (XV[v,p,3]==u ? XV[v,p,2] : 0)
 //   GRAD_FUSED   : group 0 as GRAD_MAXAVG, groups 1.. as GRAD_COMPRESS; G is the sum of both
 struct GradArgs {
   Dims d;
@@ -82,6 +104,7 @@ struct GradArgs {
   int R4;                // slots per pixel in the interleaved operands: 4 or 8
   int n1p;               // padded pixel count of the interleaved operands
   int accumulate;        // 0: out = result, 1: out += result (later channel chunks of the compression op)
+  int a_in_tmem;         // image-1-major form: generated A blocks go to tensor memory instead of shared memory
   int out_cf;            // 0: out is (B, pixels, C); 1: out is (B, C, pixels), the layout of the model's feature maps
   float out_scale;       // the result is multiplied by this before it is stored / added (out_cf only)
   const float* xu;
@@ -91,7 +114,7 @@ struct GradArgs {
 };
 
 // One source of an interleaved slot: dst[b][d][slot/4][p][slot%4] = scale * src[b][p][k][d] (raw copy when scale == 0);
-// src is (B, N1, Ksrc, D).  A null src leaves the slot zero.
+// src is (B, N1, Ksrc, D).  A null src makes the slot the constant `scale` (zero by default) for every valid pixel.
 struct SlotSource {
   const void* src;
   int Ksrc, k;

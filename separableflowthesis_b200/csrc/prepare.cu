@@ -117,9 +117,13 @@ __global__ void pack_interleaved_kernel(const SlotSources src, uint32_t* __restr
     for (int j = ty; j < 32; j += 8) {
       const int p = p0 + j, d = d0 + tx;
       uint32_t v = 0;
-      if (s != nullptr && p < N1 && d < D) {
-        v = __ldg(s + (((size_t)b * N1 + p) * src.s[r].Ksrc + src.s[r].k) * D + d);
-        if (src.s[r].scale != 0.f) v = __float_as_uint(__uint_as_float(v) * src.s[r].scale);
+      if (p < N1 && d < D) {
+        if (s == nullptr) {
+          v = __float_as_uint(src.s[r].scale);  // constant slot
+        } else {
+          v = __ldg(s + (((size_t)b * N1 + p) * src.s[r].Ksrc + src.s[r].k) * D + d);
+          if (src.s[r].scale != 0.f) v = __float_as_uint(__uint_as_float(v) * src.s[r].scale);
+        }
       }
       tile[r * RS + j * 33 + tx] = v;
     }
@@ -168,6 +172,8 @@ __global__ void pack_interleaved_cf_kernel(const SlotSources src, float4* __rest
         w[i][q][j] = 0;
         if (ss.src != nullptr && p < N1 && d0 + i < D)
           w[i][q][j] = __ldg(static_cast<const uint32_t*>(ss.src) + (((size_t)b * ss.Ksrc + ss.k) * D + d0 + i) * N1 + p);
+        else if (ss.src == nullptr && p < N1)
+          w[i][q][j] = __float_as_uint(ss.scale);  // constant slot
       }
 #pragma unroll
   for (int i = 0; i < PI_DB; ++i) {
@@ -177,8 +183,8 @@ __global__ void pack_interleaved_cf_kernel(const SlotSources src, float4* __rest
       float v[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float scale = src.s[4 * q + j].scale;
-        v[j] = scale != 0.f ? __uint_as_float(w[i][q][j]) * scale : __uint_as_float(w[i][q][j]);
+        const SlotSource& ss = src.s[4 * q + j];
+        v[j] = (ss.scale != 0.f && ss.src != nullptr) ? __uint_as_float(w[i][q][j]) * ss.scale : __uint_as_float(w[i][q][j]);
       }
       dst[(((size_t)b * D + d0 + i) * Qtot + q0 + q) * n1p + p] = make_float4(v[0], v[1], v[2], v[3]);
     }

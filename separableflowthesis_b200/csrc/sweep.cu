@@ -303,47 +303,61 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
   float* ou = a.ou.base + sc.b * a.ou.sb + e.p + k * a.ou.ss;
   float* ov = a.ov.base + sc.b * a.ov.sb + e.p + k * a.ov.ss;
 
-  float au[SWEEP_VT], cv[SWEEP_VT];
+  // Both sums run on packed FP32 pairs (two neighbouring columns per fma.rn.f32x2), which halves the
+  // instructions per cell: the epilogue warps share their schedulers' issue slots, and with scalar FMAs
+  // those slots, not the tensor pipe, set the pace of this sweep.
+  //   au2[j] = (w_u[v0+2j], w_u[v0+2j+1])         weights of this column block, per column pair
+  //   cv2[j] = running (OV[v0+2j], OV[v0+2j+1])   over the rows of the column block
+  // Cells outside the image hold S = 0 (TMA zero-fills the missing F2 rows) and get weight 0, so every
+  // tile is processed whole and only the loads and stores at the edges are predicated.
+  uint64_t au2[SWEEP_VT / 2], cv2[SWEEP_VT / 2];
   int vb = 0, ub = 0;
   for (int t = 0; t < sc.t_main; ++t) {
     const int v0 = vb * SWEEP_VT, u0 = ub * SWEEP_UT;
     const int nu = min(SWEEP_UT, H2 - u0), nv = min(SWEEP_VT, W2 - v0);
     if (ub == 0) {
+      const float* wu_t = wu + v0 * xvsd;
 #pragma unroll
-      for (int i = 0; i < SWEEP_VT; ++i) {
-        au[i] = (valid && i < nv) ? __ldg(wu + (v0 + i) * xvsd) : 0.f;
-        cv[i] = 0.f;
+      for (int j = 0; j < SWEEP_VT / 2; ++j) {
+        const float lo = (valid && 2 * j < nv) ? __ldg(wu_t + (2 * j) * xvsd) : 0.f;
+        const float hi = (valid && 2 * j + 1 < nv) ? __ldg(wu_t + (2 * j + 1) * xvsd) : 0.f;
+        au2[j] = pack2(lo, hi);
+        cv2[j] = 0ull;
       }
     }
     float av[SWEEP_UT];
+    {
+      const float* wv_t = wv + u0 * xusd;
 #pragma unroll
-    for (int ul = 0; ul < SWEEP_UT; ++ul) av[ul] = (valid && ul < nu) ? __ldg(wv + (u0 + ul) * xusd) : 0.f;
+      for (int ul = 0; ul < SWEEP_UT; ++ul) av[ul] = (valid && ul < nu) ? __ldg(wv_t + ul * xusd) : 0.f;
+    }
 
     if (!epi_wait(sm, a, t)) return;
     const uint32_t tacc = e.tbase + (t % SW_NACC) * SW_TILE_N;
     if (active) {
+      float* ou_t = ou + u0 * ousd;
+      const bool first = vb == 0;  // the first column block initialises the output, later ones accumulate
 #pragma unroll
       for (int pr = 0; pr < SWEEP_UT / 2; ++pr) {
-        if (2 * pr < nu) {  // warp-uniform; padded cells hold S = 0 (zero-filled F2 rows) and weight 0
-          float s[2 * SWEEP_VT];
-          tmem_ld32(tacc + pr * 2 * SWEEP_VT, s);
-          if (pr == SWEEP_UT / 2 - 1 || 2 * pr + 2 >= nu) epi_release(sm, t, e.lane);  // last read of this tile
+        float s[2 * SWEEP_VT];
+        tmem_ld32(tacc + pr * 2 * SWEEP_VT, s);
+        if (pr == SWEEP_UT / 2 - 1) epi_release(sm, t, e.lane);  // last read of this tile
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int ul = 2 * pr + h;
-            if (ul < nu) {
-              float r = 0.f;
+        for (int h = 0; h < 2; ++h) {
+          const int ul = 2 * pr + h;
+          const uint64_t av2 = pack2(av[ul], av[ul]);
+          uint64_t r2 = 0ull;
 #pragma unroll
-              for (int i = 0; i < SWEEP_VT; ++i) {
-                r = fmaf(s[h * SWEEP_VT + i], au[i], r);
-                cv[i] = fmaf(s[h * SWEEP_VT + i], av[ul], cv[i]);
-              }
-              if (valid) {
-                float* dst = ou + (u0 + ul) * ousd;
-                if (vb == 0) *dst = r;     // first column block initialises the output
-                else atomicAdd(dst, r);    // later blocks accumulate (same thread, same address: ordered)
-              }
-            }
+          for (int j = 0; j < SWEEP_VT / 2; ++j) {
+            const uint64_t s2 = pack2(s[h * SWEEP_VT + 2 * j], s[h * SWEEP_VT + 2 * j + 1]);
+            r2 = j == 0 ? mul2(s2, au2[0]) : fma2(s2, au2[j], r2);
+            cv2[j] = fma2(s2, av2, cv2[j]);
+          }
+          if (valid && ul < nu) {
+            float* dst = ou_t + ul * ousd;
+            const float r = sum2(r2);
+            if (first) *dst = r;
+            else atomicAdd(dst, r);  // same thread, same address in every column block: ordered
           }
         }
       }
@@ -351,9 +365,14 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
       epi_release(sm, t, e.lane);
     }
     if (ub == sc.n_ub - 1) {
+      float* ov_t = ov + v0 * ovsd;
 #pragma unroll
-      for (int i = 0; i < SWEEP_VT; ++i)
-        if (valid && i < nv) ov[(v0 + i) * ovsd] = cv[i];
+      for (int j = 0; j < SWEEP_VT / 2; ++j) {
+        float lo, hi;
+        unpack2(cv2[j], lo, hi);
+        if (valid && 2 * j < nv) ov_t[(2 * j) * ovsd] = lo;
+        if (valid && 2 * j + 1 < nv) ov_t[(2 * j + 1) * ovsd] = hi;
+      }
     }
     if (++ub == sc.n_ub) { ub = 0; ++vb; }
   }
@@ -470,7 +489,10 @@ template <int MODE>
 static cudaError_t launch_one(const SweepArgs& a, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
                               const CUtensorMap& tm_aux, cudaStream_t stream) {
   auto kern = sweep_kernel<MODE>;
-  cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SW_SMEM_BYTES);
+  static DeviceOnce configured;  // the attribute is per device and stays set
+  cudaError_t err = configured.run([&] {
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SW_SMEM_BYTES);
+  });
   if (err != cudaSuccess) return err;
   const int tiles_per_sample = (a.d.N1() + TILE_M - 1) / TILE_M;
   const dim3 grid(a.d.B * tiles_per_sample);
