@@ -2,7 +2,6 @@
 // map encoding and the launch sequence of each op.  No torch types, no allocation.
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <mutex>
@@ -46,8 +45,9 @@ EncodeTiledFn encode_fn() {
 
 // Tiled fp32 tensor map, 128-byte swizzle, innermost box = 32 channels (128 bytes), zero fill out of bounds.
 // dims/box are innermost-first; strides are implied by a contiguous tensor.
+// `pitch0` (elements, optional): distance between consecutive indices of dimension 1 when the rows are padded.
 int make_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, const uint32_t* box,
-             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, bool bf16 = false) {
+             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, bool bf16 = false, uint64_t pitch0 = 0) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
   // The driver call needs a context that is current to this thread.  A thread that has made no runtime call yet
@@ -65,7 +65,7 @@ int make_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, 
     gdim[i] = dims[i];
     bdim[i] = box[i];
     estride[i] = 1;
-    stride *= dims[i];
+    stride *= (i == 0 && pitch0 != 0) ? pitch0 : dims[i];
     if (i < rank - 1) gstride[i] = stride;  // byte stride of dimension i+1
   }
   CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank,
@@ -143,16 +143,6 @@ void drain_timing_locked() {
 // a backward runs on an autograd worker thread, not on the thread that chose the precision.
 std::atomic<int> g_sweep_operands{0};
 
-// Where the image-1-major gradient GEMM keeps its generated A blocks: 1 = tensor memory, 0 = shared memory (default).
-// SFB_GRAD_A_TMEM=0/1 in the environment overrides the default (read once).
-int grad_a_in_tmem() {
-  static const int v = [] {
-    const char* e = getenv("SFB_GRAD_A_TMEM");
-    return e != nullptr ? (e[0] != '0' ? 1 : 0) : 0;
-  }();
-  return v;
-}
-
 struct Workspace {
   int* status;
   float* F1r;
@@ -167,6 +157,9 @@ struct Workspace {
   float* ov;   // packed outputs, (B, W2, Ro, n1p)
   float* gxu;  // interleaved gradient-GEMM operands, (B, H2, n1p, Rg)
   float* gxv;  // interleaved gradient-GEMM operands, (B, W2, n1p, Rg)
+  float* F1t;  // channel-major copies of F1r / F2r for K-major B operands: (B, C, n1p) and, in column blocks of 16
+  float* F2t;  // with an even number of rows, (B, C, ceil(W2/16), h2p, 16)
+  int h2p;     // H2 rounded up to a multiple of GG_UT
   float* ga_u;  // level backward: attention gradients (B, Kc, W2, N1) / (B, Kc, H2, N1) ...
   float* ga_v;
   float* gm_u;  // ... total gradients of the max/avg channels (B, 2, W2, N1) / (B, 2, H2, N1) ...
@@ -236,6 +229,12 @@ Workspace carve(const Dims& d, void* base, const WsPlan& plan) {
   w.ov = plan.Ro ? take((size_t)d.B * d.W2 * plan.Ro * w.n1p) : nullptr;
   w.gxu = plan.Rg ? take((size_t)d.B * d.H2 * plan.Rg * w.n1p) : nullptr;
   w.gxv = plan.Rg ? take((size_t)d.B * d.W2 * plan.Rg * w.n1p) : nullptr;
+  w.h2p = (d.H2 + GG_UT - 1) / GG_UT * GG_UT;
+  w.F1t = w.F2t = nullptr;
+  if (plan.Rg) {
+    w.F1t = take((size_t)d.B * d.C * w.n1p);
+    w.F2t = take((size_t)d.B * d.C * ((d.W2 + GG_VT - 1) / GG_VT) * w.h2p * GG_VT);
+  }
   w.ga_u = w.ga_v = w.gm_u = w.gm_v = w.at_partial = nullptr;
   if (plan.level_bwd) {
     const size_t n1 = (size_t)d.N1();
@@ -408,17 +407,36 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   a.status = w.status;
   const int Q = R4 / 4;
   const int kid = mode == GRAD_MAXAVG ? KID_GRAD_MAXAVG_IMG1 : (mode == GRAD_COMPRESS ? KID_GRAD_COMPRESS_IMG1 : KID_GRAD_FUSED_IMG1);
+  // K-major B operands: channel-major copies of the rounded features (image 2 in column blocks of 16 with an even
+  // number of rows, so that a 2 x 16 block of the image is 32 consecutive values).  Rows and columns of padding must
+  // read as zero: they meet the G values of cells outside the image.
+  const uint32_t crows = (uint32_t)((d.C + KBLK - 1) / KBLK * KBLK);  // channel rows of one feature block
+  const size_t f2t_per_sample = (size_t)d.C * ((d.W2 + GG_VT - 1) / GG_VT) * w.h2p * GG_VT;
+  if (!accumulate) {  // later passes over further channel chunks reuse the copies of the first
+    SFB_CUDA(timed(KID_PREPARE, 2, st, [&] {
+      cudaMemsetAsync(w.F2t, 0, (size_t)d.B * f2t_per_sample * sizeof(float), st);
+      launch_channel_major(w.F1r, w.F1t, d.B, 1, d.N1(), w.n1p, d.C, 0, st);
+      return launch_channel_major(w.F2r, w.F2t, d.B, d.H2, d.W2, w.h2p, d.C, 1, st);
+    }));
+  }
   // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2 and 2-row blocks of XU.
-  SFB_TRY(map_f2_tile(&tm_y, d, w.F2r, GG_UT, GG_VT, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  {  // (blocked pixels, C, B); box = 32 consecutive values (2 rows x 16 columns) x all channels
+    const uint64_t dims[3] = {(uint64_t)(f2t_per_sample / d.C), (uint64_t)d.C, (uint64_t)d.B};
+    const uint32_t box[3] = {GG_KJ, crows, 1};
+    SFB_TRY(make_map(&tm_y, w.F2t, 3, dims, box));
+  }
   SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, TILE_M / 2, GG_UT));  // two 64-pixel boxes per block
   a.out_cf = out_cf;
-  a.a_in_tmem = grad_a_in_tmem();
   a.image2_major = 0;
   a.out = gF1;
   a.out_scale = scale1;
   SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(a, tm_y, tm_xu, tm_xu /* unused */, st); }));
   // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1, XU and XV.
-  SFB_TRY(map_f1_rows(&tm_y, d, w.F1r, GG_KJ, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  {  // (N1, C, B) with rows padded to n1p; box = 32 pixels x all channels
+    const uint64_t dims[3] = {(uint64_t)d.N1(), (uint64_t)d.C, (uint64_t)d.B};
+    const uint32_t box[3] = {GG_KJ, crows, 1};
+    SFB_TRY(make_map(&tm_y, w.F1t, 3, dims, box, CU_TENSOR_MAP_SWIZZLE_128B, false, (uint64_t)w.n1p));
+  }
   SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, GG_KJ, GG_ROW_UT));
   SFB_TRY(map_operands(&tm_xv, w.gxv, d.B, d.W2, Q, w.n1p, GG_KJ, GG_ROW_VT));
   a.image2_major = 1;

@@ -104,7 +104,6 @@ struct GradArgs {
   int R4;                // slots per pixel in the interleaved operands: 4 or 8
   int n1p;               // padded pixel count of the interleaved operands
   int accumulate;        // 0: out = result, 1: out += result (later channel chunks of the compression op)
-  int a_in_tmem;         // image-1-major form: generated A blocks go to tensor memory instead of shared memory
   int out_cf;            // 0: out is (B, pixels, C); 1: out is (B, C, pixels), the layout of the model's feature maps
   float out_scale;       // the result is multiplied by this before it is stored / added (out_cf only)
   const float* xu;
@@ -145,6 +144,11 @@ cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, floa
 cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
                               float* F2r, float* aux, int* status, cudaStream_t stream, uint16_t* F1h = nullptr,
                               uint16_t* F2h = nullptr, uint16_t* auxh = nullptr);
+// Channel-major copy of a (rounded) pixel-major feature array (B, rows*width, C); padding is not written.
+//   blocked = 0: dst (B, C, pitch) with pixel index row*width + x (rows = 1)
+//   blocked = 1: dst (B, C, ceil(width/16), pitch, 16), element (row, x) at ((x/16)*pitch + row)*16 + x%16
+cudaError_t launch_channel_major(const float* src, float* dst, int B, int rows, int width, int pitch, int C,
+                                 int blocked, cudaStream_t stream);
 // Pack: dst[b][d][r0 + k*rstride][p] = scale * src[b][p][ksrc0 + k][d] for k < K (raw 32-bit copy when
 // scale == 0), zero for N1 <= p < n1p.  src is (B, N1, Ksrc, D), dst is (B, D, R, n1p).
 cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,
@@ -154,7 +158,7 @@ cudaError_t launch_unpack(const float* src, void* dst, int B, int N1, int n1p, i
                           int rstride, int Kdst, int kdst0, cudaStream_t stream);
 cudaError_t launch_sweep(const SweepArgs& a, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2,
                          const CUtensorMap& tm_aux, cudaStream_t stream);
-// tm_y: features of the other image (B operand); tm_xu / tm_xv: interleaved operands (tm_xv is only read by the
+// tm_y: channel-major features of the other image (K-major B operand); tm_xu / tm_xv: interleaved operands (tm_xv is only read by the
 // image-2-major form; the image-1-major form keeps its (pixel, v) slots in registers).
 cudaError_t launch_grad_gemm(const GradArgs& a, const CUtensorMap& tm_y, const CUtensorMap& tm_xu,
                              const CUtensorMap& tm_xv, cudaStream_t stream);

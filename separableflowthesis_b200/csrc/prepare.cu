@@ -241,6 +241,42 @@ __global__ void transpose_round_kernel(const float* __restrict__ in, float* __re
   }
 }
 
+// Channel-major copies of a pixel-major feature array (B, rows*width, C), the K-major B operands of the gradient GEMMs.
+//   blocked = 0: dst (B, C, pitch), pixel index = row*width + x (image 1: rows = 1, width = N1, pitch = n1p)
+//   blocked = 1: dst (B, C, ceil(width/16), pitch, 16): columns in blocks of 16, so that the 2 rows x 16 columns of one
+//                K block of the image-1-major GEMM are 32 consecutive values (image 2: pitch = H2 rounded up to even)
+// Padding is not written (the caller clears the array).  32 x 32 tiles through shared memory; grid (ceil(width/32),
+// ceil(C/32), B*rows), block (32, 8).
+__global__ void channel_major_kernel(const float* __restrict__ in, float* __restrict__ out, int rows, int width,
+                                     int pitch, int C, int blocked) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z / rows, row = blockIdx.z - b * rows, x0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const float* src = in + ((size_t)b * rows + row) * width * C;
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int x = x0 + j, c = c0 + tx;
+    tile[j][tx] = (x < width && c < C) ? __ldg(src + (size_t)x * C + c) : 0.f;
+  }
+  __syncthreads();
+  const size_t per_channel = blocked ? (size_t)((width + 15) / 16) * pitch * 16 : (size_t)pitch;
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int c = c0 + j, x = x0 + tx;
+    if (c < C && x < width) {
+      const size_t off = blocked ? ((size_t)(x >> 4) * pitch + row) * 16 + (x & 15) : (size_t)x;
+      out[((size_t)b * C + c) * per_channel + off] = tile[tx][j];
+    }
+  }
+}
+
+cudaError_t launch_channel_major(const float* src, float* dst, int B, int rows, int width, int pitch, int C,
+                                 int blocked, cudaStream_t stream) {
+  const dim3 grid((width + 31) / 32, (C + 31) / 32, B * rows), block(32, 8);
+  channel_major_kernel<<<grid, block, 0, stream>>>(src, dst, rows, width, pitch, C, blocked);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
                               float* F2r, float* aux, int* status, cudaStream_t stream, uint16_t* F1h, uint16_t* F2h,
                               uint16_t* auxh) {

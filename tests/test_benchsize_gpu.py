@@ -1,0 +1,132 @@
+"""GPU: the entry points the benchmark times, checked against the oracle at the sizes it times them.
+
+``bench.py`` measures ``sfb_separation_level_forward`` / ``_backward`` (one pyramid level of the call site,
+core/corr.py:416-457, in one library call each way) on BASELINE config 5 (135x240, C=256, Kc=4) and, for the BF16
+configuration, config 4 (B=8, 47x156, Kc=2).  The CPU oracle cannot finish those sizes in seconds, so the same
+oracle code (oracle/separation_oracle.py: dense matmul -> max/mean -> Conv3d/softmax -> einsum, image-1 row
+chunks) runs on the GPU in FP32 with TF32 switched off everywhere; its own error (~1e-6) is far inside the
+tolerances below.  The comparison is the one the reference's tests make (scripts/test_compression_autograd.py:442-484,
+scripts/test_model.py:251-256): max |x - ref| over max(|x|max, |ref|max).
+
+Tolerances: 1e-3 for gradients and attention gradients (TF32 operands, FP32 accumulation), 2e-3 for whole-level
+outputs (their attention weights are a softmax of TF32-grade max/avg values); for BF16 sweep operands 2e-5 on
+the max channel against the oracle on BF16-rounded features (products of BF16 values are exact in FP32), 4e-3 on the
+other forward outputs and 1e-2 on the backward against the unrounded oracle.
+"""
+import pytest
+import torch
+
+from separableflowthesis_b200 import ops
+from oracle import separation_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def relerr(x, ref):
+    den = max(x.abs().max().item(), ref.abs().max().item(), 1e-30)
+    return (x.double() - ref.double()).abs().max().item() / den
+
+
+def no_tf32():
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+
+
+def level_inputs(B, H, W, C, Kc, dev, seed):
+    """Seeded N(0,1) features (image 1 pre-scaled by 1/sqrt(C), core/corr.py:419), N(0, 0.02)-grade attention
+    parameters as BASELINE config 2 states them, N(0,1) upstream gradients."""
+    g = torch.Generator().manual_seed(seed)
+    F1 = (torch.randn(B, H, W, C, generator=g) / C ** 0.5).to(dev)
+    F2 = torch.randn(B, H, W, C, generator=g).to(dev)
+    params = [(torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.02).to(dev), (torch.randn(Kc, generator=g) * 0.02).to(dev),
+              (torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.02).to(dev), (torch.randn(Kc, generator=g) * 0.02).to(dev)]
+    gd = torch.Generator(device=dev).manual_seed(seed + 1)
+    g_sep_u = torch.randn(B, 2 + Kc, W, H, W, generator=gd, device=dev)
+    g_sep_v = torch.randn(B, 2 + Kc, H, H, W, generator=gd, device=dev)
+    return F1, F2, params, g_sep_u, g_sep_v
+
+
+def check_level(F1, F2, params, g_sep_u, g_sep_v, fmaps):
+    """Forward and backward of one level through the library, every output against the oracle run on the same
+    device in FP32; the backward is evaluated with the device forward's own argmax / attention weights, as autograd
+    does.  gF2 is compared whole: the oracle accumulates it over all image-1 row chunks."""
+    wu, bu, wv, bv = params
+    C = F1.shape[-1]
+    scale = 1.0
+    a1, a2 = F1, F2
+    if fmaps:   # the model's (B, C, H, W) maps, unscaled; the library scales image 1 on the way in
+        scale = 1.0 / C ** 0.5
+        a1 = (F1 * C ** 0.5).permute(0, 3, 1, 2).contiguous()
+        a2 = F2.permute(0, 3, 1, 2).contiguous()
+    fw = ops.separation_level_forward(a1, a2, wu, bu, wv, bv, fmaps=fmaps, scale1=scale)
+    ref = orc.separation_level_forward(a1, a2, wu, bu, wv, bv, fmaps=fmaps, scale1=scale)
+    for name, i in (("sep_u", 0), ("sep_v", 1), ("a_u", 4), ("a_v", 5)):
+        assert fw[i].shape == ref[i].shape
+        assert relerr(fw[i], ref[i]) < 2 * TOL, (name, relerr(fw[i], ref[i]))
+    agree = (fw[2] == ref[2]).float().mean().item()
+    assert agree > 0.995, agree   # the rest are near-ties flipped by TF32 rounding
+    del ref
+    bw = ops.separation_level_backward(a1, a2, wu, wv, *fw, g_sep_u, g_sep_v, fmaps=fmaps, scale1=scale)
+    rb = orc.separation_level_backward(a1, a2, wu, wv, *fw, g_sep_u, g_sep_v, fmaps=fmaps, scale1=scale)
+    for name, i in (("gF1", 0), ("gF2", 1), ("gweight_u", 2), ("gweight_v", 4)):
+        assert bw[i].shape == rb[i].shape
+        assert relerr(bw[i], rb[i]) < TOL, (name, relerr(bw[i], rb[i]))
+    for name, i in (("gbias_u", 3), ("gbias_v", 5)):   # measured against the scale of the weight gradients
+        den = max(rb[i - 1].abs().max().item(), 1.0)
+        assert (bw[i].double() - rb[i].double()).abs().max().item() < TOL * den, name
+
+
+@pytest.mark.parametrize("fmaps", [False, True])
+def test_level_at_config5_size_one_sample(fmaps, cuda_device):
+    """One sample of BASELINE config 5 (135x240, C=256, Kc=4): the per-sample work of the benchmarked step."""
+    no_tf32()
+    F1, F2, params, gu, gv = level_inputs(1, 135, 240, 256, 4, cuda_device, seed=501)
+    check_level(F1, F2, params, gu, gv, fmaps)
+
+
+def test_level_at_benchmarked_batch(cuda_device):
+    """B=8, the benchmarked batch (sample strides of every view), at BASELINE config 4's size (47x156, Kc=2)."""
+    no_tf32()
+    F1, F2, params, gu, gv = level_inputs(8, 47, 156, 256, 2, cuda_device, seed=502)
+    check_level(F1, F2, params, gu, gv, fmaps=True)
+
+
+def test_level_bf16_operands_at_config4_size(cuda_device):
+    """BASELINE config 4's operand type at its image size (two samples): BF16 operands in the sweeps."""
+    no_tf32()
+    F1, F2, params, gu, gv = level_inputs(2, 47, 156, 256, 2, cuda_device, seed=503)
+    wu, bu, wv, bv = params
+    with ops.sweep_operands("bf16"):
+        fw = ops.separation_level_forward(F1, F2, wu, bu, wv, bv)
+        bw = ops.separation_level_backward(F1, F2, wu, wv, *fw, gu, gv)
+    F1b, F2b = F1.bfloat16().float(), F2.bfloat16().float()
+    ref = orc.separation_level_forward(F1b, F2b, wu, bu, wv, bv)
+    # channel 0 = max: exact products, only the accumulation order differs
+    assert relerr(fw[0][:, 0], ref[0][:, 0]) < 2e-5 and relerr(fw[1][:, 0], ref[1][:, 0]) < 2e-5
+    assert relerr(fw[0], ref[0]) < 4e-3 and relerr(fw[1], ref[1]) < 4e-3
+    ref32 = orc.separation_level_forward(F1, F2, wu, bu, wv, bv)
+    assert relerr(fw[0], ref32[0]) < 1e-2 and relerr(fw[1], ref32[1]) < 1e-2
+    rb = orc.separation_level_backward(F1, F2, wu, wv, *fw, gu, gv)
+    for i in (0, 1, 2, 4):
+        assert relerr(bw[i], rb[i]) < 1e-2, i
+
+
+def test_lookup_radius_beyond_register_window(cuda_device):
+    """CorrBlock1D lookup (core/corr.py:576-624) with radius 6: more taps than the kernel's in-register window
+    holds, which takes its general path."""
+    B, dim, D, H1, W1, levels, radius = 2, 1, 48, 9, 14, 3, 6
+    g = torch.Generator().manual_seed(77)
+    corr = torch.randn(B, dim, D, H1, W1, generator=g)
+    coord = torch.rand(B, H1, W1, generator=g) * (D + 6) - 3      # some positions outside the volume
+    gout = torch.randn(B, levels * dim * (2 * radius + 1), H1, W1, generator=g)
+    dev = cuda_device
+    for clamp in (False, True):
+        c = coord / D if clamp else coord
+        pyr = ops.lookup_build_pyramid(corr.to(dev), levels)
+        out = ops.lookup_forward(corr.to(dev), pyr, c.to(dev), levels, radius, clamp)
+        ref = orc.lookup_forward(corr.double(), c.double(), levels, radius, clamp)
+        assert relerr(out.cpu(), ref) < 5e-5
+        gc = ops.lookup_backward(tuple(corr.shape), c.to(dev), gout.to(dev), levels, radius, clamp)
+        rg = orc.lookup_backward(tuple(corr.shape), c.double(), gout.double(), levels, radius, clamp)
+        assert relerr(gc.cpu(), rg) < 5e-5
