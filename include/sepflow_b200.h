@@ -73,20 +73,26 @@ int sfb_max_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA
                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* No counterpart in the reference.  The same computation as sfb_max_avg_forward for callers that cannot
- * allocate device memory at all -- code running inside a stream capture, under a memory pool that another
- * component owns, in a real-time loop that must not enter the allocator, or in a host that only hands out
- * input and output buffers.  Its scratch is a fixed array of sfb_static_scratch_bytes() bytes (32 MiB)
- * that is part of the library image: every GPU that loads the library holds it until the process exits.
+ * allocate device memory at all: a component that runs under a memory pool some other part of the program owns, a
+ * real-time or serving loop that must never enter the allocator, a host application that hands this library nothing
+ * but input and output buffers.  Its scratch is a fixed array of sfb_static_scratch_bytes() bytes (32 MiB) that is
+ * part of the library image: every GPU that loads the library holds it until the process exits.
  *   - Shapes whose scratch need (sfb_workspace_bytes(SFB_OP_MAX_AVG_FORWARD, shape)) exceeds that size are
  *     rejected with SFB_ERR_UNSUPPORTED_SHAPE; BASELINE-style 48x64 feature maps with C=256 fit.
- *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
- *     first call outside any stream capture.  No call allocates or frees memory.
+ *   - Set-up: the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current) and caches it; the first call of a thread that has no CUDA context current binds the device's
+ *     primary context (cudaFree(0)).  Make those first calls before any stream capture begins.  Apart from that
+ *     set-up no call allocates or frees memory, and no call uses an allocating library routine.
  *   - All calls on a device share the one array, so two calls that overlap on the GPU (different streams,
  *     or different threads) race; order them on one stream.  Contents left by an earlier call are never
- *     read: the status word is cleared and everything else is rewritten before use. */
+ *     read: the status word is cleared and everything else is rewritten before use.
+ *   - sfb_static_device_status reads the device status word of the built-in scratch of the current device (the
+ *     first word of the array), like sfb_device_status does for a caller-provided workspace: 0, or the code a
+ *     bounded device-side wait left when it gave up, in which case the outputs of that call are incomplete. */
 int sfb_max_avg_forward_static(const float* F1, const float* F2, float* MA_u, float* MA_v, const sfb_shape* shape,
                                void* stream);
 size_t sfb_static_scratch_bytes(void);
+int sfb_static_device_status(void* stream, int32_t* device_status);
 
 /* Replaces MemorySaver.max_argmax_avg_forward (MemorySaver_cuda.cpp:23-34 -> MemorySaver_kernel_forward.cu:962-1016). */
 int sfb_max_argmax_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u,
@@ -294,6 +300,15 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
 /* Synchronises `stream`, reads the workspace's device status word into *device_status and returns
  * SFB_OK if it is 0, SFB_ERR_DEVICE_TIMEOUT otherwise. */
 int sfb_device_status(const void* workspace, void* stream, int32_t* device_status);
+
+/* Test hook, no counterpart in the reference.  Every device-side wait in the kernels is bounded: when it runs out
+ * the kernel writes a code to the status word (101 producer, 102 MMA issuer, 103 epilogue, 104 generator), all
+ * roles of the CTA leave their loops, tensor memory is freed and the kernel returns by itself.  This call lets a
+ * test see that path without faulting or hanging anything: `wait_limit_ns` replaces the 2 s limit of one wait
+ * (0 = back to the default) and `drop_last_load` != 0 makes the correlation sweeps launched from now on leave out
+ * the last block their producer would load, so that exactly one wait has nothing to wait for.  Process-wide; call
+ * it with (0, 0) to return to normal operation. */
+int sfb_debug_wait_timeout(uint64_t wait_limit_ns, int drop_last_load);
 
 /* Per-kernel timing, off by default; no counterpart in the reference ops (its scripts time whole calls
  * with torch.utils.benchmark, scripts/test_maxavg_cuda.py:237-265).  While enabled, every kernel launch

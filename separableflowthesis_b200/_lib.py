@@ -36,7 +36,7 @@ EXPORTED_SYMBOLS = (
     "sfb_max_argmax_avg_backward", "sfb_compression_forward", "sfb_compression_backward",
     "sfb_corr_volume", "sfb_device_status", "sfb_status_string", "sfb_last_error", "sfb_version",
     "sfb_kernel_timing_enable", "sfb_kernel_timing_count", "sfb_kernel_timing_read",
-    "sfb_max_avg_forward_static", "sfb_static_scratch_bytes", "sfb_separation_backward",
+    "sfb_max_avg_forward_static", "sfb_static_scratch_bytes", "sfb_static_device_status", "sfb_separation_backward",
     "sfb_compression_attention_backward", "sfb_separation_feature_backward",
     "sfb_max_argmax_avg_forward_cf", "sfb_compression_forward_cf", "sfb_compression_attention_backward_cf",
     "sfb_separation_feature_backward_cf", "sfb_attention_forward", "sfb_attention_backward_workspace_bytes",
@@ -44,7 +44,7 @@ EXPORTED_SYMBOLS = (
     "sfb_separation_level_forward_fmaps", "sfb_separation_level_backward_fmaps",
     "sfb_upsample_displacement", "sfb_upsample_displacement_backward", "sfb_lookup_pyramid_bytes",
     "sfb_set_sweep_operands", "sfb_get_sweep_operands", "sfb_lookup_build_pyramid", "sfb_lookup_forward", "sfb_lookup_backward",
-    "sfb_lookup4d_forward", "sfb_lookup4d_backward",
+    "sfb_lookup4d_forward", "sfb_lookup4d_backward", "sfb_debug_wait_timeout",
 )
 
 
@@ -115,6 +115,10 @@ def load() -> ctypes.CDLL:
     lib.sfb_max_avg_forward_static.argtypes = [P, P, P, P, SH, P]
     lib.sfb_static_scratch_bytes.restype = SZ
     lib.sfb_static_scratch_bytes.argtypes = []
+    lib.sfb_static_device_status.restype = ctypes.c_int
+    lib.sfb_static_device_status.argtypes = [P, ctypes.POINTER(ctypes.c_int32)]
+    lib.sfb_debug_wait_timeout.restype = ctypes.c_int
+    lib.sfb_debug_wait_timeout.argtypes = [ctypes.c_uint64, ctypes.c_int]
     lib.sfb_device_status.restype = ctypes.c_int
     lib.sfb_device_status.argtypes = [P, P, ctypes.POINTER(ctypes.c_int32)]
     lib.sfb_status_string.restype = ctypes.c_char_p

@@ -43,6 +43,36 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled is a driver call and needs a context that is current to the calling thread.  A thread that
+// has made no runtime call yet (an autograd worker whose first node is one of these ops) has none.  Whether one is
+// current is asked of the driver (cuCtxGetCurrent, which allocates nothing and is legal at any time); only when
+// there is none does the thread bind the device's primary context with cudaFree(0), once.
+typedef CUresult (*CtxGetCurrentFn)(CUcontext*);
+int bind_context() {
+  static thread_local bool bound = false;
+  if (bound) return SFB_OK;
+  static CtxGetCurrentFn get_current = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      return reinterpret_cast<CtxGetCurrentFn>(p);
+    return static_cast<CtxGetCurrentFn>(nullptr);
+  }();
+  CUcontext ctx = nullptr;
+  if (get_current == nullptr || get_current(&ctx) != CUDA_SUCCESS || ctx == nullptr) {
+    cudaError_t e = cudaFree(nullptr);
+    if (e != cudaSuccess) return fail(SFB_ERR_CUDA, "cudaFree(0): %s", cudaGetErrorString(e));
+  }
+  bound = true;
+  return SFB_OK;
+}
+#define SFB_TRY_BIND_CONTEXT()                 \
+  do {                                         \
+    int rc_ = bind_context();                  \
+    if (rc_ != SFB_OK) return rc_;             \
+  } while (0)
+
 // Tiled fp32 tensor map, 128-byte swizzle, innermost box = 32 channels (128 bytes), zero fill out of bounds.
 // dims/box are innermost-first; strides are implied by a contiguous tensor.
 // `pitch0` (elements, optional): distance between consecutive indices of dimension 1 when the rows are padded.
@@ -50,14 +80,7 @@ int make_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, 
              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, bool bf16 = false, uint64_t pitch0 = 0) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
-  // The driver call needs a context that is current to this thread.  A thread that has made no runtime call yet
-  // (an autograd worker whose first node is one of these ops) has none; cudaFree(0) binds the primary context.
-  static thread_local bool context_bound = false;
-  if (!context_bound) {
-    cudaError_t e = cudaFree(nullptr);
-    if (e != cudaSuccess) return fail(SFB_ERR_CUDA, "cudaFree(0): %s", cudaGetErrorString(e));
-    context_bound = true;
-  }
+  SFB_TRY_BIND_CONTEXT();
   cuuint64_t gdim[5], gstride[5];
   cuuint32_t bdim[5], estride[5];
   uint64_t stride = bf16 ? 2 : sizeof(float);
@@ -142,6 +165,20 @@ void drain_timing_locked() {
 // Operand type of the correlation sweeps of the level calls: 0 = TF32 (default), 1 = BF16.  Process-wide, because
 // a backward runs on an autograd worker thread, not on the thread that chose the precision.
 std::atomic<int> g_sweep_operands{0};
+
+// Test hook (sfb_debug_wait_timeout): time limit handed to the kernels' bounded waits and whether the next sweeps
+// leave out their last load.  Process-wide; 0 / 0 = normal operation.
+std::atomic<unsigned long long> g_wait_limit_ns{0};
+std::atomic<int> g_drop_last_load{0};
+SweepArgs with_wait_settings(SweepArgs a) {
+  a.wait_limit_ns = g_wait_limit_ns.load();
+  a.drop_last_load = g_drop_last_load.load();
+  return a;
+}
+GradArgs with_wait_settings(GradArgs a) {
+  a.wait_limit_ns = g_wait_limit_ns.load();
+  return a;
+}
 
 struct Workspace {
   int* status;
@@ -261,7 +298,8 @@ int check_shape(const sfb_shape* s, bool need_kc, Dims* d) {
     return fail(SFB_ERR_UNSUPPORTED_SHAPE, "image 1 has more than 2^21 pixels or image 2 more than 2^30");
   {  // element offsets inside one sample's packed array are 32-bit in the kernels
     const long long n1p = ((long long)s->H1 * s->W1 + TILE_M - 1) / TILE_M * TILE_M;
-    const long long slots = s->Kc + 2 > 8 ? s->Kc + 2 : 8;
+    const long long kc = need_kc ? s->Kc : 0;  // ops without attention channels ignore (and may not initialise) Kc
+    const long long slots = kc + 2 > 8 ? kc + 2 : 8;
     if (n1p * slots * (s->H2 > s->W2 ? s->H2 : s->W2) >= (1ll << 32))
       return fail(SFB_ERR_UNSUPPORTED_SHAPE, "H1*W1*max(H2,W2)*slots exceeds 2^32 elements per sample");
   }
@@ -353,7 +391,7 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   a.pu_arg = packed_view(w.ou, d.H2, MAXAVG_SLOTS, w.n1p, 2);
   a.pv_arg = packed_view(w.ov, d.W2, MAXAVG_SLOTS, w.n1p, 2);
   a.status = w.status;
-  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
+  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(with_wait_settings(a), tm_f1, tm_f2, tm_aux, st); }));
   // packed (displacement, slot, pixel) -> the reference's (pixel, channel, displacement) tensors
   const int N1 = d.N1(), R = MAXAVG_SLOTS;
   SFB_CUDA(timed(KID_PACK, with_argmax ? 4 : 2, st, [&] {
@@ -386,7 +424,7 @@ int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, co
     a.ou = ou; a.ov = ov;
     a.bf16 = bf16;
     a.status = status;
-    SFB_CUDA(timed(KID_SWEEP_COMPRESS, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));
+    SFB_CUDA(timed(KID_SWEEP_COMPRESS, 1, st, [&] { return launch_sweep(with_wait_settings(a), tm_f1, tm_f2, tm_f2 /* unused */, st); }));
   }
   return SFB_OK;
 }
@@ -430,7 +468,7 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   a.image2_major = 0;
   a.out = gF1;
   a.out_scale = scale1;
-  SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(a, tm_y, tm_xu, tm_xu /* unused */, st); }));
+  SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(with_wait_settings(a), tm_y, tm_xu, tm_xu /* unused */, st); }));
   // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1, XU and XV.
   {  // (N1, C, B) with rows padded to n1p; box = 32 pixels x all channels
     const uint64_t dims[3] = {(uint64_t)d.N1(), (uint64_t)d.C, (uint64_t)d.B};
@@ -442,7 +480,7 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   a.image2_major = 1;
   a.out = gF2;
   a.out_scale = 1.f;
-  SFB_CUDA(timed(kid + 1, 1, st, [&] { return launch_grad_gemm(a, tm_y, tm_xu, tm_xv, st); }));
+  SFB_CUDA(timed(kid + 1, 1, st, [&] { return launch_grad_gemm(with_wait_settings(a), tm_y, tm_xu, tm_xv, st); }));
   return SFB_OK;
 }
 
@@ -573,13 +611,19 @@ int sfb_max_avg_forward_static(const float* F1, const float* F2, float* MA_u, fl
   a.pu = packed_view(w.ou, d.H2, MAXAVG_SLOTS, w.n1p);
   a.pv = packed_view(w.ov, d.W2, MAXAVG_SLOTS, w.n1p);
   a.status = w.status;
-  SFB_CUDA(launch_sweep(a, tm_f1, tm_f2, tm_aux, st));
+  SFB_CUDA(launch_sweep(with_wait_settings(a), tm_f1, tm_f2, tm_aux, st));
   SFB_CUDA(launch_unpack(w.ou, MA_u, d.B, d.N1(), w.n1p, 2, d.H2, MAXAVG_SLOTS, 0, 1, 2, 0, st));
   SFB_CUDA(launch_unpack(w.ov, MA_v, d.B, d.N1(), w.n1p, 2, d.W2, MAXAVG_SLOTS, 0, 1, 2, 0, st));
   return SFB_OK;
 }
 
 size_t sfb_static_scratch_bytes(void) { return STATIC_SCRATCH_BYTES; }
+
+int sfb_static_device_status(void* stream, int32_t* device_status) {
+  void* scratch = nullptr;
+  SFB_TRY(static_scratch(&scratch));  // the status word is the first word of the built-in scratch
+  return sfb_device_status(scratch, stream, device_status);
+}
 
 int sfb_max_argmax_avg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u,
                                int32_t* AM_v, const sfb_shape* shape, void* workspace, size_t workspace_bytes,
@@ -767,7 +811,7 @@ int sfb_max_argmax_avg_forward_cf(const float* F1, const float* F2, float* SEP_v
   a.pu_arg = cf_view(AM_u, 1, d.H2, N1);
   a.pv_arg = cf_view(AM_v, 1, d.W2, N1);
   a.status = w.status;
-  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
+  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(with_wait_settings(a), tm_f1, tm_f2, tm_aux, st); }));
   return SFB_OK;
 }
 
@@ -976,7 +1020,7 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   a.pv_arg = cf_view(AM_v, 1, d.W2, N1);
   a.bf16 = bf16;
   a.status = w.status;
-  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_aux, st); }));
+  SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(with_wait_settings(a), tm_f1, tm_f2, tm_aux, st); }));
   const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
   SFB_CUDA(timed(KID_ATTENTION_FWD, 2 * ((K + 3) / 4), st, [&] {
     launch_attention_forward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u + (size_t)c0 * d.W2 * N1, sb_u, weight_u,
@@ -1264,7 +1308,13 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
   a.n_valid = w.n1p;
   a.dump = S;
   a.status = w.status;
-  SFB_CUDA(timed(KID_SWEEP_DUMP, 1, st, [&] { return launch_sweep(a, tm_f1, tm_f2, tm_f2 /* unused */, st); }));
+  SFB_CUDA(timed(KID_SWEEP_DUMP, 1, st, [&] { return launch_sweep(with_wait_settings(a), tm_f1, tm_f2, tm_f2 /* unused */, st); }));
+  return SFB_OK;
+}
+
+int sfb_debug_wait_timeout(uint64_t wait_limit_ns, int drop_last_load) {
+  g_wait_limit_ns.store(wait_limit_ns);
+  g_drop_last_load.store(drop_last_load != 0 ? 1 : 0);
   return SFB_OK;
 }
 

@@ -83,6 +83,8 @@ struct SweepArgs {
   int bf16;              // operands are BF16 copies (64 channels per 128-byte row, tcgen05.mma kind::f16) instead of TF32
   float* dump;           // SWEEP_DUMP: dense S (B,N1,H2,W2), test use only
   int* status;           // device status word
+  unsigned long long wait_limit_ns;  // time limit of one device-side wait; 0 = the default (2 s)
+  int drop_last_load;    // test hook: the producer leaves out its last F2 block, so that one wait runs out
 };
 
 // Gradient GEMM.  G = dLoss/dS is generated from two "interleaved" operand sets: for every displacement
@@ -110,6 +112,7 @@ struct GradArgs {
   const float* xv;
   float* out;            // gF1 (B,N1,C) or gF2 (B,N2,C)
   int* status;
+  unsigned long long wait_limit_ns;  // time limit of one device-side wait; 0 = the default (2 s)
 };
 
 // One source of an interleaved slot: dst[b][d][slot/4][p][slot%4] = scale * src[b][p][k][d] (raw copy when scale == 0);

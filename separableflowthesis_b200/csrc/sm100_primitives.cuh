@@ -19,6 +19,22 @@ enum DeviceStatus : int {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait, then give up
 
+// Per-CTA state of the bounded waits, in shared memory: the flag a role raises when it gives up (every other
+// role of the CTA then leaves its loops too) and the time limit of one wait.
+struct WaitCtl {
+  int abort_flag;
+  int reserved;
+  unsigned long long limit_ns;
+};
+__device__ __forceinline__ void wait_ctl_init(WaitCtl* ctl, unsigned long long limit_ns) {  // 0 = WAIT_LIMIT_NS
+  ctl->abort_flag = 0;
+  ctl->reserved = 0;
+  ctl->limit_ns = limit_ns != 0 ? limit_ns : WAIT_LIMIT_NS;
+}
+__device__ __forceinline__ bool wait_ctl_aborted(const WaitCtl* ctl) {
+  return *reinterpret_cast<const volatile int*>(&ctl->abort_flag) != 0;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -51,28 +67,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Waits for the phase with the given parity.  Never spins forever: after WAIT_LIMIT_NS, or as
+// Waits for the phase with the given parity.  Never spins forever: after the CTA's time limit, or as
 // soon as another role of this CTA has given up, it records `code` in *status (first error
 // wins), raises the CTA-wide abort flag and returns false.  Callers leave their loops on false.
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                            int* status, int code) {
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, WaitCtl* ctl, int* status,
+                                                   int code) {
   const unsigned long long t0 = global_ns();
+  const unsigned long long limit = *reinterpret_cast<volatile unsigned long long*>(&ctl->limit_ns);
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > WAIT_LIMIT_NS) {
-        *abort_flag = 1;
+      if (wait_ctl_aborted(ctl)) return false;
+      if (global_ns() - t0 > limit) {
+        *reinterpret_cast<volatile int*>(&ctl->abort_flag) = 1;
         atomicCAS(status, 0, code);
         return false;
       }
     }
   }
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, WaitCtl* ctl, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag, status, code);
+  return mbar_wait_slow(bar, parity, ctl, status, code);
 }
 
 __device__ __forceinline__ void fence_barrier_init() {

@@ -8,13 +8,19 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from typing import Dict, List, Tuple
 
 import torch
 
 from . import _lib
 
+# Scratch buffers handed to the library, one per (device, stream): calls that share a workspace must be ordered on
+# one stream.  A buffer grows to the largest size asked for and is kept for reuse (7.5 GB for a level backward of
+# B=8, 135x240, Kc=4); release_workspaces() drops them.  The lock covers DataParallel-style callers that run the ops
+# from several threads.
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+_workspaces_lock = threading.Lock()
 
 
 def _check(t: torch.Tensor, name: str, dtype: torch.dtype, ndim: int) -> None:
@@ -52,11 +58,24 @@ def _check_like(t: torch.Tensor, name: str, shape, dtype, device) -> None:
 
 def _workspace(nbytes: int, device: torch.device, stream: int) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-    return ws
+    with _workspaces_lock:
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            _workspaces[key] = ws
+        return ws
+
+
+def release_workspaces(device=None) -> int:
+    """Drop the cached scratch buffers (of one device, or of all) and return the bytes released to torch's
+    allocator.  Work already enqueued keeps its buffer alive through torch's stream-ordered allocator only if the
+    caller synchronises first: call this between steps, not while ops are in flight."""
+    index = None if device is None else torch.device(device).index
+    freed = 0
+    with _workspaces_lock:
+        for key in [k for k in _workspaces if index is None or k[0] == index]:
+            freed += _workspaces.pop(key).numel()
+    return freed
 
 
 def _ptr(t):

@@ -95,17 +95,25 @@ def reduce_row_partial(gF2: torch.Tensor, row_group) -> torch.Tensor:
 
 def reduce_parameter_grads(params: Iterable[torch.nn.Parameter], group=None) -> Optional[torch.Tensor]:
     """Sum the gradients of the shared attention parameters over all ranks with ONE flat all-reduce
-    (a few hundred floats: latency-bound, so one message).  Returns the flat buffer."""
-    params = [p for p in params if p.grad is not None]
+    (a few hundred floats: latency-bound, so one message).  Returns the flat buffer.
+
+    Every rank passes the same parameters in the same order, and the flat buffer always covers all of them: a
+    parameter that got no gradient on this rank (a shard whose outputs did not reach the loss) contributes zeros
+    and receives the sum of the others, so the ranks never all-reduce buffers of different lengths."""
+    params = list(params)
     if not params:
         return None
-    flat = torch.cat([p.grad.reshape(-1) for p in params])
+    flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1) for p in params])
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
     off = 0
     for p in params:
-        n = p.grad.numel()
-        p.grad.copy_(flat[off:off + n].view_as(p.grad))
+        n = p.numel()
+        piece = flat[off:off + n].view_as(p)
+        if p.grad is None:
+            p.grad = piece.clone()
+        else:
+            p.grad.copy_(piece)
         off += n
     return flat
 

@@ -97,3 +97,16 @@ def test_argument_validation_of_the_call_site_entry_points(lib):
     rc = lib.sfb_separation_level_forward_fmaps(p, p, ctypes.c_float(1.0), p, p, p, p, p, p, 5, 3, None, None, p, p,
                                                 ctypes.byref(s), p, 1 << 30, None)
     assert rc == _lib.SFB_ERR_INVALID_ARGUMENT and b"do not fit" in lib.sfb_last_error()
+
+
+def test_max_avg_ops_ignore_an_uninitialised_kc():
+    """The max/avg entry points do not read Kc (the header says so): a garbage value must neither be rejected nor
+    overflow the size checks."""
+    lib = _lib.load()
+    for kc in (0x7fffffff, -5, 0):
+        s = _lib.SfbShape(1, 48, 64, 48, 64, 256, kc)
+        assert lib.sfb_workspace_bytes(_lib.OP_MAX_AVG_FORWARD, ctypes.byref(s)) > 0
+        assert lib.sfb_workspace_bytes(_lib.OP_MAX_ARGMAX_AVG_BACKWARD, ctypes.byref(s)) > 0
+    # ops that do use Kc still check it
+    s = _lib.SfbShape(1, 48, 64, 48, 64, 256, 0)
+    assert lib.sfb_workspace_bytes(_lib.OP_COMPRESSION_FORWARD, ctypes.byref(s)) == 0

@@ -72,6 +72,15 @@ def _worker(rank, world, port, B, results):
         expect = float(sum(range(1, world + 1)))
         ok = ok and flat.numel() == 2 * 27 * Kc + Kc and bool((flat == expect).all())
         ok = ok and all(bool((p.grad == expect).all()) for p in conv.parameters())
+        # a rank without a gradient for one parameter still joins with a buffer of the full length: it contributes
+        # zeros there and receives the others' sum
+        for p in conv.parameters():
+            p.grad = torch.full_like(p, float(rank + 1))
+        if rank == 0:
+            conv.bias.grad = None
+        flat = sharding.reduce_parameter_grads(conv.parameters())
+        ok = ok and flat.numel() == 2 * 27 * Kc + Kc and bool((conv.weight.grad == expect).all())
+        ok = ok and conv.bias.grad is not None and bool((conv.bias.grad == expect - 1.0).all())
         results[rank] = ok
     finally:
         dist.destroy_process_group()
