@@ -193,8 +193,13 @@ def make_job(cfg, shard, device, path="ops"):
     if path == "level":
         job["att"] = attention_parameters(Kc, device)
         if cfg["bwd"]:
-            job["gSEP_u"] = torch.randn(b, 2 + Kc, W, h, W, generator=gd, device=device)
-            job["gSEP_v"] = torch.randn(b, 2 + Kc, H, h, W, generator=gd, device=device)
+            # drawn per sample for all image-1 rows, then sliced: every partition of the job sees the same gradients
+            job["gSEP_u"] = torch.empty(b, 2 + Kc, W, h, W, device=device)
+            job["gSEP_v"] = torch.empty(b, 2 + Kc, H, h, W, device=device)
+            for i, bi in enumerate(range(shard.b0, shard.b1)):
+                gs = torch.Generator(device=device).manual_seed(SEED + 1000 + bi)
+                job["gSEP_u"][i] = torch.randn(2 + Kc, W, H, W, generator=gs, device=device)[:, :, e0:e1]
+                job["gSEP_v"][i] = torch.randn(2 + Kc, H, H, W, generator=gs, device=device)[:, :, e0:e1]
             if shard.g_rows > 1:   # the outputs of halo rows are not used: no upstream gradient there
                 _, _, i0, i1 = _sh.halo_range(shard, H)
                 for t in (job["gSEP_u"], job["gSEP_v"]):
@@ -229,7 +234,10 @@ def run_level(ms, cfg, job, row_group=None):
         if shard.g_rows > 1:
             from separableflowthesis_b200 import sharding
             grads[0] = sharding.exchange_halo_grads(grads[0], shard, cfg["H"], row_group, dim=1)
-            grads[1] = sharding.reduce_row_partial(grads[1], row_group)
+            if grads[1].shape[0] % shard.g_rows == 0:   # each rank keeps the gradient of its slice of the samples
+                grads[1] = sharding.reduce_scatter_batch(grads[1], row_group)
+            else:
+                grads[1] = sharding.reduce_row_partial(grads[1], row_group)
         out = out + grads
     return out
 
@@ -482,7 +490,8 @@ class E2E:
     AlternateCorrBlockSepflow.separate (one level, Conv3d attention) -> backward with upstream
     gradients -> loss-sized results back on the host."""
 
-    def __init__(self, cfg, job, device, chunks=1, levels=1, shard=None, row_group=None, prefetch=False):
+    def __init__(self, cfg, job, device, chunks=1, levels=1, shard=None, row_group=None, prefetch=False,
+                 f2_from_rank0=False):
         import separableflowthesis_b200 as sfb
         self.sfb, self.cfg, self.device = sfb, cfg, device
         self.prefetch, self.prefetched = prefetch, None
@@ -491,7 +500,16 @@ class E2E:
         self.shard, self.row_group = shard, row_group
         self.copy_stream = torch.cuda.Stream(device=device)
         self.h1 = job["f1_nchw"].pin_memory()
-        self.h2 = job["f2_nchw"].pin_memory()
+        # Row shards of one sample all need the whole of image 2.  `f2_from_rank0` (the name of the first variant; now
+        # every rank holds a slice): each rank of the row group copies 1/G of the samples' image-2 features from the
+        # host and an all-gather over NVLink completes them on every GPU, instead of G host copies of all of them.
+        f2 = job["f2_nchw"]
+        self.gather_f2 = bool(f2_from_rank0 and shard is not None and shard.g_rows > 1 and f2.shape[0] % shard.g_rows == 0)
+        if self.gather_f2:
+            per = f2.shape[0] // shard.g_rows
+            ri = shard.rank % shard.g_rows
+            f2 = f2[ri * per:(ri + 1) * per].contiguous()
+        self.h2 = f2.pin_memory()
         self.att = None
         if cfg["Kc"] > 0:
             params = attention_parameters(cfg["Kc"])
@@ -523,7 +541,11 @@ class E2E:
         def stage(b0, b1):
             with torch.cuda.stream(self.copy_stream):
                 f1 = self.h1[b0:b1].to(dev, non_blocking=True)
-                f2 = self.h2[b0:b1].to(dev, non_blocking=True)
+                if self.gather_f2:   # one micro-batch in this mode: this rank's slice, then the others' over NVLink
+                    from separableflowthesis_b200 import sharding
+                    f2 = sharding.allgather_batch(self.h2.to(dev, non_blocking=True), self.row_group)
+                else:
+                    f2 = self.h2[b0:b1].to(dev, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self.copy_stream)
             return f1, f2, ev
@@ -563,7 +585,8 @@ class E2E:
                 g1, g2 = f1.grad, f2.grad
                 if sharded_rows:   # halo rows of gF1 go to the neighbouring shards, gF2 is summed over the row group
                     g1 = sharding.exchange_halo_grads(g1, self.shard, cfg["H"], self.row_group, dim=2)
-                    g2 = sharding.reduce_row_partial(g2, self.row_group)
+                    g2 = (sharding.reduce_scatter_batch(g2, self.row_group) if self.gather_f2
+                          else sharding.reduce_row_partial(g2, self.row_group))
                 pieces += [g1.sum().reshape(1), g2.sum().reshape(1)]
             else:
                 pieces += [sep_u.sum().reshape(1), sep_v.sum().reshape(1)]
@@ -665,6 +688,125 @@ def measure_tf32_peak(device):
     return fl / best / 1e9, fl / sustained / 1e9  # TFLOP/s
 
 
+# --------------------------------------------------------------------------------------- sub-records
+def extra_levels4(time_e2e, e2e_one_level):
+    """The call site with the reference's four pyramid levels (core/corr.py:377-382,416: image 2 pooled three times,
+    every op run per level), end to end like `e2e`.  The metric's cells are level-0 cells; levels 1-3 add 0.33x."""
+    rec = time_e2e(4, 3, 2)
+    out = {"ms_per_step": rec["ms_per_step"], "ms_per_step_min": rec["ms_per_step_min"],
+           "level0_cells_per_s": rec["value"], "cells_incl_coarse_levels_per_s": rec["value"] * (1 + 1 / 4 + 1 / 16 + 1 / 64)}
+    if e2e_one_level:
+        out["ratio_to_one_level"] = rec["ms_per_step"] / e2e_one_level["ms_per_step"]
+    return out
+
+
+def extra_config4_bf16(ms, device, args):
+    """BASELINE config 4 as it is stated (B=8, 47x156, Kc=2, BF16 operands, forward + backward) through the level
+    calls, device-resident, with the largest deviation of the max/mean channels of a band of image-1 rows from an
+    FP32 torch matmul on the same features (BF16 rounds the operands to 8 bits: ~1e-2 of the largest value)."""
+    from separableflowthesis_b200 import _lib, sharding
+    cfg = dict(CONFIGS[4])
+    job = make_job(cfg, sharding.make_shard(cfg["B"], cfg["H"], 1, 0), device, "level")
+    lib = _lib.load()
+    prev = lib.sfb_set_sweep_operands(1)
+    try:
+        for _ in range(3):
+            out = run_level(ms, cfg, job)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = max(5, args.steps)
+        e0.record()
+        for _ in range(steps):
+            out = run_level(ms, cfg, job)
+        e1.record()
+        torch.cuda.synchronize()
+    finally:
+        lib.sfb_set_sweep_operands(prev)
+    t = e0.elapsed_time(e1) / steps
+    sep_u, sep_v = out[0], out[1]
+    r0, r1 = 20, 24
+    prev_tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    F1, F2 = job["F1"][:1, r0:r1], job["F2"][:1]
+    S = torch.matmul(F1.reshape(1, -1, C_FEAT), F2.reshape(1, -1, C_FEAT).transpose(1, 2))
+    S = S.reshape(1, r1 - r0, cfg["W"], cfg["H"], cfg["W"])
+    torch.backends.cuda.matmul.allow_tf32 = prev_tf32
+    ref_v = torch.stack((S.max(4).values, S.mean(4)), 1).permute(0, 1, 4, 2, 3)   # (1, 2, H2, rows, W1): per-u channels
+    ref_u = torch.stack((S.max(3).values, S.mean(3)), 1).permute(0, 1, 4, 2, 3)   # (1, 2, W2, rows, W1)
+    err = max(((sep_v[:1, :2, :, r0:r1] - ref_v).abs().max() / ref_v.abs().max()).item(),
+              ((sep_u[:1, :2, :, r0:r1] - ref_u).abs().max() / ref_u.abs().max()).item())
+    return {"workload": cfg["name"].replace("(fp32 operands)", "(bf16 operands in the sweeps)"),
+            "value": job["cells"] / (t * 1e-3), "unit": "cells/s", "ms_per_step": t, "steps": steps,
+            "dtype": "bf16 operands in the sweeps, tf32 in the gradient GEMMs, fp32 accumulate",
+            "max_rel_err_max_mean_channels_vs_fp32": err, "band": f"sample 0, image-1 rows {r0}..{r1 - 1}"}
+
+
+def extra_reference_cuda(args):
+    """The reference's own CUDA extension (oracle/_ref/MemorySaver.so, built unmodified from libs/MemorySaver/src) on
+    this GPU next to this library, on BASELINE config 2 (B=2, 48x64, Kc=2: the channel count its forward kernel
+    computes), the five ops device-resident in the reference's layouts."""
+    lines = []
+    sub = argparse.Namespace(steps=max(2, min(args.steps, 3)), warmup=3)
+    cfg = dict(CONFIGS[2])
+    metric = "separated cost-volume cells/sec (fwd+bwd)"
+    run_reference_cuda(sub, cfg, metric, "cells/s", lines.append)
+    if len(lines) == 1:
+        return lines[0]
+    ref, ours = lines
+    return {"workload": cfg["name"], "path": "the five ops in the reference's layouts, device-resident",
+            "reference_cuda": {"value": ref["value"], "ms_per_step": ref["ms_per_step"], "steps": ref["steps"]},
+            "this_library": {"value": ours["value"], "ms_per_step": ours["ms_per_step"], "steps": ours["steps"]},
+            "ratio": ours["value"] / ref["value"], "unit": "cells/s"}
+
+
+def extra_row_shard(args, cfg, world, rank, device, ms, time_e2e, barrier, max_over_ranks, sum_over_ranks, e0, e1,
+                    batch_job):
+    """The partition BASELINE config 5 names: every rank holds all samples and a block of image-1 rows (plus one halo
+    row per side for the attention stencil).  Image 2's features are copied from the host once (each rank 1/N of the
+    samples) and completed on every GPU by an all-gather over NVLink; the partial image-2 feature gradients are
+    reduce-scattered back to those slices; halo rows of the image-1 gradient go to the neighbours.  Reports the
+    device-resident and end-to-end throughput and how far the gradients are from the batch-sharded run's on the same
+    seeded data."""
+    from separableflowthesis_b200 import sharding
+    shard = sharding.make_shard(cfg["B"], cfg["H"], world, rank, prefer="rows")
+    group = sharding.new_row_groups(world, shard.g_rows)
+    job = make_job(cfg, shard, device, "level")
+    total_cells = sum_over_ranks(float(job["cells"]))
+
+    def norms(j, grp):
+        out = run_level(ms, cfg, j, grp)
+        g1, g2, gw = out[6], out[7], torch.cat([out[8].reshape(-1), out[10].reshape(-1)]).double()
+        torch.distributed.all_reduce(gw)   # the parameters are shared: their gradient is the sum over all ranks
+        # every element of gF1 / gF2 is owned by exactly one rank in either partition
+        return [sum_over_ranks(g1.double().abs().sum().item()), sum_over_ranks(g2.double().abs().sum().item()),
+                gw.abs().sum().item()]
+
+    n_batch = norms(batch_job, None)
+    n_rows = norms(job, group)
+    diff = [abs(a - b) / max(abs(a), 1e-30) for a, b in zip(n_batch, n_rows)]
+    for _ in range(max(1, args.warmup - 1)):
+        run_level(ms, cfg, job, group)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        run_level(ms, cfg, job, group)
+    e1.record()
+    barrier()
+    t = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    e2e = time_e2e(1, args.steps, 2, sh=shard, grp=group, jb=job, f2_from_rank0=True)
+    e2e_value = total_cells / (e2e["ms_per_step"] * 1e-3)
+    f2_bytes = cfg["B"] * C_FEAT * cfg["H"] * cfg["W"] * 4
+    return {"sharding": f"batch x rows = {shard.g_batch} x {shard.g_rows}", "value": total_cells / (t * 1e-3),
+            "unit": "cells/s", "ms_per_step": t, "steps": args.steps,
+            "e2e": {"value": e2e_value, "ms_per_step": e2e["ms_per_step"], "ms_per_step_min": e2e["ms_per_step_min"],
+                    "h2d_bytes_per_step": e2e["h2d_bytes_per_step"], "d2h_bytes_per_step": e2e["d2h_bytes_per_step"]},
+            "nvlink_bytes_per_rank_per_step": {
+                "image2_features_all_gather": f2_bytes * (world - 1) // world,
+                "image2_gradient_reduce_scatter": f2_bytes * (world - 1) // world,
+                "image1_gradient_halo_rows": 2 * 2 * cfg["B"] * C_FEAT * cfg["W"] * 4},
+            "rel_diff_vs_batch_sharded": {"sum_abs_gF1": diff[0], "sum_abs_gF2": diff[1], "sum_abs_gweights": diff[2]}}
+
+
 def main():
     # Libraries (NCCL among them) print banners on stdout; keep stdout for the one JSON line by sending
     # everything else to stderr.
@@ -711,6 +853,10 @@ def main():
                     help="pyramid levels of the end-to-end block (the metric counts level-0 cells; the reference's "
                          "model uses 4 levels = 1.33x the cells)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small ncu captures)")
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="timed regions of --steps steps each; the first is the headline, all of them give the spread")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the sub-records (reference's CUDA kernels, config 4 in BF16, 4-level pyramid, row shards)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.batch > 0:
@@ -804,6 +950,25 @@ def main():
     clocks = sampler.stop() if sampler else None
     ms_per_step = ms_total / args.steps
     value = total_cells / (ms_per_step * 1e-3)
+    # the same timed region again, for the spread (the headline stays the first region, timed as above)
+    region_ms = [ms_per_step]
+    for _ in range(max(0, args.repeats - 1)):
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            run_ops(ms, cfg, job, not args.unfused, row_group)
+        e1.record()
+        barrier()
+        region_ms.append(max_over_ranks(e0.elapsed_time(e1)) / args.steps)
+    spread = {"regions": len(region_ms), "steps_per_region": args.steps, "ms_per_step_median": statistics.median(region_ms),
+              "ms_per_step_min": min(region_ms), "ms_per_step_max": max(region_ms)}
+    # host time of one step's launch path (Python + ctypes + tensor-map encodes + launches), device idle at the start
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        run_ops(ms, cfg, job, not args.unfused, row_group)
+    host_ms_per_step = (time.perf_counter() - t0) / 3 * 1e3
+    torch.cuda.synchronize()
 
     # ---- per-kernel device time of the same steps (separate pass: events around every launch) ----
     report = []
@@ -820,52 +985,96 @@ def main():
     if rank == 0 and report:
         tot = sum(r[1] for r in report)
         kernels = [{"kernel": n, "launches": l, "ms_per_launch": t / l, "share": t / tot} for n, t, l in report]
-        name, t, l = max((r for r in report if r[0].startswith(("sweep_kernel", "grad_gemm_kernel"))),
-                         key=lambda r: r[1])   # the dominant contraction kernel
         tf32_burst, tf32_sust = measure_tf32_peak(device)
-        fl = 2.0 * C_FEAT * job["cells"]            # one contraction over this rank's cells per launch
-        achieved = fl / (t / l * 1e-3) / 1e12
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except OSError:
             pass
-        bpc = DRAM_BYTES_PER_CELL.get(name)
-        roofline = {"bound": "tensor", "kernel": name, "achieved": achieved, "peak": tf32_sust, "unit": "TFLOP/s",
-                    "frac": achieved / tf32_sust, "traffic": (bpc * job["cells"]) if bpc else None,
-                    "peak_source": "cuBLAS TF32 8192^3 via torch.matmul measured in this run, sustained (~1 s loop); "
-                                   f"burst {tf32_burst:.1f}; MEASURED_PEAKS.json has no TF32 entry "
-                                   f"(its bf16: {peaks.get('bf16_tflops')} burst / {peaks.get('bf16_tflops_sustained')} sustained)",
-                    "algorithmic_flop_per_launch": fl, "ms_per_launch": t / l}
+        # MEASURED_PEAKS.json has dense BF16 only; TF32 runs at half its rate on the tensor cores.  The kernels are
+        # timed inside back-to-back steps under the power cap, so the sustained figure is the denominator.
+        file_sust = 0.5 * float(peaks["bf16_tflops_sustained"]) if "bf16_tflops_sustained" in peaks else None
+        file_burst = 0.5 * float(peaks["bf16_tflops"]) if "bf16_tflops" in peaks else None
+        fl = 2.0 * C_FEAT * job["cells"]            # one contraction over this rank's cells per launch
+        per_kernel = []
+        for name, t, l in report:
+            if not name.startswith(("sweep_kernel", "grad_gemm_kernel")):
+                continue
+            ach = fl / (t / l * 1e-3) / 1e12
+            per_kernel.append({"kernel": name, "ms_per_launch": t / l, "share": t / tot, "achieved": ach,
+                               "frac_of_cublas_tf32_sustained": ach / tf32_sust,
+                               "frac_of_half_bf16_sustained_file": ach / file_sust if file_sust else None})
+        dominant = max(per_kernel, key=lambda k: k["share"])
+        worst = min(per_kernel, key=lambda k: k["achieved"])
+        peak = file_sust if file_sust else tf32_sust
+        bpc = DRAM_BYTES_PER_CELL.get(dominant["kernel"])
+        roofline = {"bound": "tensor", "kernel": dominant["kernel"], "achieved": dominant["achieved"], "peak": peak,
+                    "unit": "TFLOP/s", "frac": dominant["achieved"] / peak,
+                    "traffic": (bpc * job["cells"]) if bpc else None,
+                    "peak_source": ("0.5 x bf16_tflops_sustained of MEASURED_PEAKS.json (of measured; the file has no TF32 "
+                                    "entry, TF32 runs at half the BF16 rate)" if file_sust else
+                                    "cuBLAS TF32 8192^3 via torch.matmul measured in this run, sustained (of fallback: no "
+                                    "MEASURED_PEAKS.json)"),
+                    "peak_measured_file": {"half_bf16_sustained": file_sust, "half_bf16_burst": file_burst},
+                    "peak_cublas_tf32_this_run": {"sustained": tf32_sust, "burst": tf32_burst},
+                    "algorithmic_flop_per_launch": fl, "ms_per_launch": dominant["ms_per_launch"],
+                    "worst_kernel": worst["kernel"], "worst_frac": worst["achieved"] / peak,
+                    "whole_step_frac": value * flops_per_cell(cfg) / 1e12 / world / peak,
+                    "per_kernel": per_kernel}
 
     # ---- end to end through the public API with host buffers ----
-    e2e = None
-    if not args.no_e2e:
-        runner = E2E(cfg, job, device, chunks=args.e2e_chunks, levels=args.levels, shard=shard, row_group=row_group,
-                     prefetch=not args.no_e2e_prefetch)   # warm-up runs the same pipeline (allocator steady state)
-        for _ in range(min(args.warmup, 3)):
+    def time_e2e(levels, steps, regions, sh=shard, grp=row_group, jb=job, f2_from_rank0=False):
+        """`regions` timed regions of `steps` steps each through AlternateCorrBlockSepflow from pinned host buffers; every
+        region starts without anything copied ahead and ends without a prefetch for a step outside it."""
+        runner = E2E(cfg, jb, device, chunks=args.e2e_chunks, levels=levels, shard=sh, row_group=grp,
+                     prefetch=not args.no_e2e_prefetch, f2_from_rank0=f2_from_rank0)
+        for _ in range(min(args.warmup, 3)):   # warm-up runs the same pipeline (allocator steady state)
             runner.step()
-        barrier()
-        runner.prefetched = None   # nothing copied before the timed region is used inside it
-        e0.record()
-        n_e2e = max(2, min(args.steps, 5))
-        for i in range(n_e2e):
-            runner.prefetch = (not args.no_e2e_prefetch) and i < n_e2e - 1   # the last step has no successor
-            runner.step()
-        e1.record()
-        barrier()
-        ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / n_e2e
-        e2e = {"value": total_cells / (ms_e2e * 1e-3), "unit": unit, "ms_per_step": ms_e2e,
+        per_step, host = [], []
+        for _ in range(regions):
+            barrier()
+            runner.prefetched = None   # nothing copied before the timed region is used inside it
+            t0 = time.perf_counter()
+            e0.record()
+            for i in range(steps):
+                runner.prefetch = (not args.no_e2e_prefetch) and i < steps - 1   # the last step has no successor
+                runner.step()
+            e1.record()
+            host.append((time.perf_counter() - t0) / steps * 1e3)
+            barrier()
+            per_step.append(max_over_ranks(e0.elapsed_time(e1)) / steps)
+        rec = {"value": total_cells / (per_step[0] * 1e-3), "unit": unit, "ms_per_step": per_step[0],
+               "regions": regions, "steps_per_region": steps, "ms_per_step_median": statistics.median(per_step),
+               "ms_per_step_min": min(per_step), "ms_per_step_max": max(per_step),
                "h2d_bytes_per_step": int(sum_over_ranks(float(runner.h2d))),
                "d2h_bytes_per_step": int(sum_over_ranks(float(runner.d2h))),
-               "pyramid_levels": args.levels,
-               "path": f"pinned host f1,f2 (B,C,H,W) -> AlternateCorrBlockSepflow(num_levels={args.levels}).separate with "
+               "pyramid_levels": levels, "chunks": runner.chunks}
+        del runner
+        return rec
+
+    e2e = None
+    if not args.no_e2e:
+        e2e = time_e2e(args.levels, args.steps, min(args.repeats, 3))
+        e2e["path"] = (f"pinned host f1,f2 (B,C,H,W) -> AlternateCorrBlockSepflow(num_levels={args.levels}).separate with "
                        "Conv3d attention -> autograd backward -> all-reduce of attention-parameter grads -> host; "
-                       f"{runner.chunks} micro-batch(es) per step, copy of one overlapping compute of the previous"
+                       f"{e2e['chunks']} micro-batch(es) per step, copy of one overlapping compute of the previous"
                        + ("" if args.no_e2e_prefetch else
                           "; the first micro-batch of the next timed step is copied while this step computes "
-                          "(all copies of the timed steps run inside the timed region)")}
-        del runner
+                          "(all copies of the timed steps run inside the timed region)")
+                       + ".  What returns to the host every step: the two feature-gradient checksums of each micro-batch "
+                         "and the summed attention-parameter gradients; the separated volumes and the feature gradients "
+                         "stay on the device, where the model's next layers (cost aggregation, encoder backward) "
+                         "consume them")
+
+    extras = {}
+    if not args.no_extras and args.config == 5 and args.batch == 0 and path == "level":
+        if world == 1:
+            extras["levels4"] = extra_levels4(time_e2e, e2e)
+            extras["config4_bf16"] = extra_config4_bf16(ms, device, args)
+            extras["reference_cuda"] = extra_reference_cuda(args)
+        else:
+            extras["row_shard"] = extra_row_shard(args, cfg, world, rank, device, ms, time_e2e, barrier, max_over_ranks,
+                                                  sum_over_ranks, e0, e1, job)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -887,9 +1096,11 @@ def main():
                    "sharding": f"batch x rows = {shard.g_batch} x {shard.g_rows}",
                    "l2": "inputs larger than L2" if args.config >= 3 else "inputs smaller than L2 (launch-bound case)"},
         "useful_tflops": value * flops_per_cell(cfg) / 1e12,
+        "repeats": spread, "host_ms_per_step": host_ms_per_step,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps,
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,
     }
+    line.update(extras)
     emit(line)
 
 

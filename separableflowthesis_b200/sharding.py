@@ -93,6 +93,34 @@ def reduce_row_partial(gF2: torch.Tensor, row_group) -> torch.Tensor:
     return gF2
 
 
+def allgather_batch(part: torch.Tensor, group) -> torch.Tensor:
+    """Image-2 features of all samples from the slices the ranks of a row group hold (sample-major, equal slices):
+    every rank copies 1/G of the samples from the host and the rest crosses NVLink once, instead of every rank
+    copying all of F2 from the host."""
+    world = dist.get_world_size(group)
+    full = torch.empty((part.shape[0] * world,) + tuple(part.shape[1:]), dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(full, part.contiguous(), group=group)
+    return full
+
+
+def reduce_scatter_batch(gF2: torch.Tensor, group) -> torch.Tensor:
+    """The adjoint of ``allgather_batch``: sums the partial image-2 feature gradients over the row group and leaves
+    every rank with the gradient of its own slice of the samples (half the traffic of an all-reduce, and the shard the
+    producer of that slice's features needs)."""
+    world = dist.get_world_size(group)
+    if gF2.shape[0] % world != 0:
+        raise ValueError(f"{gF2.shape[0]} samples do not split over {world} ranks")
+    out = torch.empty((gF2.shape[0] // world,) + tuple(gF2.shape[1:]), dtype=gF2.dtype, device=gF2.device)
+    if dist.get_backend(group) == "gloo":   # gloo has no reduce-scatter: all-reduce and keep the own slice
+        full = gF2.contiguous().clone()
+        dist.all_reduce(full, op=dist.ReduceOp.SUM, group=group)
+        r = dist.get_rank(group)
+        out.copy_(full[r * out.shape[0]:(r + 1) * out.shape[0]])
+        return out
+    dist.reduce_scatter_tensor(out, gF2.contiguous(), op=dist.ReduceOp.SUM, group=group)
+    return out
+
+
 def reduce_parameter_grads(params: Iterable[torch.nn.Parameter], group=None) -> Optional[torch.Tensor]:
     """Sum the gradients of the shared attention parameters over all ranks with ONE flat all-reduce
     (a few hundred floats: latency-bound, so one message).  Returns the flat buffer.
