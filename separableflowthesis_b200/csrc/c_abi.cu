@@ -101,6 +101,30 @@ int make_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, 
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+}  // namespace
+
+namespace sfb {
+cudaError_t encode_plain_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims,
+                             const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr || bind_context() != SFB_OK) return cudaErrorNotSupported;
+  cuuint64_t gdim[5], gstride[5];
+  cuuint32_t bdim[5], estride[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estride[i] = 1;
+    if (i < rank - 1) gstride[i] = strides_bytes[i];
+  }
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride, bdim,
+                        estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+}  // namespace sfb
+
+namespace {
+
 // ---- optional per-kernel timing (off by default): CUDA events around each launch on its own stream ----
 enum KernelId : int {
   KID_PREPARE = 0, KID_PACK, KID_SWEEP_MAXAVG, KID_SWEEP_COMPRESS, KID_SWEEP_DUMP, KID_GRAD_MAXAVG_IMG1, KID_GRAD_MAXAVG_IMG2,
@@ -1024,9 +1048,9 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
   SFB_CUDA(timed(KID_ATTENTION_FWD, 2 * ((K + 3) / 4), st, [&] {
     launch_attention_forward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u + (size_t)c0 * d.W2 * N1, sb_u, weight_u,
-                             bias_u, A_u, st);
+                             bias_u, A_u, st, w.status);
     return launch_attention_forward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v + (size_t)c0 * d.H2 * N1, sb_v,
-                                    weight_v, bias_v, A_v, st);
+                                    weight_v, bias_v, A_v, st, w.status);
   }));
   // C_u (per u, weights A_u per v) -> SEP_v channels 2.., C_v -> SEP_u channels 2..
   return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(A_v, K, d.H2, N1), cf_view(A_u, K, d.W2, N1), 0, 0, 1,
@@ -1099,9 +1123,9 @@ static int level_backward(Placement pl, const float* F1, const float* F2, int fm
   SFB_CUDA(timed(KID_ATTENTION_BWD, 2 * attention_backward_launches(K), st, [&] {
     const size_t ou = (size_t)c0 * d.W2 * N1, ov = (size_t)c0 * d.H2 * N1;  // first channel of this level
     launch_attention_backward(AttentionDims{d.B, K, d.W2, d.H1, d.W1}, SEP_u + ou, sb_u, weight_u, A_u, w.ga_u,
-                              gSEP_u + ou, sb_u, w.gm_u, gweight_u, gbias_u, w.at_partial, st);
+                              gSEP_u + ou, sb_u, w.gm_u, gweight_u, gbias_u, w.at_partial, st, w.status);
     return launch_attention_backward(AttentionDims{d.B, K, d.H2, d.H1, d.W1}, SEP_v + ov, sb_v, weight_v, A_v, w.ga_v,
-                                     gSEP_v + ov, sb_v, w.gm_v, gweight_v, gbias_v, w.at_partial, st);
+                                     gSEP_v + ov, sb_v, w.gm_v, gweight_v, gbias_v, w.at_partial, st, w.status);
   }));
   return run_fused_feature_grads_cf(d, w, AM_u, AM_v, w.gm_v, w.gm_u, A_u, A_v, gSEP_v, gSEP_u, Kt, c0 + 2, gF1, gF2, st,
                                     fmaps, fmaps ? scale1 : 1.f);

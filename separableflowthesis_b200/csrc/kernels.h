@@ -173,15 +173,23 @@ cudaError_t launch_grad_gemm(const GradArgs& a, const CUtensorMap& tm_y, const C
 struct AttentionDims {
   int B, Kc, D, H1, W1;
 };
+// `status` (optional): a device status word for bounded waits.  With it, and when W1 is a multiple of 4 and x is
+// 16-byte aligned, the kernels fetch their pixel tiles (with the stencil's halo, zero-filled outside the image) by
+// TMA; otherwise every thread gathers its own neighbourhood.
 cudaError_t launch_attention_forward(const AttentionDims& d, const float* x, long long x_sb, const float* weight,
-                                     const float* bias, float* a, cudaStream_t stream);
+                                     const float* bias, float* a, cudaStream_t stream, int* status = nullptr);
+// Tiled fp32 tensor map without swizzle, zero fill out of bounds; dims / box innermost first, `strides_bytes` for
+// dimensions 1 .. rank-1.  Implemented next to the other tensor maps (c_abi.cu).
+cudaError_t encode_plain_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims,
+                             const uint64_t* strides_bytes, const uint32_t* box);
 // Floats of scratch the backward needs for its per-block partial sums.
 size_t attention_partial_floats(const AttentionDims& d);
 // Backward: `g` holds dLoss/dA on entry and the logit gradients on return; gx (B, 2, D, H1, W1) = add + dLoss/dX
 // where `add` (same shape, `add_sb` elements between samples) may be null; gweight (Kc, 2, 3, 3, 3), gbias (Kc).
 cudaError_t launch_attention_backward(const AttentionDims& d, const float* x, long long x_sb, const float* weight,
                                       const float* a, float* g, const float* add, long long add_sb, float* gx,
-                                      float* gweight, float* gbias, float* partial, cudaStream_t stream);
+                                      float* gweight, float* gbias, float* partial, cudaStream_t stream,
+                                      int* status = nullptr);
 
 
 // Linear resampling along the displacement axis (core/corr.py:459-467: trilinear interpolate with unchanged H1, W1):
