@@ -548,21 +548,23 @@ attention_weight_grad_kernel(const float* __restrict__ x, long long x_sb, const 
   }
 }
 
-// out[i] = sum over rows of partial[row][i], rows added in order.  One thread per column.
-__global__ void attention_reduce_partials_kernel(const float* __restrict__ partial, int rows, int cols,
-                                                 float* __restrict__ out) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= cols) return;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int r = 0;
-  for (; r + 4 <= rows; r += 4) {
-    s0 += __ldg(partial + (size_t)r * cols + i);
-    s1 += __ldg(partial + (size_t)(r + 1) * cols + i);
-    s2 += __ldg(partial + (size_t)(r + 2) * cols + i);
-    s3 += __ldg(partial + (size_t)(r + 3) * cols + i);
+// out[i] = sum over rows of partial[row][i].  One block per column: thread t adds rows t, t + 256, ... in order, then
+// the 256 partial sums are combined in a fixed tree, so the result does not depend on scheduling (bit-reproducible).
+constexpr int RP_THREADS = 256;
+__global__ void __launch_bounds__(RP_THREADS)
+attention_reduce_partials_kernel(const float* __restrict__ partial, int rows, int cols, float* __restrict__ out) {
+  __shared__ float red[RP_THREADS];
+  const int i = blockIdx.x;
+  float s = 0.f;
+  for (int r = threadIdx.x; r < rows; r += RP_THREADS) s += __ldg(partial + (size_t)r * cols + i);
+  red[threadIdx.x] = s;
+  __syncthreads();
+#pragma unroll
+  for (int o = RP_THREADS / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
   }
-  for (; r < rows; ++r) s0 += __ldg(partial + (size_t)r * cols + i);
-  out[i] = (s0 + s1) + (s2 + s3);
+  if (threadIdx.x == 0) out[i] = red[0];
 }
 
 // ---- input and weight gradients, pixel tiles fetched by TMA -------------------------------------------------
@@ -913,8 +915,8 @@ cudaError_t launch_attention_backward(const AttentionDims& d, const float* x, lo
 #undef SFB_AT_WG
   }
   const int wcols = d.Kc * 2 * AT_TAPS;
-  attention_reduce_partials_kernel<<<(wcols + 63) / 64, 64, 0, st>>>(weight_partial, wrows, wcols, gweight);
-  attention_reduce_partials_kernel<<<(d.Kc + 63) / 64, 64, 0, st>>>(bias_partial, rows, d.Kc, gbias);
+  attention_reduce_partials_kernel<<<wcols, RP_THREADS, 0, st>>>(weight_partial, wrows, wcols, gweight);
+  attention_reduce_partials_kernel<<<d.Kc, RP_THREADS, 0, st>>>(bias_partial, rows, d.Kc, gbias);
   return cudaGetLastError();
 }
 
