@@ -435,7 +435,7 @@ def run_lookup4d_bench(args, cfg, device, emit):
 def run_reference_cuda(args, cfg, metric, unit, emit):
     """`--impl reference-cuda`: the five ops of the reference's own CUDA extension (oracle/_ref/MemorySaver.so, built
     unmodified from libs/MemorySaver/src) on one GPU, and this library's five ops on the same tensors, in the
-    reference's layouts with random softmaxed attention weights (the op sequence of the survey's metric).  One
+    reference's layouts with random softmaxed attention weights (the op sequence the metric is defined on).  One
     line per implementation.  The reference needs seconds per step, so it runs `steps` capped at 3."""
     import importlib.util
     so = os.path.join(ROOT, "oracle", "_ref", "MemorySaver.so")
@@ -822,7 +822,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"],
-                    help="reference: the CPU port of the reference's dense path (the driver's reference arm); "
+                    help="reference: the CPU port of the reference's dense path (the reference arm of the benchmark contract); "
                          "reference-cuda: the reference's own CUDA extension built by oracle/build_ref_cuda.py, timed on "
                          "the five ops next to this library's five ops (configs with Kc = 2 only: the reference's forward "
                          "kernel is compiled for two attention channels, MemorySaver_kernel_forward.cu:20)")
