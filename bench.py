@@ -735,9 +735,9 @@ def extra_config4_bf16(ms, device, args):
     ref_u = torch.stack((S.max(3).values, S.mean(3)), 1).permute(0, 1, 4, 2, 3)   # (1, 2, W2, rows, W1)
     err = max(((sep_v[:1, :2, :, r0:r1] - ref_v).abs().max() / ref_v.abs().max()).item(),
               ((sep_u[:1, :2, :, r0:r1] - ref_u).abs().max() / ref_u.abs().max()).item())
-    return {"workload": cfg["name"].replace("(fp32 operands)", "(bf16 operands in the sweeps)"),
+    return {"workload": cfg["name"].replace("(fp32 operands)", "(bf16 operands)"),
             "value": job["cells"] / (t * 1e-3), "unit": "cells/s", "ms_per_step": t, "steps": steps,
-            "dtype": "bf16 operands in the sweeps, tf32 in the gradient GEMMs, fp32 accumulate",
+            "dtype": "bf16 operands in the sweeps and the gradient GEMMs, fp32 accumulate",
             "max_rel_err_max_mean_channels_vs_fp32": err, "band": f"sample 0, image-1 rows {r0}..{r1 - 1}"}
 
 
@@ -1089,7 +1089,7 @@ def main():
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": ("tf32 operands (fp32 in HBM), fp32 accumulate" if args.operands == "tf32" else
-                  "bf16 operands in the sweeps, tf32 in the gradient GEMMs (fp32 in HBM), fp32 accumulate"),
+                  "bf16 operands in the sweeps and the gradient GEMMs (fp32 in HBM), fp32 accumulate"),
         "data": "synthetic",
         "config": {"workload": cfg["name"], "path": path, "cells_per_step": total_cells,
                    "flop_per_cell": flops_per_cell(cfg),

@@ -280,13 +280,14 @@ int sfb_lookup4d_backward(const float* F1, const float* const* F2_levels, const 
                           float* const* gF2_levels, int32_t B, int32_t H1, int32_t W1, int32_t C, int32_t radius,
                           float scale, void* stream);
 
-/* Operand type of the correlation sweeps inside the level calls (sfb_separation_level_forward / _backward and their
- * _fmaps forms).  SFB_OPERANDS_TF32 (default): features rounded to TF32.  SFB_OPERANDS_BF16: features rounded to
- * BF16 (round to nearest even), products exact in FP32, FP32 accumulation -- twice the tensor-core rate per
- * instruction at about 8 mantissa bits (needs C % 8 == 0); the gradient GEMMs keep TF32 operands.  The setting is
- * process-wide (a
- * backward runs on another thread than the forward); sfb_set_sweep_operands returns the previous value, or -1 for
- * an unknown one.  All other entry points always use TF32. */
+/* Operand type of every contraction (the correlation sweeps and the gradient GEMMs) of the five ops, their fused and
+ * channels-first forms and the level calls.  SFB_OPERANDS_TF32 (default): features and the generated gradient operand
+ * rounded to TF32.  SFB_OPERANDS_BF16: rounded to BF16 (round to nearest even), products exact in FP32, FP32
+ * accumulation -- twice the tensor-core rate per instruction at about 8 mantissa bits (needs C % 8 == 0).  The
+ * reference computes in FP32 only; this is the operand type BASELINE's bf16 configuration asks for.  The setting
+ * is process-wide (a backward runs on another thread than the forward); sfb_set_sweep_operands returns the
+ * previous value, or -1 for an unknown one.  sfb_max_avg_forward_static, sfb_corr_volume and the lookups always
+ * compute as they do by default. */
 enum { SFB_OPERANDS_TF32 = 0, SFB_OPERANDS_BF16 = 1 };
 int sfb_set_sweep_operands(int operands);
 int sfb_get_sweep_operands(void);

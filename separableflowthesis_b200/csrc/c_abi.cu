@@ -249,13 +249,13 @@ int grad_slots(int kc) { return 2 * kc <= 4 ? 4 : 8; }  // two slots per channel
 
 WsPlan plan_for(int op, const Dims& d) {
   switch (op) {
-    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS, 0, false, false};
-    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc, 0, false, false};
+    case SFB_OP_MAX_AVG_FORWARD: return {true, 0, MAXAVG_SLOTS, 0, false, true};
+    case SFB_OP_COMPRESSION_FORWARD: return {false, d.Kc, d.Kc, 0, false, true};
     case SFB_OP_MAX_ARGMAX_AVG_BACKWARD: return {false, 0, 0, 4, false, false};
-    case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc)), false, false};
-    case SFB_OP_SEPARATION_BACKWARD: return {false, d.Kc, d.Kc, 4 + grad_slots(chunk_channels(d.Kc)), false, false};
-    case SFB_OP_MAX_AVG_FORWARD_CF: return {true, 0, 0, 0, false, false};
-    case SFB_OP_COMPRESSION_CF: return {false, 0, 0, 0, false, false};
+    case SFB_OP_COMPRESSION_BACKWARD: return {false, d.Kc, d.Kc, grad_slots(chunk_channels(d.Kc)), false, true};
+    case SFB_OP_SEPARATION_BACKWARD: return {false, d.Kc, d.Kc, 4 + grad_slots(chunk_channels(d.Kc)), false, true};
+    case SFB_OP_MAX_AVG_FORWARD_CF: return {true, 0, 0, 0, false, true};
+    case SFB_OP_COMPRESSION_CF: return {false, 0, 0, 0, false, true};
     case SFB_OP_SEPARATION_FEATURE_BACKWARD_CF: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc)), false, false};
     case SFB_OP_SEPARATION_LEVEL_FORWARD: return {true, 0, 0, 0, false, true};
     case SFB_OP_SEPARATION_LEVEL_BACKWARD: return {false, 0, 0, 4 + grad_slots(chunk_channels(d.Kc)), true, true};
@@ -391,6 +391,35 @@ int map_aux(CUtensorMap* tm, const Dims& d, const void* aux, bool bf16 = false) 
   return make_map(tm, aux, 3, dims, box, CU_TENSOR_MAP_SWIZZLE_128B, bf16);
 }
 
+// Operand type of this call's contractions: the process-wide switch (sfb_set_sweep_operands).
+int operand_mode(const Dims& d, int* bf16) {
+  *bf16 = g_sweep_operands.load() == 1 ? 1 : 0;
+  if (*bf16 && d.C % 8 != 0)
+    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "BF16 operands need a feature dimension that is a multiple of 8 (C=%d)", d.C);
+  return SFB_OK;
+}
+
+// Tensor maps of the sweeps' operands in a workspace: the rounded FP32 copies or their BF16 copies (aux may be null).
+int map_sweep_operands(const Dims& d, const Workspace& w, int bf16, CUtensorMap* f1, CUtensorMap* f2, CUtensorMap* aux) {
+  if (bf16) {
+    SFB_TRY(map_f1_rows(f1, d, w.F1h, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, true));
+    SFB_TRY(map_f2_tile(f2, d, w.F2h, SWEEP_UT, SWEEP_VT, CU_TENSOR_MAP_SWIZZLE_128B, true));
+    if (aux != nullptr) SFB_TRY(map_aux(aux, d, w.auxh, true));
+  } else {
+    SFB_TRY(map_f1_rows(f1, d, w.F1r, TILE_M));
+    SFB_TRY(map_f2_tile(f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+    if (aux != nullptr) SFB_TRY(map_aux(aux, d, w.aux));
+  }
+  return SFB_OK;
+}
+
+// Rounded copies of a call's features (and of the mean rows of image 2 when with_aux), plus BF16 copies when bf16.
+cudaError_t prepare_operands(const Dims& d, const Workspace& w, const float* F1, const float* F2, bool with_aux,
+                             int bf16, cudaStream_t st) {
+  return launch_prepare(d, F1, F2, w.F1r, w.F2r, with_aux ? w.aux : nullptr, w.status, st, bf16 ? w.F1h : nullptr,
+                        bf16 ? w.F2h : nullptr, bf16 && with_aux ? w.auxh : nullptr);
+}
+
 int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u, int32_t* AM_v,
                        bool with_argmax, const sfb_shape* shape, void* ws, size_t ws_bytes, void* stream) {
   Dims d;
@@ -400,14 +429,15 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   Workspace w;
   SFB_TRY(check_workspace(d, ws, ws_bytes, SFB_OP_MAX_AVG_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
   CUtensorMap tm_f1, tm_f2, tm_aux;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_TRY(map_aux(&tm_aux, d, w.aux));
-  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st); }));
+  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, &tm_aux));
+  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return prepare_operands(d, w, F1, F2, true, bf16, st); }));
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
+  a.bf16 = bf16;
   a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
   a.n_valid = w.n1p;
   a.pu = packed_view(w.ou, d.H2, MAXAVG_SLOTS, w.n1p);
@@ -456,6 +486,9 @@ int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, co
 // out_cf: the gradients are written channel-major, (B, C, pixels), gF1 multiplied by scale1.
 int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accumulate, float* gF1, float* gF2,
                   cudaStream_t st, int out_cf = 0, float scale1 = 1.f) {
+  // BF16 form when the operand switch says so and the feature dimension allows it (callers that sweep have already
+  // refused other shapes)
+  const int bf16 = (g_sweep_operands.load() == 1 && d.C % 8 == 0) ? 1 : 0;
   CUtensorMap tm_y, tm_xu, tm_xv;
   GradArgs a;
   memset(&a, 0, sizeof(a));
@@ -467,25 +500,28 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   a.xu = w.gxu;
   a.xv = w.gxv;
   a.status = w.status;
+  a.bf16 = bf16;
   const int Q = R4 / 4;
   const int kid = mode == GRAD_MAXAVG ? KID_GRAD_MAXAVG_IMG1 : (mode == GRAD_COMPRESS ? KID_GRAD_COMPRESS_IMG1 : KID_GRAD_FUSED_IMG1);
   // K-major B operands: channel-major copies of the rounded features (image 2 in column blocks of 16 with an even
   // number of rows, so that a 2 x 16 block of the image is 32 consecutive values).  Rows and columns of padding must
   // read as zero: they meet the G values of cells outside the image.
   const uint32_t crows = (uint32_t)((d.C + KBLK - 1) / KBLK * KBLK);  // channel rows of one feature block
+  // a row of 32 K-values is 128 bytes of FP32 or 64 bytes of BF16: the swizzle span follows
+  const CUtensorMapSwizzle fswz = bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   const size_t f2t_per_sample = (size_t)d.C * ((d.W2 + GG_VT - 1) / GG_VT) * w.h2p * GG_VT;
   if (!accumulate) {  // later passes over further channel chunks reuse the copies of the first
     SFB_CUDA(timed(KID_PREPARE, 2, st, [&] {
-      cudaMemsetAsync(w.F2t, 0, (size_t)d.B * f2t_per_sample * sizeof(float), st);
-      launch_channel_major(w.F1r, w.F1t, d.B, 1, d.N1(), w.n1p, d.C, 0, st);
-      return launch_channel_major(w.F2r, w.F2t, d.B, d.H2, d.W2, w.h2p, d.C, 1, st);
+      cudaMemsetAsync(w.F2t, 0, (size_t)d.B * f2t_per_sample * (bf16 ? 2 : sizeof(float)), st);
+      launch_channel_major(w.F1r, w.F1t, d.B, 1, d.N1(), w.n1p, d.C, 0, bf16, st);
+      return launch_channel_major(w.F2r, w.F2t, d.B, d.H2, d.W2, w.h2p, d.C, 1, bf16, st);
     }));
   }
   // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2 and 2-row blocks of XU.
   {  // (blocked pixels, C, B); box = 32 consecutive values (2 rows x 16 columns) x all channels
     const uint64_t dims[3] = {(uint64_t)(f2t_per_sample / d.C), (uint64_t)d.C, (uint64_t)d.B};
     const uint32_t box[3] = {GG_KJ, crows, 1};
-    SFB_TRY(make_map(&tm_y, w.F2t, 3, dims, box));
+    SFB_TRY(make_map(&tm_y, w.F2t, 3, dims, box, fswz, bf16 != 0));
   }
   SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, TILE_M / 2, GG_UT));  // two 64-pixel boxes per block
   a.out_cf = out_cf;
@@ -497,7 +533,7 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   {  // (N1, C, B) with rows padded to n1p; box = 32 pixels x all channels
     const uint64_t dims[3] = {(uint64_t)d.N1(), (uint64_t)d.C, (uint64_t)d.B};
     const uint32_t box[3] = {GG_KJ, crows, 1};
-    SFB_TRY(make_map(&tm_y, w.F1t, 3, dims, box, CU_TENSOR_MAP_SWIZZLE_128B, false, (uint64_t)w.n1p));
+    SFB_TRY(make_map(&tm_y, w.F1t, 3, dims, box, fswz, bf16 != 0, (uint64_t)w.n1p));
   }
   SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, GG_KJ, GG_ROW_UT));
   SFB_TRY(map_operands(&tm_xv, w.gxv, d.B, d.W2, Q, w.n1p, GG_KJ, GG_ROW_VT));
@@ -543,17 +579,16 @@ void compress_slot_sources(int K, int k0, int kc, const float* A_u, const float*
 // gA_u[p,k,v] = sum_u S * gC_u[p,k,u] -- the forward compression sweep with the upstream gradients in the
 // role of the weights (w_u = gC_v, w_v = gC_u).
 int run_attention_grads(const Dims& d, const Workspace& w, const float* gC_u, const float* gC_v, float* gA_u,
-                        float* gA_v, cudaStream_t st) {
+                        float* gA_v, cudaStream_t st, int bf16) {
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
+  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, nullptr));
   const int N1 = d.N1(), K = d.Kc;
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_pack(gC_v, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);
     return launch_pack(gC_u, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);
   }));
   SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, packed_view(w.xu, d.H2, K, w.n1p), packed_view(w.xv, d.W2, K, w.n1p),
-                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st));
+                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st, bf16));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_unpack(w.ou, gA_v, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
     return launch_unpack(w.ov, gA_u, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
@@ -611,14 +646,16 @@ int sfb_max_avg_forward_static(const float* F1, const float* F2, float* MA_u, fl
   Dims d;
   SFB_TRY(check_shape(shape, false, &d));
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(MA_u); SFB_CHECK_PTR(MA_v);
-  const size_t need = carve(d, nullptr, plan_for(SFB_OP_MAX_AVG_FORWARD, d)).bytes;
+  WsPlan plan = plan_for(SFB_OP_MAX_AVG_FORWARD, d);
+  plan.bf16 = false;  // this entry point always computes with TF32 operands: no room is set aside for BF16 copies
+  const size_t need = carve(d, nullptr, plan).bytes;
   if (need > STATIC_SCRATCH_BYTES)
     return fail(SFB_ERR_UNSUPPORTED_SHAPE,
                 "this shape needs %zu bytes of scratch but the built-in scratch holds %zu; use sfb_max_avg_forward "
                 "with a caller-provided workspace", need, (size_t)STATIC_SCRATCH_BYTES);
   void* scratch = nullptr;
   SFB_TRY(static_scratch(&scratch));
-  const Workspace w = carve(d, scratch, plan_for(SFB_OP_MAX_AVG_FORWARD, d));
+  const Workspace w = carve(d, scratch, plan);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap tm_f1, tm_f2, tm_aux;
   SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
@@ -664,17 +701,18 @@ int sfb_compression_forward(const float* F1, const float* F2, const float* A_u, 
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, nullptr));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
   const int N1 = d.N1(), K = d.Kc;
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_pack(A_u, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);         // w_u[k][v] = XV slot k
     return launch_pack(A_v, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);  // w_v[k][u] = XU slot k
   }));
   SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, packed_view(w.xu, d.H2, K, w.n1p), packed_view(w.xv, d.W2, K, w.n1p),
-                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st));
+                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st, bf16));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_unpack(w.ou, C_u, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
     return launch_unpack(w.ov, C_v, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
@@ -692,7 +730,9 @@ int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t*
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_MAX_ARGMAX_AVG_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     SlotSources su, sv;
     maxavg_slot_sources(d, AM_u, AM_v, gMA_u, gMA_v, &su, &sv);
@@ -713,9 +753,11 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
   const int N1 = d.N1(), K = d.Kc;
-  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st));
+  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, bf16));
   // gradient GEMMs, at most KC_MAX_PER_SWEEP channels per pass; later passes add to gF1 / gF2.
   for (int k0 = 0; k0 < K; k0 += KC_MAX_PER_SWEEP) {
     const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
@@ -739,8 +781,10 @@ int sfb_compression_attention_backward(const float* F1, const float* F2, const f
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
-  return run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st);
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  return run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, bf16);
 }
 
 // Feature gradients of both backward ops from one GEMM pair (plus accumulated passes for channels beyond
@@ -786,7 +830,9 @@ int sfb_separation_feature_backward(const float* F1, const float* F2, const int3
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
   return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
 }
 
@@ -803,8 +849,10 @@ int sfb_separation_backward(const float* F1, const float* F2, const int32_t* AM_
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
-  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st));
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, bf16));
   return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
 }
 
@@ -819,15 +867,16 @@ int sfb_max_argmax_avg_forward_cf(const float* F1, const float* F2, float* SEP_v
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_MAX_AVG_FORWARD_CF, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
   CUtensorMap tm_f1, tm_f2, tm_aux;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_TRY(map_aux(&tm_aux, d, w.aux));
-  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st); }));
+  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, &tm_aux));
+  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return prepare_operands(d, w, F1, F2, true, bf16, st); }));
   const int N1 = d.N1();
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
+  a.bf16 = bf16;
   a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
   a.n_valid = N1;
   a.pu = cf_view(SEP_v, 2, d.H2, N1);       // per-u channels live in the tensor the call site calls sep_v
@@ -849,14 +898,15 @@ static int run_compress_cf(const float* F1, const float* F2, const float* W_u, c
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_CF, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, nullptr));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
   const int N1 = d.N1(), K = d.Kc;
   // W_u (B,K,W2,N1) weights per v, W_v (B,K,H2,N1) per u; O_u (B,K,H2,N1), O_v (B,K,W2,N1)
   return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(W_v, K, d.H2, N1), cf_view(W_u, K, d.W2, N1), 0, 0, 1,
-                             cf_view(O_u, K, d.H2, N1), cf_view(O_v, K, d.W2, N1), N1, st);
+                             cf_view(O_u, K, d.H2, N1), cf_view(O_v, K, d.W2, N1), N1, st, bf16);
 }
 
 int sfb_compression_forward_cf(const float* F1, const float* F2, const float* A_u, const float* A_v, float* C_u,
@@ -918,7 +968,9 @@ int sfb_separation_feature_backward_cf(const float* F1, const float* F2, const i
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_FEATURE_BACKWARD_CF, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
   return run_fused_feature_grads_cf(d, w, AM_u, AM_v, gSEP_v, gSEP_u, A_u, A_v, gC_u, gC_v, d.Kc, 0, gF1, gF2, st);
 }
 
@@ -1321,10 +1373,11 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_CORR_VOLUME, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int bf16;
+  SFB_TRY(operand_mode(d, &bf16));
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-  SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st); }));
+  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, nullptr));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;

@@ -108,6 +108,7 @@ struct GradArgs {
   int accumulate;        // 0: out = result, 1: out += result (later channel chunks of the compression op)
   int out_cf;            // 0: out is (B, pixels, C); 1: out is (B, C, pixels), the layout of the model's feature maps
   float out_scale;       // the result is multiplied by this before it is stored / added (out_cf only)
+  int bf16;              // G and the feature copies are BF16 (tcgen05.mma kind::f16) instead of TF32
   const float* xu;
   const float* xv;
   float* out;            // gF1 (B,N1,C) or gF2 (B,N2,C)
@@ -147,11 +148,12 @@ cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, floa
 cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
                               float* F2r, float* aux, int* status, cudaStream_t stream, uint16_t* F1h = nullptr,
                               uint16_t* F2h = nullptr, uint16_t* auxh = nullptr);
-// Channel-major copy of a (rounded) pixel-major feature array (B, rows*width, C); padding is not written.
+// Channel-major copy of a (rounded) pixel-major feature array (B, rows*width, C), as FP32 or (bf16 != 0) rounded to
+// BF16; padding is not written.
 //   blocked = 0: dst (B, C, pitch) with pixel index row*width + x (rows = 1)
 //   blocked = 1: dst (B, C, ceil(width/16), pitch, 16), element (row, x) at ((x/16)*pitch + row)*16 + x%16
-cudaError_t launch_channel_major(const float* src, float* dst, int B, int rows, int width, int pitch, int C,
-                                 int blocked, cudaStream_t stream);
+cudaError_t launch_channel_major(const float* src, void* dst, int B, int rows, int width, int pitch, int C,
+                                 int blocked, int bf16, cudaStream_t stream);
 // Pack: dst[b][d][r0 + k*rstride][p] = scale * src[b][p][ksrc0 + k][d] for k < K (raw 32-bit copy when
 // scale == 0), zero for N1 <= p < n1p.  src is (B, N1, Ksrc, D), dst is (B, D, R, n1p).
 cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,

@@ -247,7 +247,8 @@ __global__ void transpose_round_kernel(const float* __restrict__ in, float* __re
 //                K block of the image-1-major GEMM are 32 consecutive values (image 2: pitch = H2 rounded up to even)
 // Padding is not written (the caller clears the array).  32 x 32 tiles through shared memory; grid (ceil(width/32),
 // ceil(C/32), B*rows), block (32, 8).
-__global__ void channel_major_kernel(const float* __restrict__ in, float* __restrict__ out, int rows, int width,
+template <typename T>
+__global__ void channel_major_kernel(const float* __restrict__ in, T* __restrict__ out, int rows, int width,
                                      int pitch, int C, int blocked) {
   __shared__ float tile[32][33];
   const int b = blockIdx.z / rows, row = blockIdx.z - b * rows, x0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
@@ -265,15 +266,19 @@ __global__ void channel_major_kernel(const float* __restrict__ in, float* __rest
     const int c = c0 + j, x = x0 + tx;
     if (c < C && x < width) {
       const size_t off = blocked ? ((size_t)(x >> 4) * pitch + row) * 16 + (x & 15) : (size_t)x;
-      out[((size_t)b * C + c) * per_channel + off] = tile[tx][j];
+      if constexpr (sizeof(T) == 2) out[((size_t)b * C + c) * per_channel + off] = __float2bfloat16_rn(tile[tx][j]);
+      else out[((size_t)b * C + c) * per_channel + off] = tile[tx][j];
     }
   }
 }
 
-cudaError_t launch_channel_major(const float* src, float* dst, int B, int rows, int width, int pitch, int C,
-                                 int blocked, cudaStream_t stream) {
+cudaError_t launch_channel_major(const float* src, void* dst, int B, int rows, int width, int pitch, int C,
+                                 int blocked, int bf16, cudaStream_t stream) {
   const dim3 grid((width + 31) / 32, (C + 31) / 32, B * rows), block(32, 8);
-  channel_major_kernel<<<grid, block, 0, stream>>>(src, dst, rows, width, pitch, C, blocked);
+  if (bf16)
+    channel_major_kernel<<<grid, block, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), rows, width, pitch, C, blocked);
+  else
+    channel_major_kernel<<<grid, block, 0, stream>>>(src, static_cast<float*>(dst), rows, width, pitch, C, blocked);
   return cudaGetLastError();
 }
 

@@ -584,8 +584,8 @@ def lookup_backward(corr_shape, coord, grad_out, levels=4, radius=4, clamp_unit=
 
 
 class sweep_operands:
-    """Context manager / setter for the operand type of the correlation sweeps inside the level calls:
-    ``with ops.sweep_operands("bf16"): ...`` (process-wide; "tf32" is the default)."""
+    """Context manager / setter for the operand type of every contraction (correlation sweeps and gradient GEMMs) of
+    the ops and the level calls: ``with ops.sweep_operands("bf16"): ...`` (process-wide; "tf32" is the default)."""
     _codes = {"tf32": 0, "bf16": 1}
 
     def __init__(self, kind: str):

@@ -130,3 +130,42 @@ def test_lookup_radius_beyond_register_window(cuda_device):
         gc = ops.lookup_backward(tuple(corr.shape), c.to(dev), gout.to(dev), levels, radius, clamp)
         rg = orc.lookup_backward(tuple(corr.shape), c.double(), gout.double(), levels, radius, clamp)
         assert relerr(gc.cpu(), rg) < 5e-5
+
+
+@pytest.mark.parametrize("shape", [(2, 47, 156, 47, 156, 256, 2), (1, 13, 22, 11, 19, 64, 3)])
+def test_five_ops_with_bf16_operands(shape, cuda_device):
+    """The five reference-layout ops (MemorySaver_cuda.cpp:105-112) with BF16 operands in every contraction (BASELINE
+    config 4's operand type), at its image size and on a ragged small case.  Forward ops against the oracle on
+    BF16-rounded features (max channel: exact products, 2e-5; sums 4e-3); backward ops, whose generated operand is
+    rounded to BF16 as well, against the unrounded oracle with 1e-2."""
+    no_tf32()
+    B, H1, W1, H2, W2, C, Kc = shape
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(601)
+    F1 = torch.randn(B, H1, W1, C, generator=g, device=dev) / C ** 0.5
+    F2 = torch.randn(B, H2, W2, C, generator=g, device=dev)
+    A_u = torch.softmax(torch.randn(B, H1, W1, Kc, W2, generator=g, device=dev), -1)
+    A_v = torch.softmax(torch.randn(B, H1, W1, Kc, H2, generator=g, device=dev), -1)
+    gMA_u = torch.randn(B, H1, W1, 2, H2, generator=g, device=dev)
+    gMA_v = torch.randn(B, H1, W1, 2, W2, generator=g, device=dev)
+    gC_u = torch.randn(B, H1, W1, Kc, H2, generator=g, device=dev)
+    gC_v = torch.randn(B, H1, W1, Kc, W2, generator=g, device=dev)
+    with ops.sweep_operands("bf16"):
+        MA_u, MA_v, AM_u, AM_v = ops.max_argmax_avg_forward(F1, F2)
+        MA_u2, MA_v2 = ops.max_avg_forward(F1, F2)
+        C_u, C_v = ops.compression_forward(F1, F2, A_u, A_v)
+        gF1m, gF2m = ops.max_argmax_avg_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v)
+        gF1c, gF2c, gA_u, gA_v = ops.compression_backward(F1, F2, A_u, A_v, gC_u, gC_v)
+    F1b, F2b = F1.bfloat16().float(), F2.bfloat16().float()
+    rMA_u, rMA_v, rAM_u, rAM_v = orc.max_argmax_avg_forward(F1b, F2b)
+    assert torch.equal(MA_u, MA_u2) and torch.equal(MA_v, MA_v2)
+    assert relerr(MA_u[..., 0, :], rMA_u[..., 0, :]) < 2e-5 and relerr(MA_v[..., 0, :], rMA_v[..., 0, :]) < 2e-5
+    assert relerr(MA_u, rMA_u) < 4e-3 and relerr(MA_v, rMA_v) < 4e-3
+    assert (AM_u == rAM_u).float().mean().item() > 0.99 and (AM_v == rAM_v).float().mean().item() > 0.99
+    rC_u, rC_v = orc.compression_forward(F1b, F2b, A_u, A_v)
+    assert relerr(C_u, rC_u) < 4e-3 and relerr(C_v, rC_v) < 4e-3
+    r1, r2 = orc.max_argmax_avg_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v)
+    assert relerr(gF1m, r1) < 1e-2 and relerr(gF2m, r2) < 1e-2
+    rc = orc.compression_backward(F1, F2, A_u, A_v, gC_u, gC_v)
+    for name, x, r in zip(("gF1", "gF2", "gA_u", "gA_v"), (gF1c, gF2c, gA_u, gA_v), rc):
+        assert relerr(x, r) < 1e-2, name
