@@ -481,7 +481,7 @@ def run_reference_cuda(args, cfg, metric, unit, emit):
         ms = e0.elapsed_time(e1) / steps
         emit({"impl": name, "metric": metric, "value": cells / (ms * 1e-3), "unit": unit, "n_gpus": 1, "steps": steps,
               "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-              "dtype": "f32" if name != "ours" else "tf32 operands, fp32 accumulate", "data": "synthetic",
+              "dtype": "f32" if name != "ours" else DTYPE_TEXT["fp16"], "data": "synthetic",
               "config": {"workload": cfg["name"], "path": "the five ops in the reference's layouts, device-resident"}})
 
 
@@ -662,13 +662,21 @@ def time_cpu(cfg, budget_s, steps=None, warmup=1):
 
 
 # --------------------------------------------------------------------------------------- main
-def measure_tf32_peak(device):
-    """cuBLAS TF32 GEMM 8192^3 through torch.matmul, best of 10 (burst) and back to back for ~1 s."""
+OPERAND_CODES = {"tf32": 0, "bf16": 1, "fp16": 2}
+DTYPE_TEXT = {
+    "fp16": "fp16 operands (10 mantissa bits like TF32; per-tensor power-of-two scaling; fp32 in HBM), fp32 accumulate",
+    "tf32": "tf32 operands (fp32 in HBM), fp32 accumulate",
+    "bf16": "bf16 operands in the sweeps and the gradient GEMMs (fp32 in HBM), fp32 accumulate",
+}
+
+
+def measure_tf32_peak(device, dtype=torch.float32):
+    """cuBLAS GEMM 8192^3 through torch.matmul (TF32 for float32 inputs), best of 10 (burst) and back to back for ~1 s."""
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = True
     n = 8192
-    a = torch.randn(n, n, device=device)
-    b = torch.randn(n, n, device=device)
+    a = torch.randn(n, n, device=device).to(dtype)
+    b = torch.randn(n, n, device=device).to(dtype)
     for _ in range(3):
         a @ b
     best = float("inf")
@@ -739,6 +747,30 @@ def extra_config4_bf16(ms, device, args):
             "value": job["cells"] / (t * 1e-3), "unit": "cells/s", "ms_per_step": t, "steps": steps,
             "dtype": "bf16 operands in the sweeps and the gradient GEMMs, fp32 accumulate",
             "max_rel_err_max_mean_channels_vs_fp32": err, "band": f"sample 0, image-1 rows {r0}..{r1 - 1}"}
+
+
+def extra_tf32_operands(ms, cfg, job, args):
+    """The same job with TF32 operands (sfb_set_sweep_operands(TF32)): the operand type of the same precision at half
+    the tensor-core rate, for comparison with the headline."""
+    from separableflowthesis_b200 import _lib
+    lib = _lib.load()
+    prev = lib.sfb_set_sweep_operands(OPERAND_CODES["tf32"])
+    try:
+        for _ in range(3):
+            run_level(ms, cfg, job)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = max(5, args.steps)
+        e0.record()
+        for _ in range(steps):
+            run_level(ms, cfg, job)
+        e1.record()
+        torch.cuda.synchronize()
+    finally:
+        lib.sfb_set_sweep_operands(prev)
+    t = e0.elapsed_time(e1) / steps
+    return {"dtype": DTYPE_TEXT["tf32"], "value": job["cells"] / (t * 1e-3), "unit": "cells/s", "ms_per_step": t,
+            "steps": steps}
 
 
 def extra_reference_cuda(args):
@@ -846,9 +878,10 @@ def main():
                     help="batch: samples first, image-1 rows for what is left (no data-path exchange when the batch "
                          "is a multiple of the GPUs); rows: every rank gets all samples and a block of image-1 rows "
                          "plus a halo row per side, gF2 is summed and halo-row gradients exchanged over NCCL")
-    ap.add_argument("--operands", default="tf32", choices=["tf32", "bf16"],
-                    help="operand type of the correlation sweeps of the level calls (bf16: BASELINE's bf16 configuration; "
-                         "lower precision than the default, so not the headline)")
+    ap.add_argument("--operands", default="fp16", choices=["fp16", "tf32", "bf16"],
+                    help="operand type of every contraction: fp16 (the library's default: TF32's 10 mantissa bits at "
+                         "twice its tensor-core rate, per-tensor power-of-two scaling), tf32, or bf16 (BASELINE's bf16 "
+                         "configuration; lower precision, so not the headline)")
     ap.add_argument("--levels", type=int, default=1,
                     help="pyramid levels of the end-to-end block (the metric counts level-0 cells; the reference's "
                          "model uses 4 levels = 1.33x the cells)")
@@ -910,10 +943,7 @@ def main():
     if path == "level" and cfg["Kc"] == 0:
         raise SystemExit("--path level needs attention channels")
     job = make_job(cfg, shard, device, path)
-    if args.operands == "bf16":
-        if path != "level":
-            raise SystemExit("--operands bf16 applies to the level calls (--path level)")
-        _lib.load().sfb_set_sweep_operands(1)
+    _lib.load().sfb_set_sweep_operands(OPERAND_CODES[args.operands])
 
     def barrier():
         if world > 1:
@@ -991,10 +1021,14 @@ def main():
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except OSError:
             pass
-        # MEASURED_PEAKS.json has dense BF16 only; TF32 runs at half its rate on the tensor cores.  The kernels are
-        # timed inside back-to-back steps under the power cap, so the sustained figure is the denominator.
-        file_sust = 0.5 * float(peaks["bf16_tflops_sustained"]) if "bf16_tflops_sustained" in peaks else None
-        file_burst = 0.5 * float(peaks["bf16_tflops"]) if "bf16_tflops" in peaks else None
+        # MEASURED_PEAKS.json has the dense BF16 rate (the kind::f16 pipe, which FP16 operands use as well); TF32 runs
+        # at half of it.  The kernels are timed inside back-to-back steps under the power cap, so the sustained figure
+        # is the denominator: the full one for 16-bit operands, half of it for TF32 operands.
+        op16 = args.operands != "tf32"
+        f16_sust = float(peaks["bf16_tflops_sustained"]) if "bf16_tflops_sustained" in peaks else None
+        f16_burst = float(peaks["bf16_tflops"]) if "bf16_tflops" in peaks else None
+        file_sust = (f16_sust if op16 else 0.5 * f16_sust) if f16_sust else None
+        f16c_burst, f16c_sust = measure_tf32_peak(device, torch.float16) if op16 else (None, None)
         fl = 2.0 * C_FEAT * job["cells"]            # one contraction over this rank's cells per launch
         per_kernel = []
         for name, t, l in report:
@@ -1002,24 +1036,34 @@ def main():
                 continue
             ach = fl / (t / l * 1e-3) / 1e12
             per_kernel.append({"kernel": name, "ms_per_launch": t / l, "share": t / tot, "achieved": ach,
+                               "frac_of_pipe_sustained_file": ach / file_sust if file_sust else None,
+                               "frac_of_half_bf16_sustained_file": ach / (0.5 * f16_sust) if f16_sust else None,
                                "frac_of_cublas_tf32_sustained": ach / tf32_sust,
-                               "frac_of_half_bf16_sustained_file": ach / file_sust if file_sust else None})
+                               "frac_of_cublas_fp16_sustained": ach / f16c_sust if f16c_sust else None})
         dominant = max(per_kernel, key=lambda k: k["share"])
         worst = min(per_kernel, key=lambda k: k["achieved"])
-        peak = file_sust if file_sust else tf32_sust
+        peak = file_sust if file_sust else (f16c_sust if op16 else tf32_sust)
         bpc = DRAM_BYTES_PER_CELL.get(dominant["kernel"])
         roofline = {"bound": "tensor", "kernel": dominant["kernel"], "achieved": dominant["achieved"], "peak": peak,
                     "unit": "TFLOP/s", "frac": dominant["achieved"] / peak,
                     "traffic": (bpc * job["cells"]) if bpc else None,
-                    "peak_source": ("0.5 x bf16_tflops_sustained of MEASURED_PEAKS.json (of measured; the file has no TF32 "
-                                    "entry, TF32 runs at half the BF16 rate)" if file_sust else
-                                    "cuBLAS TF32 8192^3 via torch.matmul measured in this run, sustained (of fallback: no "
+                    "peak_source": ((("bf16_tflops_sustained of MEASURED_PEAKS.json (of measured): the 16-bit tensor pipe "
+                                      "these operands run on" if op16 else
+                                      "0.5 x bf16_tflops_sustained of MEASURED_PEAKS.json (of measured; the file has no "
+                                      "TF32 entry, TF32 runs at half the BF16 rate)")) if file_sust else
+                                    "cuBLAS 8192^3 via torch.matmul measured in this run, sustained (of fallback: no "
                                     "MEASURED_PEAKS.json)"),
-                    "peak_measured_file": {"half_bf16_sustained": file_sust, "half_bf16_burst": file_burst},
+                    "peak_measured_file": {"bf16_sustained": f16_sust, "bf16_burst": f16_burst,
+                                           "half_bf16_sustained": 0.5 * f16_sust if f16_sust else None,
+                                           "half_bf16_burst": 0.5 * f16_burst if f16_burst else None},
                     "peak_cublas_tf32_this_run": {"sustained": tf32_sust, "burst": tf32_burst},
+                    "peak_cublas_fp16_this_run": {"sustained": f16c_sust, "burst": f16c_burst},
+                    "frac_of_half_bf16_sustained_file": dominant["achieved"] / (0.5 * f16_sust) if f16_sust else None,
                     "algorithmic_flop_per_launch": fl, "ms_per_launch": dominant["ms_per_launch"],
                     "worst_kernel": worst["kernel"], "worst_frac": worst["achieved"] / peak,
                     "whole_step_frac": value * flops_per_cell(cfg) / 1e12 / world / peak,
+                    "whole_step_frac_of_half_bf16_sustained_file":
+                        value * flops_per_cell(cfg) / 1e12 / world / (0.5 * f16_sust) if f16_sust else None,
                     "per_kernel": per_kernel}
 
     # ---- end to end through the public API with host buffers ----
@@ -1071,6 +1115,8 @@ def main():
         if world == 1:
             extras["levels4"] = extra_levels4(time_e2e, e2e)
             extras["config4_bf16"] = extra_config4_bf16(ms, device, args)
+            if args.operands != "tf32":
+                extras["tf32_operands"] = extra_tf32_operands(ms, cfg, job, args)
             extras["reference_cuda"] = extra_reference_cuda(args)
         else:
             extras["row_shard"] = extra_row_shard(args, cfg, world, rank, device, ms, time_e2e, barrier, max_over_ranks,
@@ -1088,8 +1134,7 @@ def main():
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": ("tf32 operands (fp32 in HBM), fp32 accumulate" if args.operands == "tf32" else
-                  "bf16 operands in the sweeps and the gradient GEMMs (fp32 in HBM), fp32 accumulate"),
+        "dtype": DTYPE_TEXT[args.operands],
         "data": "synthetic",
         "config": {"workload": cfg["name"], "path": path, "cells_per_step": total_cells,
                    "flop_per_cell": flops_per_cell(cfg),

@@ -281,14 +281,19 @@ int sfb_lookup4d_backward(const float* F1, const float* const* F2_levels, const 
                           float scale, void* stream);
 
 /* Operand type of every contraction (the correlation sweeps and the gradient GEMMs) of the five ops, their fused and
- * channels-first forms and the level calls.  SFB_OPERANDS_TF32 (default): features and the generated gradient operand
- * rounded to TF32.  SFB_OPERANDS_BF16: rounded to BF16 (round to nearest even), products exact in FP32, FP32
- * accumulation -- twice the tensor-core rate per instruction at about 8 mantissa bits (needs C % 8 == 0).  The
- * reference computes in FP32 only; this is the operand type BASELINE's bf16 configuration asks for.  The setting
- * is process-wide (a backward runs on another thread than the forward); sfb_set_sweep_operands returns the
- * previous value, or -1 for an unknown one.  sfb_max_avg_forward_static, sfb_corr_volume and the lookups always
- * compute as they do by default. */
-enum { SFB_OPERANDS_TF32 = 0, SFB_OPERANDS_BF16 = 1 };
+ * channels-first forms and the level calls; accumulation is FP32 in every case, tensors stay FP32 in memory.
+ *   SFB_OPERANDS_FP16 (default): features and the generated gradient operand rounded to FP16 -- the 10 mantissa bits
+ *     of TF32 at twice its tensor-core rate.  FP16 has five exponent bits, so every tensor that becomes an operand is
+ *     first multiplied by a power of two that brings its largest magnitude next to 1 (found on the device, applied
+ *     exactly, undone when results are stored); results match the TF32 path to its own tolerance for data whose
+ *     largest magnitudes lie within about 1e-12 .. 1e12.  Feature dimensions that are not multiples of 8 run as TF32.
+ *   SFB_OPERANDS_TF32: rounded to TF32 (round to nearest), no scaling.
+ *   SFB_OPERANDS_BF16: rounded to BF16 (8 mantissa bits; needs C % 8 == 0): the operand type BASELINE's bf16
+ *     configuration asks for; gradients are then accurate to about 3e-3 instead of 3e-4.
+ * The reference computes in FP32 only.  The setting is process-wide (a backward runs on another thread than the
+ * forward); sfb_set_sweep_operands returns the previous value, or -1 for an unknown one.  sfb_max_avg_forward_static,
+ * sfb_corr_volume and the lookups always compute with TF32 / FP32 as documented at their declarations. */
+enum { SFB_OPERANDS_TF32 = 0, SFB_OPERANDS_BF16 = 1, SFB_OPERANDS_FP16 = 2 };
 int sfb_set_sweep_operands(int operands);
 int sfb_get_sweep_operands(void);
 

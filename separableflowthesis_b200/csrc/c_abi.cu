@@ -80,6 +80,7 @@ int make_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims, 
              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, bool bf16 = false, uint64_t pitch0 = 0) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(SFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+  if (base == nullptr) return fail(SFB_ERR_INVALID_ARGUMENT, "internal: tensor map over an array this workspace does not hold");
   SFB_TRY_BIND_CONTEXT();
   cuuint64_t gdim[5], gstride[5];
   cuuint32_t bdim[5], estride[5];
@@ -186,9 +187,9 @@ void drain_timing_locked() {
   g_timing_pending.clear();
 }
 
-// Operand type of the correlation sweeps of the level calls: 0 = TF32 (default), 1 = BF16.  Process-wide, because
+// Operand type of the contractions (sfb_set_sweep_operands): FP16 (default), TF32 or BF16.  Process-wide, because
 // a backward runs on an autograd worker thread, not on the thread that chose the precision.
-std::atomic<int> g_sweep_operands{0};
+std::atomic<int> g_sweep_operands{SFB_OPERANDS_FP16};
 
 // Test hook (sfb_debug_wait_timeout): time limit handed to the kernels' bounded waits and whether the next sweeps
 // leave out their last load.  Process-wide; 0 / 0 = normal operation.
@@ -206,6 +207,7 @@ GradArgs with_wait_settings(GradArgs a) {
 
 struct Workspace {
   int* status;
+  float* scales;  // scale slots of the FP16 operand kind (kernels.h, SCALE_*), in the header after the status word
   float* F1r;
   float* F2r;
   float* aux;
@@ -273,7 +275,8 @@ Workspace carve(const Dims& d, void* base, const WsPlan& plan) {
     return r;
   };
   w.status = reinterpret_cast<int*>(p + off);
-  off += 256;
+  w.scales = reinterpret_cast<float*>(p + off + WS_SCALES_OFFSET);
+  off += WS_HEADER_BYTES;
   w.n1p = padded_pixels(d);
   w.F1r = take((size_t)d.B * d.N1() * d.C);
   w.F2r = take((size_t)d.B * d.N2() * d.C);
@@ -391,17 +394,26 @@ int map_aux(CUtensorMap* tm, const Dims& d, const void* aux, bool bf16 = false) 
   return make_map(tm, aux, 3, dims, box, CU_TENSOR_MAP_SWIZZLE_128B, bf16);
 }
 
-// Operand type of this call's contractions: the process-wide switch (sfb_set_sweep_operands).
-int operand_mode(const Dims& d, int* bf16) {
-  *bf16 = g_sweep_operands.load() == 1 ? 1 : 0;
-  if (*bf16 && d.C % 8 != 0)
-    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "BF16 operands need a feature dimension that is a multiple of 8 (C=%d)", d.C);
+// Operand type of this call's contractions: the process-wide switch (sfb_set_sweep_operands), as OP16_NONE (TF32),
+// OP16_BF16 or OP16_FP16.
+int operand_mode(const Dims& d, int* op16) {
+  const int m = g_sweep_operands.load();
+  *op16 = m == SFB_OPERANDS_BF16 ? OP16_BF16 : (m == SFB_OPERANDS_FP16 ? OP16_FP16 : OP16_NONE);
+  if (d.C % 8 != 0) {  // 16-bit rows must be multiples of 16 bytes for TMA
+    if (*op16 == OP16_BF16)
+      return fail(SFB_ERR_UNSUPPORTED_SHAPE, "BF16 operands need a feature dimension that is a multiple of 8 (C=%d)", d.C);
+    *op16 = OP16_NONE;  // FP16 and TF32 operands have the same precision: such shapes run with TF32
+  }
   return SFB_OK;
+}
+// What the sweeps multiply their outputs by: the inverse of the feature scales of FP16 operands, else nothing.
+const float* sweep_out_scale(const Workspace& w, int op16) {
+  return op16 == OP16_FP16 ? w.scales + SCALE_INV_F1F2 : nullptr;
 }
 
 // Tensor maps of the sweeps' operands in a workspace: the rounded FP32 copies or their BF16 copies (aux may be null).
-int map_sweep_operands(const Dims& d, const Workspace& w, int bf16, CUtensorMap* f1, CUtensorMap* f2, CUtensorMap* aux) {
-  if (bf16) {
+int map_sweep_operands(const Dims& d, const Workspace& w, int op16, CUtensorMap* f1, CUtensorMap* f2, CUtensorMap* aux) {
+  if (op16) {
     SFB_TRY(map_f1_rows(f1, d, w.F1h, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, true));
     SFB_TRY(map_f2_tile(f2, d, w.F2h, SWEEP_UT, SWEEP_VT, CU_TENSOR_MAP_SWIZZLE_128B, true));
     if (aux != nullptr) SFB_TRY(map_aux(aux, d, w.auxh, true));
@@ -413,11 +425,12 @@ int map_sweep_operands(const Dims& d, const Workspace& w, int bf16, CUtensorMap*
   return SFB_OK;
 }
 
-// Rounded copies of a call's features (and of the mean rows of image 2 when with_aux), plus BF16 copies when bf16.
+// Rounded copies of a call's features (and of the mean rows of image 2 when with_aux), plus 16-bit copies of kind op16.
 cudaError_t prepare_operands(const Dims& d, const Workspace& w, const float* F1, const float* F2, bool with_aux,
-                             int bf16, cudaStream_t st) {
-  return launch_prepare(d, F1, F2, w.F1r, w.F2r, with_aux ? w.aux : nullptr, w.status, st, bf16 ? w.F1h : nullptr,
-                        bf16 ? w.F2h : nullptr, bf16 && with_aux ? w.auxh : nullptr);
+                             int op16, cudaStream_t st) {
+  // (an op without sweeps has no 16-bit copies in its workspace, but its gradient GEMMs still need the feature scales)
+  return launch_prepare(d, F1, F2, w.F1r, w.F2r, with_aux ? w.aux : nullptr, w.status, st, op16 ? w.F1h : nullptr,
+                        op16 ? w.F2h : nullptr, op16 && with_aux ? w.auxh : nullptr, op16, w.scales);
 }
 
 int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_v, int32_t* AM_u, int32_t* AM_v,
@@ -429,15 +442,16 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   Workspace w;
   SFB_TRY(check_workspace(d, ws, ws_bytes, SFB_OP_MAX_AVG_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2, tm_aux;
-  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, &tm_aux));
-  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return prepare_operands(d, w, F1, F2, true, bf16, st); }));
+  SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, &tm_aux));
+  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return prepare_operands(d, w, F1, F2, true, op16, st); }));
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
-  a.bf16 = bf16;
+  a.op16 = op16;
+  a.out_scale = sweep_out_scale(w, op16);
   a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
   a.n_valid = w.n1p;
   a.pu = packed_view(w.ou, d.H2, MAXAVG_SLOTS, w.n1p);
@@ -464,7 +478,7 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
 // channels per sweep.  Weight k is slot (slot0 + k*stride) of the views xu (per u: w_v) / xv (per v: w_u).
 int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, const CUtensorMap& tm_f2, PixView xu,
                         PixView xv, int wu_slot0, int wv_slot0, int w_stride, PixView ou, PixView ov, int n_valid,
-                        cudaStream_t st, int bf16 = 0) {
+                        cudaStream_t st, int op16 = 0, const float* out_scale = nullptr) {
   for (int k0 = 0; k0 < d.Kc; k0 += KC_MAX_PER_SWEEP) {
     SweepArgs a;
     memset(&a, 0, sizeof(a));
@@ -476,7 +490,8 @@ int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, co
     a.xu = xu; a.xv = xv;
     a.wu_slot0 = wu_slot0; a.wv_slot0 = wv_slot0; a.w_stride = w_stride;
     a.ou = ou; a.ov = ov;
-    a.bf16 = bf16;
+    a.op16 = op16;
+    a.out_scale = out_scale;
     a.status = status;
     SFB_CUDA(timed(KID_SWEEP_COMPRESS, 1, st, [&] { return launch_sweep(with_wait_settings(a), tm_f1, tm_f2, tm_f2 /* unused */, st); }));
   }
@@ -486,9 +501,12 @@ int run_compress_sweeps(const Dims& d, int* status, const CUtensorMap& tm_f1, co
 // out_cf: the gradients are written channel-major, (B, C, pixels), gF1 multiplied by scale1.
 int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accumulate, float* gF1, float* gF2,
                   cudaStream_t st, int out_cf = 0, float scale1 = 1.f) {
-  // BF16 form when the operand switch says so and the feature dimension allows it (callers that sweep have already
-  // refused other shapes)
-  const int bf16 = (g_sweep_operands.load() == 1 && d.C % 8 == 0) ? 1 : 0;
+  // 16-bit form when the operand switch says so (callers have refused feature dimensions that do not allow it); with
+  // FP16 the callers have run grad_operand_scales and packed the operands with those scales
+  int op16 = OP16_NONE;
+  SFB_TRY(operand_mode(d, &op16));
+  const float* const s1 = op16 == OP16_FP16 ? w.scales + SCALE_F1 : nullptr;
+  const float* const s2 = op16 == OP16_FP16 ? w.scales + SCALE_F2 : nullptr;
   CUtensorMap tm_y, tm_xu, tm_xv;
   GradArgs a;
   memset(&a, 0, sizeof(a));
@@ -500,7 +518,7 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   a.xu = w.gxu;
   a.xv = w.gxv;
   a.status = w.status;
-  a.bf16 = bf16;
+  a.op16 = op16;
   const int Q = R4 / 4;
   const int kid = mode == GRAD_MAXAVG ? KID_GRAD_MAXAVG_IMG1 : (mode == GRAD_COMPRESS ? KID_GRAD_COMPRESS_IMG1 : KID_GRAD_FUSED_IMG1);
   // K-major B operands: channel-major copies of the rounded features (image 2 in column blocks of 16 with an even
@@ -508,46 +526,49 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   // read as zero: they meet the G values of cells outside the image.
   const uint32_t crows = (uint32_t)((d.C + KBLK - 1) / KBLK * KBLK);  // channel rows of one feature block
   // a row of 32 K-values is 128 bytes of FP32 or 64 bytes of BF16: the swizzle span follows
-  const CUtensorMapSwizzle fswz = bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  const CUtensorMapSwizzle fswz = op16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   const size_t f2t_per_sample = (size_t)d.C * ((d.W2 + GG_VT - 1) / GG_VT) * w.h2p * GG_VT;
   if (!accumulate) {  // later passes over further channel chunks reuse the copies of the first
     SFB_CUDA(timed(KID_PREPARE, 2, st, [&] {
-      cudaMemsetAsync(w.F2t, 0, (size_t)d.B * f2t_per_sample * (bf16 ? 2 : sizeof(float)), st);
-      launch_channel_major(w.F1r, w.F1t, d.B, 1, d.N1(), w.n1p, d.C, 0, bf16, st);
-      return launch_channel_major(w.F2r, w.F2t, d.B, d.H2, d.W2, w.h2p, d.C, 1, bf16, st);
+      cudaMemsetAsync(w.F2t, 0, (size_t)d.B * f2t_per_sample * (op16 ? 2 : sizeof(float)), st);
+      launch_channel_major(w.F1r, w.F1t, d.B, 1, d.N1(), w.n1p, d.C, 0, op16, s1, st);
+      return launch_channel_major(w.F2r, w.F2t, d.B, d.H2, d.W2, w.h2p, d.C, 1, op16, s2, st);
     }));
   }
   // gF1 = G * F2 : rows are image-1 pixels, the K sweep streams 2 x 16 blocks of F2 and 2-row blocks of XU.
   {  // (blocked pixels, C, B); box = 32 consecutive values (2 rows x 16 columns) x all channels
     const uint64_t dims[3] = {(uint64_t)(f2t_per_sample / d.C), (uint64_t)d.C, (uint64_t)d.B};
     const uint32_t box[3] = {GG_KJ, crows, 1};
-    SFB_TRY(make_map(&tm_y, w.F2t, 3, dims, box, fswz, bf16 != 0));
+    SFB_TRY(make_map(&tm_y, w.F2t, 3, dims, box, fswz, op16 != 0));
   }
   SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, TILE_M / 2, GG_UT));  // two 64-pixel boxes per block
   a.out_cf = out_cf;
   a.image2_major = 0;
   a.out = gF1;
   a.out_scale = scale1;
+  a.dev_scale = op16 == OP16_FP16 ? w.scales + SCALE_INV_GF1 : nullptr;
   SFB_CUDA(timed(kid, 1, st, [&] { return launch_grad_gemm(with_wait_settings(a), tm_y, tm_xu, tm_xu /* unused */, st); }));
   // gF2 = G^T * F1 : rows are an 8 x 16 block of image-2 pixels, the K sweep streams 32 pixels of F1, XU and XV.
   {  // (N1, C, B) with rows padded to n1p; box = 32 pixels x all channels
     const uint64_t dims[3] = {(uint64_t)d.N1(), (uint64_t)d.C, (uint64_t)d.B};
     const uint32_t box[3] = {GG_KJ, crows, 1};
-    SFB_TRY(make_map(&tm_y, w.F1t, 3, dims, box, fswz, bf16 != 0, (uint64_t)w.n1p));
+    SFB_TRY(make_map(&tm_y, w.F1t, 3, dims, box, fswz, op16 != 0, (uint64_t)w.n1p));
   }
   SFB_TRY(map_operands(&tm_xu, w.gxu, d.B, d.H2, Q, w.n1p, GG_KJ, GG_ROW_UT));
   SFB_TRY(map_operands(&tm_xv, w.gxv, d.B, d.W2, Q, w.n1p, GG_KJ, GG_ROW_VT));
   a.image2_major = 1;
   a.out = gF2;
   a.out_scale = 1.f;
+  a.dev_scale = op16 == OP16_FP16 ? w.scales + SCALE_INV_GF2 : nullptr;
   SFB_CUDA(timed(kid + 1, 1, st, [&] { return launch_grad_gemm(with_wait_settings(a), tm_y, tm_xu, tm_xv, st); }));
   return SFB_OK;
 }
 
 // Interleaved slots of the max/avg backward (kernels.h): XU = (mean-gradient / W2, 1, max-gradient, argmax bits),
 // XV = (1, mean-gradient / H2, max-gradient, argmax bits); slots 0 and 1 of the two sides multiply to the mean terms.
+// `scales` (FP16 operands, else null): the call's scale slots; the gradient values are then multiplied by sg * sa.
 void maxavg_slot_sources(const Dims& d, const int32_t* AM_u, const int32_t* AM_v, const float* gMA_u,
-                         const float* gMA_v, SlotSources* su, SlotSources* sv) {
+                         const float* gMA_v, SlotSources* su, SlotSources* sv, const float* scales) {
   memset(su, 0, sizeof(*su));
   memset(sv, 0, sizeof(*sv));
   su->s[0] = {gMA_u, 2, 1, 1.f / (float)d.W2};
@@ -558,12 +579,18 @@ void maxavg_slot_sources(const Dims& d, const int32_t* AM_u, const int32_t* AM_v
   sv->s[1] = {gMA_v, 2, 1, 1.f / (float)d.H2};
   sv->s[2] = {gMA_v, 2, 0, 0.f};
   sv->s[3] = {AM_v, 1, 0, 0.f};
+  if (scales != nullptr) {
+    su->dev_scales = sv->dev_scales = scales;
+    su->s[0].dev = su->s[2].dev = sv->s[1].dev = sv->s[2].dev = SCALE_GA + 1;
+  }
 }
 // Interleaved slots of the compression backward for channels k0 .. k0+kc-1, local channel j:
 // XU 2j = gC_u, 2j+1 = A_v;  XV 2j = A_u, 2j+1 = gC_v, so that G[p,u,v] = sum_slots XU[u,p,slot] * XV[v,p,slot].
 // The gradients may be channels g0.. of a tensor with gK channels (the concatenated tensors of the call site).
+// `scales` (FP16 operands, else null): gradients are multiplied by sg, weights by sa.
 void compress_slot_sources(int K, int k0, int kc, const float* A_u, const float* A_v, const float* gC_u,
-                           const float* gC_v, SlotSources* su, SlotSources* sv, int gK = 0, int g0 = 0) {
+                           const float* gC_v, SlotSources* su, SlotSources* sv, const float* scales, int gK = 0,
+                           int g0 = 0) {
   if (gK == 0) gK = K;
   memset(su, 0, sizeof(*su));
   memset(sv, 0, sizeof(*sv));
@@ -572,23 +599,45 @@ void compress_slot_sources(int K, int k0, int kc, const float* A_u, const float*
     su->s[2 * j + 1] = {A_v, K, k0 + j, 0.f};
     sv->s[2 * j] = {A_u, K, k0 + j, 0.f};
     sv->s[2 * j + 1] = {gC_v, gK, g0 + k0 + j, 0.f};
+    if (scales != nullptr) {
+      su->s[2 * j].dev = sv->s[2 * j + 1].dev = SCALE_G + 1;
+      su->s[2 * j + 1].dev = sv->s[2 * j].dev = SCALE_A + 1;
+    }
   }
+  if (scales != nullptr) su->dev_scales = sv->dev_scales = scales;
 }
+
+// FP16 operands: the gradient-operand scales of this call (kernels.h, SCALE_*) from the largest magnitudes of the
+// gradient tensors and of the weight tensors that multiply them.  No weight tensors: the weights are softmax outputs,
+// known to lie in [0, 1], and their scale stays 1.  Runs after the call's launch_prepare, which cleared the slots and
+// found the feature scales.
+struct AbsmaxSrc { const float* p; size_t n; };
+int grad_operand_scales(const Workspace& w, int op16, std::initializer_list<AbsmaxSrc> grads,
+                        std::initializer_list<AbsmaxSrc> weights, cudaStream_t st) {
+  if (op16 != OP16_FP16) return SFB_OK;
+  SFB_CUDA(timed(KID_PREPARE, (int)(grads.size() + weights.size()) + 1, st, [&] {
+    for (const AbsmaxSrc& g : grads) launch_absmax(g.p, g.n, 1.f, w.scales + SCALE_AMAX_G, st);
+    for (const AbsmaxSrc& a : weights) launch_absmax(a.p, a.n, 1.f, w.scales + SCALE_AMAX_A, st);
+    return launch_grad_scales(w.scales, st);
+  }));
+  return SFB_OK;
+}
+const float* grad_slot_scales(const Workspace& w, int op16) { return op16 == OP16_FP16 ? w.scales : nullptr; }
 
 // Attention gradients of the compression backward: gA_v[p,k,u] = sum_v S * gC_v[p,k,v] and
 // gA_u[p,k,v] = sum_u S * gC_u[p,k,u] -- the forward compression sweep with the upstream gradients in the
 // role of the weights (w_u = gC_v, w_v = gC_u).
 int run_attention_grads(const Dims& d, const Workspace& w, const float* gC_u, const float* gC_v, float* gA_u,
-                        float* gA_v, cudaStream_t st, int bf16) {
+                        float* gA_v, cudaStream_t st, int op16) {
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, nullptr));
+  SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
   const int N1 = d.N1(), K = d.Kc;
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_pack(gC_v, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);
     return launch_pack(gC_u, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);
   }));
   SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, packed_view(w.xu, d.H2, K, w.n1p), packed_view(w.xv, d.W2, K, w.n1p),
-                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st, bf16));
+                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st, op16, sweep_out_scale(w, op16)));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_unpack(w.ou, gA_v, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
     return launch_unpack(w.ov, gA_u, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
@@ -701,18 +750,18 @@ int sfb_compression_forward(const float* F1, const float* F2, const float* A_u, 
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, nullptr));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   const int N1 = d.N1(), K = d.Kc;
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_pack(A_u, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);         // w_u[k][v] = XV slot k
     return launch_pack(A_v, w.xu, d.B, N1, w.n1p, K, 0, K, d.H2, K, 0, 1, 0.f, st);  // w_v[k][u] = XU slot k
   }));
   SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, packed_view(w.xu, d.H2, K, w.n1p), packed_view(w.xv, d.W2, K, w.n1p),
-                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st, bf16));
+                              0, 0, 1, packed_view(w.ou, d.H2, K, w.n1p), packed_view(w.ov, d.W2, K, w.n1p), w.n1p, st, op16, sweep_out_scale(w, op16)));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_unpack(w.ou, C_u, d.B, N1, w.n1p, K, d.H2, K, 0, 1, K, 0, st);
     return launch_unpack(w.ov, C_v, d.B, N1, w.n1p, K, d.W2, K, 0, 1, K, 0, st);
@@ -730,12 +779,14 @@ int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t*
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_MAX_ARGMAX_AVG_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  const size_t pix = (size_t)d.B * d.N1();
+  SFB_TRY(grad_operand_scales(w, op16, {{gMA_u, pix * 2 * d.H2}, {gMA_v, pix * 2 * d.W2}}, {}, st));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     SlotSources su, sv;
-    maxavg_slot_sources(d, AM_u, AM_v, gMA_u, gMA_v, &su, &sv);
+    maxavg_slot_sources(d, AM_u, AM_v, gMA_u, gMA_v, &su, &sv, grad_slot_scales(w, op16));
     launch_pack_interleaved(su, w.gxu, d.B, d.N1(), w.n1p, d.H2, 4, 1, 0, st);
     return launch_pack_interleaved(sv, w.gxv, d.B, d.N1(), w.n1p, d.W2, 4, 1, 0, st);
   }));
@@ -753,17 +804,21 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   const int N1 = d.N1(), K = d.Kc;
-  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, bf16));
+  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, op16));
+  {
+    const size_t pk = (size_t)d.B * N1 * K;
+    SFB_TRY(grad_operand_scales(w, op16, {{gC_u, pk * d.H2}, {gC_v, pk * d.W2}}, {{A_u, pk * d.W2}, {A_v, pk * d.H2}}, st));
+  }
   // gradient GEMMs, at most KC_MAX_PER_SWEEP channels per pass; later passes add to gF1 / gF2.
   for (int k0 = 0; k0 < K; k0 += KC_MAX_PER_SWEEP) {
     const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
     SFB_CUDA(timed(KID_PACK, 2, st, [&] {
       SlotSources su, sv;
-      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
+      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, grad_slot_scales(w, op16));
       launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
       return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
     }));
@@ -781,10 +836,10 @@ int sfb_compression_attention_backward(const float* F1, const float* F2, const f
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
-  return run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, bf16);
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  return run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, op16);
 }
 
 // Feature gradients of both backward ops from one GEMM pair (plus accumulated passes for channels beyond
@@ -793,14 +848,23 @@ static int run_fused_feature_grads(const Dims& d, const Workspace& w, const int3
                                    const float* gMA_u, const float* gMA_v, const float* A_u, const float* A_v,
                                    const float* gC_u, const float* gC_v, float* gF1, float* gF2, cudaStream_t st) {
   const int N1 = d.N1(), K = d.Kc;
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
+  {
+    const size_t pix = (size_t)d.B * N1;
+    SFB_TRY(grad_operand_scales(w, op16,
+                                {{gMA_u, pix * 2 * d.H2}, {gMA_v, pix * 2 * d.W2}, {gC_u, pix * K * d.H2}, {gC_v, pix * K * d.W2}},
+                                {{A_u, pix * K * d.W2}, {A_v, pix * K * d.H2}}, st));
+  }
+  const float* const gs = grad_slot_scales(w, op16);
   {  // group 0 = max/avg slots, groups 1.. = the first (up to 4) compression channels; G is their sum
     const int kc = chunk_channels(K), Qc = grad_slots(kc) / 4, Q = 1 + Qc;
     SFB_CUDA(timed(KID_PACK, 4, st, [&] {
       SlotSources su, sv;
-      maxavg_slot_sources(d, AM_u, AM_v, gMA_u, gMA_v, &su, &sv);
+      maxavg_slot_sources(d, AM_u, AM_v, gMA_u, gMA_v, &su, &sv, gs);
       launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, 4, Q, 0, st);
       launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4, Q, 0, st);
-      compress_slot_sources(K, 0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
+      compress_slot_sources(K, 0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, gs);
       launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, 4 * Qc, Q, 1, st);
       return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4 * Qc, Q, 1, st);
     }));
@@ -810,7 +874,7 @@ static int run_fused_feature_grads(const Dims& d, const Workspace& w, const int3
     const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
     SFB_CUDA(timed(KID_PACK, 2, st, [&] {
       SlotSources su, sv;
-      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv);
+      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, gs);
       launch_pack_interleaved(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
       return launch_pack_interleaved(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
     }));
@@ -830,9 +894,9 @@ int sfb_separation_feature_backward(const float* F1, const float* F2, const int3
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
 }
 
@@ -849,10 +913,10 @@ int sfb_separation_backward(const float* F1, const float* F2, const int32_t* AM_
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
-  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, bf16));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, op16));
   return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
 }
 
@@ -867,16 +931,17 @@ int sfb_max_argmax_avg_forward_cf(const float* F1, const float* F2, float* SEP_v
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_MAX_AVG_FORWARD_CF, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2, tm_aux;
-  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, &tm_aux));
-  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return prepare_operands(d, w, F1, F2, true, bf16, st); }));
+  SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, &tm_aux));
+  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return prepare_operands(d, w, F1, F2, true, op16, st); }));
   const int N1 = d.N1();
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
-  a.bf16 = bf16;
+  a.op16 = op16;
+  a.out_scale = sweep_out_scale(w, op16);
   a.mode = with_argmax ? SWEEP_MAXARGAVG : SWEEP_MAXAVG;
   a.n_valid = N1;
   a.pu = cf_view(SEP_v, 2, d.H2, N1);       // per-u channels live in the tensor the call site calls sep_v
@@ -898,15 +963,15 @@ static int run_compress_cf(const float* F1, const float* F2, const float* W_u, c
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_COMPRESSION_CF, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, nullptr));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   const int N1 = d.N1(), K = d.Kc;
   // W_u (B,K,W2,N1) weights per v, W_v (B,K,H2,N1) per u; O_u (B,K,H2,N1), O_v (B,K,W2,N1)
   return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(W_v, K, d.H2, N1), cf_view(W_u, K, d.W2, N1), 0, 0, 1,
-                             cf_view(O_u, K, d.H2, N1), cf_view(O_v, K, d.W2, N1), N1, st, bf16);
+                             cf_view(O_u, K, d.H2, N1), cf_view(O_v, K, d.W2, N1), N1, st, op16, sweep_out_scale(w, op16));
 }
 
 int sfb_compression_forward_cf(const float* F1, const float* F2, const float* A_u, const float* A_v, float* C_u,
@@ -927,17 +992,29 @@ int sfb_compression_attention_backward_cf(const float* F1, const float* F2, cons
 static int run_fused_feature_grads_cf(const Dims& d, const Workspace& w, const int32_t* AM_u, const int32_t* AM_v,
                                       const float* gM_v, const float* gM_u, const float* A_u, const float* A_v,
                                       const float* gC_u, const float* gC_v, int gK, int g0, float* gF1, float* gF2,
-                                      cudaStream_t st, int out_cf = 0, float scale1 = 1.f) {
+                                      cudaStream_t st, int out_cf = 0, float scale1 = 1.f, bool unit_weights = false) {
   const int N1 = d.N1(), K = d.Kc;
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
+  {  // FP16 operands: scales from the whole gradient tensors (an upper bound when only some channels are this level's);
+     // unit_weights: A_u / A_v are softmax outputs
+    const size_t bn = (size_t)d.B * N1;
+    if (unit_weights)
+      SFB_TRY(grad_operand_scales(w, op16, {{gM_v, bn * 2 * d.H2}, {gM_u, bn * 2 * d.W2}, {gC_u, bn * gK * d.H2}, {gC_v, bn * gK * d.W2}}, {}, st));
+    else
+      SFB_TRY(grad_operand_scales(w, op16, {{gM_v, bn * 2 * d.H2}, {gM_u, bn * 2 * d.W2}, {gC_u, bn * gK * d.H2}, {gC_v, bn * gK * d.W2}},
+                                  {{A_u, bn * K * d.W2}, {A_v, bn * K * d.H2}}, st));
+  }
+  const float* const gs = grad_slot_scales(w, op16);
   {
     const int kc = chunk_channels(K), Qc = grad_slots(kc) / 4, Q = 1 + Qc;
     SFB_CUDA(timed(KID_PACK, 4, st, [&] {
       SlotSources su, sv;
       // channel 0 = max gradient, channel 1 = mean gradient (same slots as the reference layout)
-      maxavg_slot_sources(d, AM_u, AM_v, gM_v, gM_u, &su, &sv);
+      maxavg_slot_sources(d, AM_u, AM_v, gM_v, gM_u, &su, &sv, gs);
       launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4, Q, 0, st);
       launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4, Q, 0, st);
-      compress_slot_sources(K, 0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, gK, g0);
+      compress_slot_sources(K, 0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, gs, gK, g0);
       launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, 4 * Qc, Q, 1, st);
       return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, 4 * Qc, Q, 1, st);
     }));
@@ -947,7 +1024,7 @@ static int run_fused_feature_grads_cf(const Dims& d, const Workspace& w, const i
     const int kc = chunk_channels(K - k0), R4 = grad_slots(kc);
     SFB_CUDA(timed(KID_PACK, 2, st, [&] {
       SlotSources su, sv;
-      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, gK, g0);
+      compress_slot_sources(K, k0, kc, A_u, A_v, gC_u, gC_v, &su, &sv, gs, gK, g0);
       launch_pack_interleaved_cf(su, w.gxu, d.B, N1, w.n1p, d.H2, R4, R4 / 4, 0, st);
       return launch_pack_interleaved_cf(sv, w.gxv, d.B, N1, w.n1p, d.W2, R4, R4 / 4, 0, st);
     }));
@@ -968,9 +1045,9 @@ int sfb_separation_feature_backward_cf(const float* F1, const float* F2, const i
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_FEATURE_BACKWARD_CF, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   return run_fused_feature_grads_cf(d, w, AM_u, AM_v, gSEP_v, gSEP_u, A_u, A_v, gC_u, gC_v, d.Kc, 0, gF1, gF2, st);
 }
 
@@ -1064,25 +1141,16 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_LEVEL_FORWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int bf16 = g_sweep_operands.load() == 1 ? 1 : 0;
-  if (bf16 && d.C % 8 != 0)
-    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "BF16 sweep operands need a feature dimension that is a multiple of 8 (C=%d)", d.C);
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2, tm_aux;
-  if (bf16) {
-    SFB_TRY(map_f1_rows(&tm_f1, d, w.F1h, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, true));
-    SFB_TRY(map_f2_tile(&tm_f2, d, w.F2h, SWEEP_UT, SWEEP_VT, CU_TENSOR_MAP_SWIZZLE_128B, true));
-    SFB_TRY(map_aux(&tm_aux, d, w.auxh, true));
-  } else {
-    SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-    SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-    SFB_TRY(map_aux(&tm_aux, d, w.aux));
-  }
-  uint16_t* const F1h = bf16 ? w.F1h : nullptr;
-  uint16_t* const F2h = bf16 ? w.F2h : nullptr;
-  uint16_t* const auxh = bf16 ? w.auxh : nullptr;
+  SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, &tm_aux));
+  uint16_t* const F1h = op16 ? w.F1h : nullptr;
+  uint16_t* const F2h = op16 ? w.F2h : nullptr;
+  uint16_t* const auxh = op16 ? w.auxh : nullptr;
   SFB_CUDA(timed(KID_PREPARE, 3, st, [&] {
-    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, w.aux, w.status, st, F1h, F2h, auxh)
-                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st, F1h, F2h, auxh);
+    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, w.aux, w.status, st, F1h, F2h, auxh, op16, w.scales)
+                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st, F1h, F2h, auxh, op16, w.scales);
   }));
   const int N1 = d.N1(), K = d.Kc, Kt = pl.Ktot, c0 = pl.c0;
   SweepArgs a;
@@ -1094,7 +1162,8 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   a.pv = cf_channels(SEP_u, Kt, c0, d.W2, N1);
   a.pu_arg = cf_view(AM_u, 1, d.H2, N1);
   a.pv_arg = cf_view(AM_v, 1, d.W2, N1);
-  a.bf16 = bf16;
+  a.op16 = op16;
+  a.out_scale = sweep_out_scale(w, op16);
   a.status = w.status;
   SFB_CUDA(timed(KID_SWEEP_MAXAVG, 1, st, [&] { return launch_sweep(with_wait_settings(a), tm_f1, tm_f2, tm_aux, st); }));
   const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
@@ -1107,7 +1176,7 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   // C_u (per u, weights A_u per v) -> SEP_v channels 2.., C_v -> SEP_u channels 2..
   return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(A_v, K, d.H2, N1), cf_view(A_u, K, d.W2, N1), 0, 0, 1,
                              cf_channels(SEP_v, Kt, c0 + 2, d.H2, N1), cf_channels(SEP_u, Kt, c0 + 2, d.W2, N1), N1, st,
-                             bf16);
+                             op16, sweep_out_scale(w, op16));
 }
 
 int sfb_separation_level_forward(const float* F1, const float* F2, const float* weight_u, const float* bias_u,
@@ -1146,30 +1215,22 @@ static int level_backward(Placement pl, const float* F1, const float* F2, int fm
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_SEPARATION_LEVEL_BACKWARD, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // the attention-gradient sweep follows the chosen operand type; the gradient GEMMs always use the TF32 copies
-  const int bf16 = g_sweep_operands.load() == 1 ? 1 : 0;
-  if (bf16 && d.C % 8 != 0)
-    return fail(SFB_ERR_UNSUPPORTED_SHAPE, "BF16 sweep operands need a feature dimension that is a multiple of 8 (C=%d)", d.C);
+  int op16;
+  SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2;
-  if (bf16) {
-    SFB_TRY(map_f1_rows(&tm_f1, d, w.F1h, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, true));
-    SFB_TRY(map_f2_tile(&tm_f2, d, w.F2h, SWEEP_UT, SWEEP_VT, CU_TENSOR_MAP_SWIZZLE_128B, true));
-  } else {
-    SFB_TRY(map_f1_rows(&tm_f1, d, w.F1r, TILE_M));
-    SFB_TRY(map_f2_tile(&tm_f2, d, w.F2r, SWEEP_UT, SWEEP_VT));
-  }
-  uint16_t* const F1h = bf16 ? w.F1h : nullptr;
-  uint16_t* const F2h = bf16 ? w.F2h : nullptr;
+  SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
+  uint16_t* const F1h = op16 ? w.F1h : nullptr;
+  uint16_t* const F2h = op16 ? w.F2h : nullptr;
   SFB_CUDA(timed(KID_PREPARE, 2, st, [&] {
-    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, nullptr, w.status, st, F1h, F2h, nullptr)
-                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st, F1h, F2h, nullptr);
+    return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, nullptr, w.status, st, F1h, F2h, nullptr, op16, w.scales)
+                 : launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st, F1h, F2h, nullptr, op16, w.scales);
   }));
   const int N1 = d.N1(), K = d.Kc, Kt = pl.Ktot, c0 = pl.c0;
   // attention gradients: gA_v(b,k,u,p) = sum_v S * gC_v(b,k,v,p), gA_u(b,k,v,p) = sum_u S * gC_u(b,k,u,p), with
   // gC_u = gSEP_v[:, 2:] (per u) and gC_v = gSEP_u[:, 2:] (per v) in the role of the weights
   SFB_TRY(run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_channels(gSEP_v, Kt, c0 + 2, d.H2, N1),
                               cf_channels(gSEP_u, Kt, c0 + 2, d.W2, N1), 0, 0, 1, cf_view(w.ga_v, K, d.H2, N1),
-                              cf_view(w.ga_u, K, d.W2, N1), N1, st, bf16));
+                              cf_view(w.ga_u, K, d.W2, N1), N1, st, op16, sweep_out_scale(w, op16)));
   // through softmax and Conv3d: parameter gradients, and the total gradients of the max/avg channels
   const long long sb_u = (long long)Kt * d.W2 * N1, sb_v = (long long)Kt * d.H2 * N1;
   SFB_CUDA(timed(KID_ATTENTION_BWD, 2 * attention_backward_launches(K), st, [&] {
@@ -1180,7 +1241,7 @@ static int level_backward(Placement pl, const float* F1, const float* F2, int fm
                                      gSEP_v + ov, sb_v, w.gm_v, gweight_v, gbias_v, w.at_partial, st, w.status);
   }));
   return run_fused_feature_grads_cf(d, w, AM_u, AM_v, w.gm_v, w.gm_u, A_u, A_v, gSEP_v, gSEP_u, Kt, c0 + 2, gF1, gF2, st,
-                                    fmaps, fmaps ? scale1 : 1.f);
+                                    fmaps, fmaps ? scale1 : 1.f, /*unit_weights=*/true);
 }
 
 int sfb_separation_level_backward(const float* F1, const float* F2, const float* weight_u, const float* weight_v,
@@ -1360,7 +1421,7 @@ int sfb_lookup4d_backward(const float* F1, const float* const* F2_levels, const 
 }
 
 int sfb_set_sweep_operands(int operands) {
-  if (operands != SFB_OPERANDS_TF32 && operands != SFB_OPERANDS_BF16) return -1;
+  if (operands != SFB_OPERANDS_TF32 && operands != SFB_OPERANDS_BF16 && operands != SFB_OPERANDS_FP16) return -1;
   return g_sweep_operands.exchange(operands);
 }
 int sfb_get_sweep_operands(void) { return g_sweep_operands.load(); }
@@ -1373,11 +1434,10 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
   Workspace w;
   SFB_TRY(check_workspace(d, workspace, workspace_bytes, SFB_OP_CORR_VOLUME, &w));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int bf16;
-  SFB_TRY(operand_mode(d, &bf16));
+  const int op16 = OP16_NONE;  // this test aid always computes with TF32 operands (its workspace has no 16-bit copies)
   CUtensorMap tm_f1, tm_f2;
-  SFB_TRY(map_sweep_operands(d, w, bf16, &tm_f1, &tm_f2, nullptr));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, bf16, st); }));
+  SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
+  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;

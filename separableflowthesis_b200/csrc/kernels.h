@@ -51,6 +51,11 @@ constexpr int GG_VT = 16;
 constexpr int GG_KJ = 32;     // K extent (pixels of the other image) of one gradient-GEMM block
 constexpr int KC_MAX_PER_SWEEP = 4;  // attention channels handled by one compression sweep
 
+// 16-bit operand kinds of the contractions (0 = none: TF32 operands in FP32 storage).
+#ifndef SFB_OP16_KINDS
+#define SFB_OP16_KINDS
+enum : int { OP16_NONE = 0, OP16_BF16 = 1, OP16_FP16 = 2 };
+#endif
 enum SweepMode : int { SWEEP_MAXAVG = 0, SWEEP_MAXARGAVG = 1, SWEEP_COMPRESS = 2, SWEEP_DUMP = 3 };
 enum GradMode : int { GRAD_MAXAVG = 0, GRAD_COMPRESS = 1, GRAD_FUSED = 2 };
 
@@ -80,7 +85,10 @@ struct SweepArgs {
   PixView xu, xv;
   int wu_slot0, wv_slot0, w_stride;
   PixView ou, ov;
-  int bf16;              // operands are BF16 copies (64 channels per 128-byte row, tcgen05.mma kind::f16) instead of TF32
+  int op16;              // operands are 16-bit copies (64 channels per 128-byte row, tcgen05.mma kind::f16) instead of
+                         // TF32: OP16_BF16 or OP16_FP16
+  const float* out_scale;  // device scalar every output value is multiplied by before it is stored (null = 1): undoes
+                           // the power-of-two scaling of FP16 operands
   float* dump;           // SWEEP_DUMP: dense S (B,N1,H2,W2), test use only
   int* status;           // device status word
   unsigned long long wait_limit_ns;  // time limit of one device-side wait; 0 = the default (2 s)
@@ -108,7 +116,8 @@ struct GradArgs {
   int accumulate;        // 0: out = result, 1: out += result (later channel chunks of the compression op)
   int out_cf;            // 0: out is (B, pixels, C); 1: out is (B, C, pixels), the layout of the model's feature maps
   float out_scale;       // the result is multiplied by this before it is stored / added (out_cf only)
-  int bf16;              // G and the feature copies are BF16 (tcgen05.mma kind::f16) instead of TF32
+  int op16;              // G and the feature copies are 16-bit (tcgen05.mma kind::f16) instead of TF32: OP16_BF16 / OP16_FP16
+  const float* dev_scale;  // device scalar the result is multiplied by as well (null = 1), see SweepArgs::out_scale
   const float* xu;
   const float* xv;
   float* out;            // gF1 (B,N1,C) or gF2 (B,N2,C)
@@ -122,10 +131,13 @@ struct SlotSource {
   const void* src;
   int Ksrc, k;
   float scale;
+  int dev;   // 0: nothing more; i > 0: the value is multiplied by dev_scales[i - 1] as well (FP16 operands: the
+             // power-of-two scales of the gradient and weight tensors, known on the device only)
 };
 constexpr int MAX_SLOTS = 8;
 struct SlotSources {
   SlotSource s[MAX_SLOTS];
+  const float* dev_scales;  // may be null when no slot has dev != 0
 };
 // Same, from channels-first sources: dst[b][d][q][p][j] = scale * src[b][k][d][p], src is (B, Ksrc, D, N1).
 cudaError_t launch_pack_interleaved_cf(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
@@ -135,25 +147,38 @@ cudaError_t launch_pack_interleaved_cf(const SlotSources& src, float* dst, int B
 cudaError_t launch_pack_interleaved(const SlotSources& src, float* dst, int B, int N1, int n1p, int D, int R4,
                                     int Qtot, int q0, cudaStream_t stream);
 
+// Workspace header: the status word, then (64 bytes in) the scale slots of the FP16 operand kind, all cleared by
+// launch_prepare.  amax slots hold float bits (atomicMax), the others floats; every scale is a power of two.
+constexpr size_t WS_HEADER_BYTES = 256, WS_SCALES_OFFSET = 64, WS_HEADER_CLEAR_BYTES = 128;
+enum : int {
+  SCALE_AMAX_F1 = 0, SCALE_AMAX_F2 = 1, SCALE_AMAX_G = 2, SCALE_AMAX_A = 3,
+  SCALE_F1 = 4, SCALE_F2 = 5, SCALE_INV_F1F2 = 6,   // F1h = fp16(s1 F1), F2h = fp16(s2 F2), sweep outputs * 1/(s1 s2)
+  SCALE_GA = 7, SCALE_G = 8, SCALE_A = 9,           // gradient slots * sg (* sa when no weight multiplies them), weights * sa
+  SCALE_INV_GF1 = 10, SCALE_INV_GF2 = 11            // gF1 * 1/(sg sa s2), gF2 * 1/(sg sa s1)
+};
 // Rounds F1/F2 to TF32 (round-to-nearest) into the workspace copies, optionally builds the
-// row/column mean rows of F2, and clears the status word.
-// F1h / F2h / auxh (optional): the same three arrays rounded to BF16 from the unrounded values, the operands of the
-// BF16 form of the sweeps.
+// row/column mean rows of F2, and clears the workspace header.
+// F1h / F2h / auxh (optional): the same three arrays as 16-bit operands of kind `op16` from the unrounded values: BF16,
+// or FP16 after scaling by the powers of two this call derives from the arrays' largest magnitudes (scales[]).
 cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
                            int* status, cudaStream_t stream, uint16_t* F1h = nullptr, uint16_t* F2h = nullptr,
-                           uint16_t* auxh = nullptr);
+                           uint16_t* auxh = nullptr, int op16 = 0, float* scales = nullptr);
 // The same from the model's feature maps fmap1 (B, C, H1, W1), fmap2 (B, C, H2, W2): F1r = round(scale1 * fmap1)
 // transposed to (B, H1, W1, C), F2r = round(fmap2) transposed (core/corr.py:419-422 does this with
 // permute().contiguous() and a division).
 cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
                               float* F2r, float* aux, int* status, cudaStream_t stream, uint16_t* F1h = nullptr,
-                              uint16_t* F2h = nullptr, uint16_t* auxh = nullptr);
-// Channel-major copy of a (rounded) pixel-major feature array (B, rows*width, C), as FP32 or (bf16 != 0) rounded to
-// BF16; padding is not written.
+                              uint16_t* F2h = nullptr, uint16_t* auxh = nullptr, int op16 = 0, float* scales = nullptr);
+// Largest |x| * premul of n floats, combined into the amax slot; the gradient-operand scales from the amax slots.
+cudaError_t launch_absmax(const float* x, size_t n, float premul, float* slot, cudaStream_t stream);
+cudaError_t launch_feature_scales(float* scales, cudaStream_t stream);
+cudaError_t launch_grad_scales(float* scales, cudaStream_t stream);
+// Channel-major copy of a (rounded) pixel-major feature array (B, rows*width, C), as FP32 or (op16 != 0) as 16-bit
+// operands (FP16: times the device scalar *scale16); padding is not written.
 //   blocked = 0: dst (B, C, pitch) with pixel index row*width + x (rows = 1)
 //   blocked = 1: dst (B, C, ceil(width/16), pitch, 16), element (row, x) at ((x/16)*pitch + row)*16 + x%16
 cudaError_t launch_channel_major(const float* src, void* dst, int B, int rows, int width, int pitch, int C,
-                                 int blocked, int bf16, cudaStream_t stream);
+                                 int blocked, int op16, const float* scale16, cudaStream_t stream);
 // Pack: dst[b][d][r0 + k*rstride][p] = scale * src[b][p][ksrc0 + k][d] for k < K (raw 32-bit copy when
 // scale == 0), zero for N1 <= p < n1p.  src is (B, N1, Ksrc, D), dst is (B, D, R, n1p).
 cudaError_t launch_pack(const void* src, float* dst, int B, int N1, int n1p, int Ksrc, int ksrc0, int K, int D,

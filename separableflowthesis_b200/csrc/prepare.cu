@@ -5,6 +5,10 @@
 //  * the "aux" rows of F2 used for the mean channels: row u of aux = mean over v of F2[u,v,:],
 //    row H2+v = mean over u of F2[u,v,:]  (mean_v S[p,u,v] = F1[p] . mean_v F2[u,v], the same sum the
 //    reference accumulates cell by cell, MemorySaver_kernel_forward.cu:286-290).
+//  * 16-bit operand copies (BF16, or FP16 for the operand type with TF32's mantissa at twice its tensor-core rate).
+//    FP16 has a narrow exponent range, so every tensor that becomes an FP16 operand is first multiplied by a power
+//    of two that brings its largest magnitude next to 1 (exact, undone when results are stored): absmax_kernel
+//    finds the magnitudes, *_scales_kernel turn them into the multipliers, all on the device.
 #include <algorithm>
 
 #include <cuda_bf16.h>
@@ -14,15 +18,82 @@
 
 namespace sfb {
 
-// `outh` (optional): the same values rounded to BF16 instead (operands of the BF16 sweeps).
-__global__ void round_copy_kernel(const float4* __restrict__ in, float4* __restrict__ out, size_t n4,
-                                  uint2* __restrict__ outh) {
+// Largest |x| * premul of an array, as the bits of a non-negative float, combined into *out with atomicMax (integer
+// order = float order for non-negative values; NaNs are ignored).  n4 = number of float4.
+__global__ void absmax_kernel(const float4* __restrict__ x, size_t n4, int tail, float premul,
+                              unsigned* __restrict__ out) {
+  float m = 0.f;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = __ldg(x + i);
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+  if (blockIdx.x == 0 && (int)threadIdx.x < tail) m = fmaxf(m, fabsf(__ldg(reinterpret_cast<const float*>(x + n4) + threadIdx.x)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(out, __float_as_uint(m * fabsf(premul)));
+}
+
+cudaError_t launch_absmax(const float* x, size_t n, float premul, float* slot, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  const size_t n4 = n / 4;  // the arrays are 16-byte aligned; up to three trailing values are read one by one
+  const int threads = 256;
+  const unsigned blocks = (unsigned)std::max<size_t>(1, std::min<size_t>((n4 + threads - 1) / threads, 148 * 8));
+  absmax_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const float4*>(x), n4, (int)(n - 4 * n4), premul,
+                                                reinterpret_cast<unsigned*>(slot));
+  return cudaGetLastError();
+}
+
+// The power of two that brings a largest magnitude (float bits in `amax_bits`) into [target, 2*target); 1 when the
+// magnitude is zero, not finite or subnormal, and never beyond 2^+-40, so that products of three scales stay finite
+// (tensors whose largest magnitude lies outside about 1e-12 .. 1e12 are not brought all the way into FP16's range;
+// TF32 operands are the choice for such data).
+__device__ __forceinline__ float pow2_scale(unsigned amax_bits, int target_log2) {
+  const int e = (int)(amax_bits >> 23) & 0xff;
+  if (e == 0 || e == 255) return 1.f;
+  int shift = target_log2 - (e - 127);
+  shift = max(-40, min(40, shift));
+  return __uint_as_float((unsigned)(127 + shift) << 23);
+}
+
+// scales[] (SCALE_* in kernels.h): feature scales from the two magnitudes found by absmax_kernel.
+__global__ void feature_scales_kernel(float* scales) {
+  const float s1 = pow2_scale(__float_as_uint(scales[SCALE_AMAX_F1]), 0);
+  const float s2 = pow2_scale(__float_as_uint(scales[SCALE_AMAX_F2]), 0);
+  scales[SCALE_F1] = s1;
+  scales[SCALE_F2] = s2;
+  scales[SCALE_INV_F1F2] = 1.f / (s1 * s2);
+}
+// Gradient-operand scales (after feature_scales_kernel of the same call): G is generated as (sg * sa) * G.
+__global__ void grad_scales_kernel(float* scales) {
+  const float sg = pow2_scale(__float_as_uint(scales[SCALE_AMAX_G]), 7);   // largest gradient value -> [128, 256)
+  const float sa = pow2_scale(__float_as_uint(scales[SCALE_AMAX_A]), 0);   // largest weight -> [1, 2)
+  scales[SCALE_GA] = sg * sa;
+  scales[SCALE_G] = sg;
+  scales[SCALE_A] = sa;
+  scales[SCALE_INV_GF1] = 1.f / (sg * sa * scales[SCALE_F2]);   // gF1 = G * F2
+  scales[SCALE_INV_GF2] = 1.f / (sg * sa * scales[SCALE_F1]);   // gF2 = G^T * F1
+}
+cudaError_t launch_feature_scales(float* scales, cudaStream_t stream) {
+  feature_scales_kernel<<<1, 1, 0, stream>>>(scales);
+  return cudaGetLastError();
+}
+cudaError_t launch_grad_scales(float* scales, cudaStream_t stream) {
+  grad_scales_kernel<<<1, 1, 0, stream>>>(scales);
+  return cudaGetLastError();
+}
+
+// `outh` (optional): the same values as 16-bit operands of kind `op16` instead (BF16, or FP16 of the value times the
+// device scalar *scale16).
+__global__ void round_copy_kernel(const float4* __restrict__ in, float4* __restrict__ out, size_t n4,
+                                  uint2* __restrict__ outh, int op16, const float* __restrict__ scale16) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const float sc = (outh != nullptr && scale16 != nullptr) ? __ldg(scale16) : 1.f;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
     float4 v = __ldg(in + i);
     if (outh != nullptr) {
-      const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-      outh[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+      if (op16 == OP16_FP16) outh[i] = make_uint2(pack_fp16x2(v.x * sc, v.y * sc), pack_fp16x2(v.z * sc, v.w * sc));
+      else outh[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
     }
     v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w);
     out[i] = v;
@@ -31,7 +102,7 @@ __global__ void round_copy_kernel(const float4* __restrict__ in, float4* __restr
 
 // grid (H2 + W2, B), block = min(C, 256) threads over channels.
 __global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict__ aux, int H2, int W2, int C,
-                                __nv_bfloat16* __restrict__ auxh) {
+                                uint16_t* __restrict__ auxh, int op16, const float* __restrict__ scale16) {
   const int r = blockIdx.x, b = blockIdx.y;
   const float* base = F2 + (size_t)b * H2 * W2 * C;
   float* dst = aux + ((size_t)b * (H2 + W2) + r) * C;
@@ -47,7 +118,8 @@ __global__ void f2_means_kernel(const float* __restrict__ F2, float* __restrict_
       acc /= (float)H2;
     }
     dst[c] = round_tf32(acc);
-    if (auxh != nullptr) auxh[((size_t)b * (H2 + W2) + r) * C + c] = __float2bfloat16_rn(acc);
+    if (auxh != nullptr)
+      auxh[((size_t)b * (H2 + W2) + r) * C + c] = to_op16(op16 == OP16_FP16 && scale16 != nullptr ? acc * __ldg(scale16) : acc, op16);
   }
 }
 
@@ -123,6 +195,7 @@ __global__ void pack_interleaved_kernel(const SlotSources src, uint32_t* __restr
         } else {
           v = __ldg(s + (((size_t)b * N1 + p) * src.s[r].Ksrc + src.s[r].k) * D + d);
           if (src.s[r].scale != 0.f) v = __float_as_uint(__uint_as_float(v) * src.s[r].scale);
+          if (src.s[r].dev != 0) v = __float_as_uint(__uint_as_float(v) * __ldg(src.dev_scales + src.s[r].dev - 1));
         }
       }
       tile[r * RS + j * 33 + tx] = v;
@@ -185,6 +258,7 @@ __global__ void pack_interleaved_cf_kernel(const SlotSources src, float4* __rest
       for (int j = 0; j < 4; ++j) {
         const SlotSource& ss = src.s[4 * q + j];
         v[j] = (ss.scale != 0.f && ss.src != nullptr) ? __uint_as_float(w[i][q][j]) * ss.scale : __uint_as_float(w[i][q][j]);
+        if (ss.dev != 0 && ss.src != nullptr) v[j] *= __ldg(src.dev_scales + ss.dev - 1);
       }
       dst[(((size_t)b * D + d0 + i) * Qtot + q0 + q) * n1p + p] = make_float4(v[0], v[1], v[2], v[3]);
     }
@@ -220,8 +294,10 @@ cudaError_t launch_unpack(const float* src, void* dst, int B, int N1, int n1p, i
 // (B, C, N) -> (B, N, C), scaled and rounded to TF32.  32 x 32 tiles through shared memory; grid
 // (ceil(N/32), ceil(C/32), B), block (32, 8).
 __global__ void transpose_round_kernel(const float* __restrict__ in, float* __restrict__ out, int C, int N,
-                                       float scale, __nv_bfloat16* __restrict__ outh) {
+                                       float scale, uint16_t* __restrict__ outh, int op16,
+                                       const float* __restrict__ scale16) {
   __shared__ float tile[32][33];
+  const float sc16 = (outh != nullptr && op16 == OP16_FP16 && scale16 != nullptr) ? __ldg(scale16) : 1.f;
   const int b = blockIdx.z, p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
   const int tx = threadIdx.x, ty = threadIdx.y;
 #pragma unroll
@@ -236,7 +312,7 @@ __global__ void transpose_round_kernel(const float* __restrict__ in, float* __re
     if (p < N && c < C) {
       const float v = tile[tx][j] * scale;
       out[((size_t)b * N + p) * C + c] = round_tf32(v);
-      if (outh != nullptr) outh[((size_t)b * N + p) * C + c] = __float2bfloat16_rn(v);
+      if (outh != nullptr) outh[((size_t)b * N + p) * C + c] = to_op16(v * sc16, op16);
     }
   }
 }
@@ -249,8 +325,9 @@ __global__ void transpose_round_kernel(const float* __restrict__ in, float* __re
 // ceil(C/32), B*rows), block (32, 8).
 template <typename T>
 __global__ void channel_major_kernel(const float* __restrict__ in, T* __restrict__ out, int rows, int width,
-                                     int pitch, int C, int blocked) {
+                                     int pitch, int C, int blocked, int op16, const float* __restrict__ scale16) {
   __shared__ float tile[32][33];
+  const float sc16 = (op16 == OP16_FP16 && scale16 != nullptr) ? __ldg(scale16) : 1.f;
   const int b = blockIdx.z / rows, row = blockIdx.z - b * rows, x0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
   const int tx = threadIdx.x, ty = threadIdx.y;
   const float* src = in + ((size_t)b * rows + row) * width * C;
@@ -266,57 +343,72 @@ __global__ void channel_major_kernel(const float* __restrict__ in, T* __restrict
     const int c = c0 + j, x = x0 + tx;
     if (c < C && x < width) {
       const size_t off = blocked ? ((size_t)(x >> 4) * pitch + row) * 16 + (x & 15) : (size_t)x;
-      if constexpr (sizeof(T) == 2) out[((size_t)b * C + c) * per_channel + off] = __float2bfloat16_rn(tile[tx][j]);
+      if constexpr (sizeof(T) == 2) out[((size_t)b * C + c) * per_channel + off] = to_op16(tile[tx][j] * sc16, op16);
       else out[((size_t)b * C + c) * per_channel + off] = tile[tx][j];
     }
   }
 }
 
 cudaError_t launch_channel_major(const float* src, void* dst, int B, int rows, int width, int pitch, int C,
-                                 int blocked, int bf16, cudaStream_t stream) {
+                                 int blocked, int op16, const float* scale16, cudaStream_t stream) {
   const dim3 grid((width + 31) / 32, (C + 31) / 32, B * rows), block(32, 8);
-  if (bf16)
-    channel_major_kernel<<<grid, block, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), rows, width, pitch, C, blocked);
+  if (op16)
+    channel_major_kernel<<<grid, block, 0, stream>>>(src, static_cast<uint16_t*>(dst), rows, width, pitch, C, blocked,
+                                                     op16, scale16);
   else
-    channel_major_kernel<<<grid, block, 0, stream>>>(src, static_cast<float*>(dst), rows, width, pitch, C, blocked);
+    channel_major_kernel<<<grid, block, 0, stream>>>(src, static_cast<float*>(dst), rows, width, pitch, C, blocked, 0,
+                                                     nullptr);
   return cudaGetLastError();
+}
+
+// Clears the workspace header (status word and scale slots) and, for FP16 operands, finds the two feature scales.
+static cudaError_t begin_prepare(const Dims& d, const float* F1, const float* F2, float premul1, int* status, int op16,
+                                 float* scales, cudaStream_t stream) {
+  cudaError_t err = cudaMemsetAsync(status, 0, WS_HEADER_CLEAR_BYTES, stream);
+  if (err != cudaSuccess || op16 != OP16_FP16 || scales == nullptr) return err;
+  launch_absmax(F1, (size_t)d.B * d.N1() * d.C, premul1, scales + SCALE_AMAX_F1, stream);
+  launch_absmax(F2, (size_t)d.B * d.N2() * d.C, 1.f, scales + SCALE_AMAX_F2, stream);
+  return launch_feature_scales(scales, stream);
 }
 
 cudaError_t launch_prepare_cf(const Dims& d, const float* fmap1, const float* fmap2, float scale1, float* F1r,
                               float* F2r, float* aux, int* status, cudaStream_t stream, uint16_t* F1h, uint16_t* F2h,
-                              uint16_t* auxh) {
-  cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), stream);
+                              uint16_t* auxh, int op16, float* scales) {
+  cudaError_t err = begin_prepare(d, fmap1, fmap2, scale1, status, op16, scales, stream);
   if (err != cudaSuccess) return err;
+  const float* s1 = (op16 == OP16_FP16 && scales != nullptr) ? scales + SCALE_F1 : nullptr;
+  const float* s2 = (op16 == OP16_FP16 && scales != nullptr) ? scales + SCALE_F2 : nullptr;
   const dim3 block(32, 8);
   transpose_round_kernel<<<dim3((d.N1() + 31) / 32, (d.C + 31) / 32, d.B), block, 0, stream>>>(
-      fmap1, F1r, d.C, d.N1(), scale1, reinterpret_cast<__nv_bfloat16*>(F1h));
+      fmap1, F1r, d.C, d.N1(), scale1, F1h, op16, s1);
   transpose_round_kernel<<<dim3((d.N2() + 31) / 32, (d.C + 31) / 32, d.B), block, 0, stream>>>(
-      fmap2, F2r, d.C, d.N2(), 1.f, reinterpret_cast<__nv_bfloat16*>(F2h));
+      fmap2, F2r, d.C, d.N2(), 1.f, F2h, op16, s2);
   if (aux != nullptr) {  // mean rows from the transposed copy (already rounded: the means differ by < 2^-12 relative)
     const dim3 grid(d.H2 + d.W2, d.B);
-    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2r, aux, d.H2, d.W2, d.C,
-                                                             reinterpret_cast<__nv_bfloat16*>(auxh));
+    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2r, aux, d.H2, d.W2, d.C, auxh, op16, s2);
   }
   return cudaGetLastError();
 }
 
 cudaError_t launch_prepare(const Dims& d, const float* F1, const float* F2, float* F1r, float* F2r, float* aux,
-                           int* status, cudaStream_t stream, uint16_t* F1h, uint16_t* F2h, uint16_t* auxh) {
-  cudaError_t err = cudaMemsetAsync(status, 0, sizeof(int), stream);
+                           int* status, cudaStream_t stream, uint16_t* F1h, uint16_t* F2h, uint16_t* auxh, int op16,
+                           float* scales) {
+  cudaError_t err = begin_prepare(d, F1, F2, 1.f, status, op16, scales, stream);
   if (err != cudaSuccess) return err;
+  const float* s1 = (op16 == OP16_FP16 && scales != nullptr) ? scales + SCALE_F1 : nullptr;
+  const float* s2 = (op16 == OP16_FP16 && scales != nullptr) ? scales + SCALE_F2 : nullptr;
   const size_t n1 = (size_t)d.B * d.N1() * d.C / 4, n2 = (size_t)d.B * d.N2() * d.C / 4;  // C % 4 == 0
   const int threads = 256;
   auto blocks = [&](size_t n) { return (unsigned)std::min<size_t>((n + threads - 1) / threads, 148 * 16); };
   round_copy_kernel<<<blocks(n1), threads, 0, stream>>>(reinterpret_cast<const float4*>(F1),
                                                         reinterpret_cast<float4*>(F1r), n1,
-                                                        reinterpret_cast<uint2*>(F1h));
+                                                        reinterpret_cast<uint2*>(F1h), op16, s1);
   round_copy_kernel<<<blocks(n2), threads, 0, stream>>>(reinterpret_cast<const float4*>(F2),
                                                         reinterpret_cast<float4*>(F2r), n2,
-                                                        reinterpret_cast<uint2*>(F2h));
+                                                        reinterpret_cast<uint2*>(F2h), op16, s2);
   if (aux != nullptr) {
     const dim3 grid(d.H2 + d.W2, d.B);
-    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2, aux, d.H2, d.W2, d.C,
-                                                             reinterpret_cast<__nv_bfloat16*>(auxh));
+    f2_means_kernel<<<grid, std::min(d.C, 256), 0, stream>>>(F2, aux, d.H2, d.W2, d.C, auxh, op16, s2);
   }
   return cudaGetLastError();
 }

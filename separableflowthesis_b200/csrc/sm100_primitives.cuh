@@ -204,6 +204,17 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// The same to FP16.
+__device__ __forceinline__ uint32_t pack_fp16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// One value to the 16-bit operand kind `op16` (OP16_BF16 / OP16_FP16), as bits.
+__device__ __forceinline__ uint16_t to_op16(float v, int op16) {
+  const uint32_t r = op16 == 2 ? pack_fp16x2(v, 0.f) : pack_bf16x2(v, 0.f);
+  return static_cast<uint16_t>(r & 0xFFFFu);
+}
 
 // 16 consecutive 32-bit TMEM columns of this thread's lane -> 16 registers (whole warp).
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
@@ -316,6 +327,18 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, bool a_mn_m
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
          (static_cast<uint32_t>(M >> 4) << 24);
+}
+// The same with FP16 A and B (format code 0).
+__host__ __device__ constexpr uint32_t make_idesc_fp16(int M, int N) {
+  return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+// 16-bit operand kinds of the contractions (0 = none: TF32 operands in FP32 storage).
+#ifndef SFB_OP16_KINDS
+#define SFB_OP16_KINDS
+enum : int { OP16_NONE = 0, OP16_BF16 = 1, OP16_FP16 = 2 };
+#endif
+__host__ __device__ constexpr uint32_t make_idesc_op16(int op16, int M, int N) {
+  return op16 == OP16_FP16 ? make_idesc_fp16(M, N) : make_idesc_bf16(M, N);
 }
 
 // Round-to-nearest (ties away from zero) to TF32's 10 mantissa bits.  Same result as cvt.rna.tf32.f32 for

@@ -66,7 +66,7 @@ struct SweepSched {
 // ---------------------------------------------------------------------------------- producer
 __device__ void sweep_producer(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc, const CUtensorMap* tm_f1,
                                const CUtensorMap* tm_f2, const CUtensorMap* tm_aux) {
-  const int kel = a.bf16 ? 2 * KBLK : KBLK;  // channels in one 128-byte row
+  const int kel = a.op16 ? 2 * KBLK : KBLK;  // channels in one 128-byte row
   mbar_expect_tx(&sm.f1_full, sc.nkb * SW_F1_BLOCK_BYTES);
   for (int kb = 0; kb < sc.nkb; ++kb) tma_load_3d(sm.f1[kb], tm_f1, &sm.f1_full, kb * kel, sc.m0, sc.b);
   uint32_t it = 0;
@@ -90,8 +90,8 @@ __device__ void sweep_producer(SweepSmem& sm, const SweepArgs& a, const SweepSch
 // ---------------------------------------------------------------------------------- MMA issuer
 __device__ void sweep_mma(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc) {
   constexpr uint32_t idesc_tf32 = make_idesc_tf32(TILE_M, SW_TILE_N, false, false);
-  constexpr uint32_t idesc_bf16 = make_idesc_bf16(TILE_M, SW_TILE_N);
-  const bool bf16 = a.bf16 != 0;
+  const uint32_t idesc_bf16 = make_idesc_op16(a.op16, TILE_M, SW_TILE_N);  // BF16 or FP16 operands
+  const bool bf16 = a.op16 != 0;
   if (!mbar_wait(&sm.f1_full, 0, &sm.ctl, a.status, DEV_TIMEOUT_MMA)) return;
   tc_fence_after();
   uint32_t it = 0;
@@ -128,6 +128,8 @@ struct EpiCtx {
   int p;            // pixel index inside the sample: m0 + 32*quarter + lane
   bool valid;       // p < n_valid: lanes past the end compute but never touch memory
   uint32_t tbase;   // TMEM address of this warp's lane quarter, column 0
+  float osc;        // every stored value is multiplied by this (1, or the inverse of the FP16 operands' scaling: a
+                    // power of two, so the order of values and exact ties are unchanged)
 };
 
 // Waits for accumulator `t`; the result is warp-uniform so that the warp-collective tcgen05.ld that
@@ -222,6 +224,7 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
 #pragma unroll
             for (int j = 0; j < SWEEP_VT; ++j) cm[j] = fmaxf(cm[j], r[j]);
           }
+          m *= e.osc;  // memory holds scaled-back values; compare and store in that domain
           if (valid && (vb == 0 || m > rold[ul])) {  // strict: the lowest column block wins ties
             pu[u * usd] = m;
             if (ARG) pua[u * uasd] = __int_as_float(v0 + arg);
@@ -236,7 +239,7 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
 #pragma unroll
         for (int j = 0; j < SWEEP_VT; ++j) {
           if (valid && j < nv) {
-            pv[(v0 + j) * vsd] = cm[j];
+            pv[(v0 + j) * vsd] = cm[j] * e.osc;
             if (ARG) pva[(v0 + j) * vasd] = __int_as_float(ca[j]);
           }
         }
@@ -251,7 +254,7 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
           if (valid && j < nv) {
             float* dst = pv + (v0 + j) * vsd;
             const float om = __ldcg(dst);
-            float best = cm[j];
+            float best = cm[j] * e.osc;
             int besta = ca[j];
             if (ARG) {
               float* dsta = pva + (v0 + j) * vasd;
@@ -283,8 +286,8 @@ __device__ void epilogue_maxavg(SweepSmem& sm, const SweepArgs& a, const SweepSc
         for (int j = 0; j < 64; ++j) {
           const int r = r0 + j;
           if (!valid) continue;
-          if (r < H2) pu[r * usd + uss] = s[j];
-          else if (r < naux) pv[(r - H2) * vsd + vss] = s[j];
+          if (r < H2) pu[r * usd + uss] = s[j] * e.osc;
+          else if (r < naux) pv[(r - H2) * vsd + vss] = s[j] * e.osc;
         }
       }
     }
@@ -356,7 +359,7 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
           }
           if (valid && ul < nu) {
             float* dst = ou_t + ul * ousd;
-            const float r = sum2(r2);
+            const float r = sum2(r2) * e.osc;
             if (first) *dst = r;
             else atomicAdd(dst, r);  // same thread, same address in every column block: ordered
           }
@@ -371,8 +374,8 @@ __device__ void epilogue_compress(SweepSmem& sm, const SweepArgs& a, const Sweep
       for (int j = 0; j < SWEEP_VT / 2; ++j) {
         float lo, hi;
         unpack2(cv2[j], lo, hi);
-        if (valid && 2 * j < nv) ov_t[(2 * j) * ovsd] = lo;
-        if (valid && 2 * j + 1 < nv) ov_t[(2 * j + 1) * ovsd] = hi;
+        if (valid && 2 * j < nv) ov_t[(2 * j) * ovsd] = lo * e.osc;
+        if (valid && 2 * j + 1 < nv) ov_t[(2 * j + 1) * ovsd] = hi * e.osc;
       }
     }
     if (++ub == sc.n_ub) { ub = 0; ++vb; }
@@ -401,7 +404,7 @@ __device__ void epilogue_dump(SweepSmem& sm, const SweepArgs& a, const SweepSche
 #pragma unroll
           for (int j = 0; j < SWEEP_VT; ++j) {
             const int ul = half * (SW_RW / 2) + hl;
-            if (ul < nu && j < nv) out[(size_t)(ubase + ul) * W2 + v0 + j] = s[hl * SWEEP_VT + j];
+            if (ul < nu && j < nv) out[(size_t)(ubase + ul) * W2 + v0 + j] = s[hl * SWEEP_VT + j] * e.osc;
           }
       }
     }
@@ -426,7 +429,7 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
   SweepSched sc;
   sc.b = blockIdx.x / tiles_per_sample;
   sc.m0 = (blockIdx.x - sc.b * tiles_per_sample) * TILE_M;
-  sc.nkb = a.bf16 ? (a.d.C + 2 * KBLK - 1) / (2 * KBLK) : (a.d.C + KBLK - 1) / KBLK;
+  sc.nkb = a.op16 ? (a.d.C + 2 * KBLK - 1) / (2 * KBLK) : (a.d.C + KBLK - 1) / KBLK;
   sc.n_ub = (a.d.H2 + SWEEP_UT - 1) / SWEEP_UT;
   sc.n_vb = (a.d.W2 + SWEEP_VT - 1) / SWEEP_VT;
   sc.t_main = sc.n_ub * sc.n_vb;
@@ -466,6 +469,7 @@ sweep_kernel(const __grid_constant__ CUtensorMap tm_f1, const __grid_constant__ 
     e.p = sc.m0 + q * 32 + lane;
     e.valid = e.p < a.n_valid;
     e.tbase = sm.tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    e.osc = a.out_scale != nullptr ? __ldg(a.out_scale) : 1.f;
     if (MODE == SWEEP_MAXAVG) epilogue_maxavg<false>(sm, a, sc, e);
     else if (MODE == SWEEP_MAXARGAVG) epilogue_maxavg<true>(sm, a, sc, e);
     else if (MODE == SWEEP_COMPRESS) epilogue_compress(sm, a, sc, e);

@@ -585,12 +585,14 @@ def lookup_backward(corr_shape, coord, grad_out, levels=4, radius=4, clamp_unit=
 
 class sweep_operands:
     """Context manager / setter for the operand type of every contraction (correlation sweeps and gradient GEMMs) of
-    the ops and the level calls: ``with ops.sweep_operands("bf16"): ...`` (process-wide; "tf32" is the default)."""
-    _codes = {"tf32": 0, "bf16": 1}
+    the ops and the level calls: ``with ops.sweep_operands("tf32"): ...`` (process-wide).  "fp16" is the default (TF32's
+    mantissa at twice the tensor-core rate, inputs scaled by powers of two on the device), "tf32" the same precision
+    without scaling, "bf16" the lower-precision type of BASELINE's bf16 configuration."""
+    _codes = {"tf32": 0, "bf16": 1, "fp16": 2}
 
     def __init__(self, kind: str):
         if kind not in self._codes:
-            raise ValueError(f"operand type must be 'tf32' or 'bf16', got {kind!r}")
+            raise ValueError(f"operand type must be 'tf32', 'bf16' or 'fp16', got {kind!r}")
         self.prev = _lib.load().sfb_set_sweep_operands(self._codes[kind])
 
     def __enter__(self):

@@ -8,8 +8,9 @@ chunks) runs on the GPU in FP32 with TF32 switched off everywhere; its own error
 tolerances below.  The comparison is the one the reference's tests make (scripts/test_compression_autograd.py:442-484,
 scripts/test_model.py:251-256): max |x - ref| over max(|x|max, |ref|max).
 
-Tolerances: 1e-3 for gradients and attention gradients (TF32 operands, FP32 accumulation), 2e-3 for whole-level
-outputs (their attention weights are a softmax of TF32-grade max/avg values); for BF16 sweep operands 2e-5 on
+Tolerances: 1e-3 for gradients and attention gradients (FP16 operands by default, TF32 on request: both keep 10
+mantissa bits; FP32 accumulation), 2e-3 for whole-level outputs (their attention weights are a softmax of
+max/avg values of that accuracy); for BF16 operands 2e-5 on
 the max channel against the oracle on BF16-rounded features (products of BF16 values are exact in FP32), 4e-3 on the
 other forward outputs and 1e-2 on the backward against the unrounded oracle.
 """
@@ -169,3 +170,62 @@ def test_five_ops_with_bf16_operands(shape, cuda_device):
     rc = orc.compression_backward(F1, F2, A_u, A_v, gC_u, gC_v)
     for name, x, r in zip(("gF1", "gF2", "gA_u", "gA_v"), (gF1c, gF2c, gA_u, gA_v), rc):
         assert relerr(x, r) < 1e-2, name
+
+
+@pytest.mark.parametrize("kind", ["tf32", "fp16"])
+def test_level_with_each_10_bit_operand_type(kind, cuda_device):
+    """The default (FP16 operands with per-tensor power-of-two scaling) and the TF32 path, one sample at BASELINE
+    config 4's size, against the same oracle with the same tolerances."""
+    no_tf32()
+    F1, F2, params, gu, gv = level_inputs(1, 47, 156, 256, 2, cuda_device, seed=504)
+    with ops.sweep_operands(kind):
+        check_level(F1, F2, params, gu, gv, fmaps=False)
+        check_level(F1, F2, params, gu, gv, fmaps=True)
+
+
+@pytest.mark.parametrize("scales", [(1e4, 3e3, 1e-7), (1e-5, 1e-6, 1e5), (1.0, 1.0, 1e-10)])
+def test_fp16_operands_follow_the_scale_of_the_inputs(scales, cuda_device):
+    """FP16 has five exponent bits; the library multiplies every tensor that becomes an FP16 operand by a power of two
+    found on the device from its largest magnitude, and undoes it when results are stored.  Features and upstream
+    gradients far outside FP16's range must therefore give the same accuracy as at unit scale (the attention filters are
+    scaled inversely so that the softmax stays unsaturated)."""
+    no_tf32()
+    fs1, fs2, gs = scales
+    F1, F2, params, gu, gv = level_inputs(1, 24, 40, 256, 2, cuda_device, seed=505)
+    wu, bu, wv, bv = params
+    params = [wu / (fs1 * fs2), bu, wv / (fs1 * fs2), bv]
+    with ops.sweep_operands("fp16"):
+        check_level(F1 * fs1, F2 * fs2, params, gu * gs, gv * gs, fmaps=False)
+
+
+def test_five_ops_with_tf32_and_fp16_operands_agree(cuda_device):
+    """The five reference-layout ops under the two 10-bit operand types, including weights far above 1 in the
+    compression backward (the weights of that op need not be softmax outputs): each within 1e-3 of the oracle."""
+    no_tf32()
+    B, H1, W1, H2, W2, C, Kc = 1, 13, 22, 11, 19, 64, 3
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(602)
+    F1 = torch.randn(B, H1, W1, C, generator=g, device=dev) / C ** 0.5
+    F2 = torch.randn(B, H2, W2, C, generator=g, device=dev)
+    A_u = torch.randn(B, H1, W1, Kc, W2, generator=g, device=dev) * 300.0
+    A_v = torch.randn(B, H1, W1, Kc, H2, generator=g, device=dev) * 300.0
+    gMA_u = torch.randn(B, H1, W1, 2, H2, generator=g, device=dev) * 1e-6
+    gMA_v = torch.randn(B, H1, W1, 2, W2, generator=g, device=dev) * 1e-6
+    gC_u = torch.randn(B, H1, W1, Kc, H2, generator=g, device=dev) * 1e-6
+    gC_v = torch.randn(B, H1, W1, Kc, W2, generator=g, device=dev) * 1e-6
+    _, _, AM_u, AM_v = orc.max_argmax_avg_forward(F1, F2)
+    r_ma = orc.max_argmax_avg_forward(F1, F2)
+    r_c = orc.compression_forward(F1, F2, A_u, A_v)
+    r_mb = orc.max_argmax_avg_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v)
+    r_cb = orc.compression_backward(F1, F2, A_u, A_v, gC_u, gC_v)
+    r_sb = orc.separation_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v)
+    for kind in ("tf32", "fp16"):
+        with ops.sweep_operands(kind):
+            ma = ops.max_argmax_avg_forward(F1, F2)
+            c = ops.compression_forward(F1, F2, A_u, A_v)
+            mb = ops.max_argmax_avg_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v)
+            cb = ops.compression_backward(F1, F2, A_u, A_v, gC_u, gC_v)
+            sb = ops.separation_backward(F1, F2, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v)
+        for got, ref in ((ma[:2], r_ma[:2]), (c, r_c), (mb, r_mb), (cb, r_cb), (sb, r_sb)):
+            for x, r in zip(got, ref):
+                assert relerr(x, r) < TOL, kind

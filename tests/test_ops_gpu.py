@@ -483,8 +483,8 @@ def test_separation_level_with_bf16_sweep_operands(shape, cuda_device):
     """BF16 operands in the sweeps of the level calls (BASELINE's bf16 configuration): products of BF16 values are
     exact in FP32, so the max channel must match the float64 oracle evaluated on the BF16-rounded features to
     accumulation-order accuracy; the mean rows of F2 are rounded once more (BF16), which the mean, attention and
-    compression channels inherit; the backward (TF32 gradient GEMMs on the unrounded features, BF16 attention-
-    gradient sweep) stays within BF16 accuracy of the TF32 path."""
+    compression channels inherit; the backward (BF16 gradient GEMMs and attention-gradient sweep) stays within BF16
+    accuracy of the default path."""
     B, H1, W1, H2, W2, C, Kc = shape
     F1, F2, _, _, g = make_inputs(shape, 23)
     params = [torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(Kc, generator=g) * 0.1,
@@ -492,12 +492,13 @@ def test_separation_level_with_bf16_sweep_operands(shape, cuda_device):
     dev = cuda_device
     F1d, F2d = F1.to(dev), F2.to(dev)
     wu, bu, wv, bv = [t.to(dev) for t in params]
+    before = _lib_operands()
     with ops.sweep_operands("bf16"):
         fw = ops.separation_level_forward(F1d, F2d, wu, bu, wv, bv)
         g_sep_u = torch.randn(fw[0].shape, generator=g).to(dev)
         g_sep_v = torch.randn(fw[1].shape, generator=g).to(dev)
         bw = ops.separation_level_backward(F1d, F2d, wu, wv, *fw, g_sep_u, g_sep_v)
-    assert _lib_operands() == 0                                   # restored
+    assert _lib_operands() == before == 2                         # restored to the default, FP16
     F1b, F2b = F1.bfloat16().double(), F2.bfloat16().double()
     ref = orc.separation_level_forward(F1b, F2b, *[t.double() for t in params])
     assert relerr(fw[0][:, 0], ref[0][:, 0]) < 2e-5 and relerr(fw[1][:, 0], ref[1][:, 0]) < 2e-5

@@ -48,8 +48,14 @@ def run_block(f1, f2, convs, gu, gv, keep=None):
             [c.bias.grad.clone() for c in convs])
 
 
-@pytest.mark.parametrize("blocks", [2, 3])
-def test_row_blocks_combine_to_the_unsharded_result(blocks, cuda_device):
+@pytest.mark.parametrize("blocks,kind", [(2, "tf32"), (3, "tf32"), (2, "fp16"), (3, "fp16")])
+def test_row_blocks_combine_to_the_unsharded_result(blocks, kind, cuda_device):
+    from separableflowthesis_b200 import ops
+    with ops.sweep_operands(kind):
+        _row_blocks_combine(blocks, kind, cuda_device)
+
+
+def _row_blocks_combine(blocks, kind, cuda_device):
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
     dev = cuda_device
@@ -81,10 +87,15 @@ def test_row_blocks_combine_to_the_unsharded_result(blocks, cuda_device):
         for i in range(2):
             gw[i] += part[4][i]
             gb[i] += part[5][i]
-    # Same sweeps on the same features: the outputs are identical.  The gradients are not bit-identical: at a block
-    # border dLoss/dS of a pixel is the sum of what two blocks generate (the stencil's transpose reaches across the
-    # border), and each part is rounded to TF32 on its own before its GEMM.
-    assert torch.equal(su, full[0]) and torch.equal(sv, full[1])
+    # Same sweeps on the same features: with TF32 operands the outputs are identical.  With FP16 operands a block's
+    # image-1 rows get their own power-of-two scale; scaling is exact except for the few values that land in FP16's
+    # subnormal range under one scale and not the other, so the outputs agree to 1e-6 instead of bit for bit.  The
+    # gradients are not bit-identical either way: at a block border dLoss/dS of a pixel is the sum of what two blocks
+    # generate (the stencil's transpose reaches across the border), and each part is rounded on its own before its GEMM.
+    if kind == "tf32":
+        assert torch.equal(su, full[0]) and torch.equal(sv, full[1])
+    else:
+        assert relerr(su, full[0]) < 1e-6 and relerr(sv, full[1]) < 1e-6
     errs = {"g_fmap1": relerr(g1, full[2]), "g_fmap2": relerr(g2, full[3]), "g_weight1": relerr(gw[0], full[4][0]),
             "g_weight2": relerr(gw[1], full[4][1])}
     assert max(errs.values()) < 1e-3, errs
