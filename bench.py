@@ -39,7 +39,8 @@ C_FEAT = 256
 SEED = 1234  # the reference's default seed (train.py:52)
 
 # DRAM bytes per cell (dram__bytes_read.sum + dram__bytes_write.sum of one launch / cells of that launch)
-# from the ncu captures summarised under profiles/; traffic grows in proportion to the cells swept.
+# from the ncu captures summarised under profiles/ (one table per operand width); traffic grows in proportion to
+# the cells swept.
 DRAM_BYTES_PER_CELL = {}
 try:
     with open(os.path.join(ROOT, "profiles", "dram_bytes_per_cell.json")) as _f:
@@ -1043,7 +1044,7 @@ def main():
         dominant = max(per_kernel, key=lambda k: k["share"])
         worst = min(per_kernel, key=lambda k: k["achieved"])
         peak = file_sust if file_sust else (f16c_sust if op16 else tf32_sust)
-        bpc = DRAM_BYTES_PER_CELL.get(dominant["kernel"])
+        bpc = DRAM_BYTES_PER_CELL.get("16bit_operands" if op16 else "tf32_operands", {}).get(dominant["kernel"])
         roofline = {"bound": "tensor", "kernel": dominant["kernel"], "achieved": dominant["achieved"], "peak": peak,
                     "unit": "TFLOP/s", "frac": dominant["achieved"] / peak,
                     "traffic": (bpc * job["cells"]) if bpc else None,

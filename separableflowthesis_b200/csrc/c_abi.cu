@@ -446,7 +446,7 @@ int run_maxavg_forward(const float* F1, const float* F2, float* MA_u, float* MA_
   SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2, tm_aux;
   SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, &tm_aux));
-  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return prepare_operands(d, w, F1, F2, true, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 3 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, true, op16, st); }));
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
@@ -754,7 +754,7 @@ int sfb_compression_forward(const float* F1, const float* F2, const float* A_u, 
   SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   const int N1 = d.N1(), K = d.Kc;
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
     launch_pack(A_u, w.xv, d.B, N1, w.n1p, K, 0, K, d.W2, K, 0, 1, 0.f, st);         // w_u[k][v] = XV slot k
@@ -781,7 +781,7 @@ int sfb_max_argmax_avg_backward(const float* F1, const float* F2, const int32_t*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int op16;
   SFB_TRY(operand_mode(d, &op16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   const size_t pix = (size_t)d.B * d.N1();
   SFB_TRY(grad_operand_scales(w, op16, {{gMA_u, pix * 2 * d.H2}, {gMA_v, pix * 2 * d.W2}}, {}, st));
   SFB_CUDA(timed(KID_PACK, 2, st, [&] {
@@ -806,7 +806,7 @@ int sfb_compression_backward(const float* F1, const float* F2, const float* A_u,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int op16;
   SFB_TRY(operand_mode(d, &op16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   const int N1 = d.N1(), K = d.Kc;
   SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, op16));
   {
@@ -838,7 +838,7 @@ int sfb_compression_attention_backward(const float* F1, const float* F2, const f
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int op16;
   SFB_TRY(operand_mode(d, &op16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   return run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, op16);
 }
 
@@ -896,7 +896,7 @@ int sfb_separation_feature_backward(const float* F1, const float* F2, const int3
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int op16;
   SFB_TRY(operand_mode(d, &op16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
 }
 
@@ -915,7 +915,7 @@ int sfb_separation_backward(const float* F1, const float* F2, const int32_t* AM_
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int op16;
   SFB_TRY(operand_mode(d, &op16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   SFB_TRY(run_attention_grads(d, w, gC_u, gC_v, gA_u, gA_v, st, op16));
   return run_fused_feature_grads(d, w, AM_u, AM_v, gMA_u, gMA_v, A_u, A_v, gC_u, gC_v, gF1, gF2, st);
 }
@@ -935,7 +935,7 @@ int sfb_max_argmax_avg_forward_cf(const float* F1, const float* F2, float* SEP_v
   SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2, tm_aux;
   SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, &tm_aux));
-  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] { return prepare_operands(d, w, F1, F2, true, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 3 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, true, op16, st); }));
   const int N1 = d.N1();
   SweepArgs a;
   memset(&a, 0, sizeof(a));
@@ -967,7 +967,7 @@ static int run_compress_cf(const float* F1, const float* F2, const float* W_u, c
   SFB_TRY(operand_mode(d, &op16));
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   const int N1 = d.N1(), K = d.Kc;
   // W_u (B,K,W2,N1) weights per v, W_v (B,K,H2,N1) per u; O_u (B,K,H2,N1), O_v (B,K,W2,N1)
   return run_compress_sweeps(d, w.status, tm_f1, tm_f2, cf_view(W_v, K, d.H2, N1), cf_view(W_u, K, d.W2, N1), 0, 0, 1,
@@ -1047,7 +1047,7 @@ int sfb_separation_feature_backward_cf(const float* F1, const float* F2, const i
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int op16;
   SFB_TRY(operand_mode(d, &op16));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   return run_fused_feature_grads_cf(d, w, AM_u, AM_v, gSEP_v, gSEP_u, A_u, A_v, gC_u, gC_v, d.Kc, 0, gF1, gF2, st);
 }
 
@@ -1148,7 +1148,7 @@ static int level_forward(Placement pl, const float* F1, const float* F2, int fma
   uint16_t* const F1h = op16 ? w.F1h : nullptr;
   uint16_t* const F2h = op16 ? w.F2h : nullptr;
   uint16_t* const auxh = op16 ? w.auxh : nullptr;
-  SFB_CUDA(timed(KID_PREPARE, 3, st, [&] {
+  SFB_CUDA(timed(KID_PREPARE, 3 + (op16 == OP16_FP16 ? 3 : 0), st, [&] {
     return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, w.aux, w.status, st, F1h, F2h, auxh, op16, w.scales)
                  : launch_prepare(d, F1, F2, w.F1r, w.F2r, w.aux, w.status, st, F1h, F2h, auxh, op16, w.scales);
   }));
@@ -1221,7 +1221,7 @@ static int level_backward(Placement pl, const float* F1, const float* F2, int fm
   SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
   uint16_t* const F1h = op16 ? w.F1h : nullptr;
   uint16_t* const F2h = op16 ? w.F2h : nullptr;
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] {
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] {
     return fmaps ? launch_prepare_cf(d, F1, F2, scale1, w.F1r, w.F2r, nullptr, w.status, st, F1h, F2h, nullptr, op16, w.scales)
                  : launch_prepare(d, F1, F2, w.F1r, w.F2r, nullptr, w.status, st, F1h, F2h, nullptr, op16, w.scales);
   }));
@@ -1437,7 +1437,7 @@ int sfb_corr_volume(const float* F1, const float* F2, float* S, const sfb_shape*
   const int op16 = OP16_NONE;  // this test aid always computes with TF32 operands (its workspace has no 16-bit copies)
   CUtensorMap tm_f1, tm_f2;
   SFB_TRY(map_sweep_operands(d, w, op16, &tm_f1, &tm_f2, nullptr));
-  SFB_CUDA(timed(KID_PREPARE, 2, st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
+  SFB_CUDA(timed(KID_PREPARE, 2 + (op16 == OP16_FP16 ? 3 : 0), st, [&] { return prepare_operands(d, w, F1, F2, false, op16, st); }));
   SweepArgs a;
   memset(&a, 0, sizeof(a));
   a.d = d;
