@@ -522,7 +522,9 @@ class E2E:
                     conv.bias.copy_(params[2 * i + 1])
                 self.att.append(conv.to(device))
         self.up = None
-        self.host_out = torch.empty(1024, dtype=torch.float32).pin_memory()
+        # two pinned result buffers: a step's result is read on the host while the next step is already queued
+        self.host_out = [torch.empty(1024, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self.pending, self.last_value, self.nstep = None, None, 0
         self.h2d = self.h1.numel() * 4 + self.h2.numel() * 4
         self.d2h = 0
 
@@ -533,7 +535,9 @@ class E2E:
         across micro-batches as autograd does for any repeated use).  With `prefetch` the copy of the NEXT step's
         first micro-batch is issued while this step's last one computes, as an input pipeline does; every step still
         copies all of its inputs from pinned host memory inside the timed region (the step after the last timed one
-        gets its first micro-batch copied there too, unused)."""
+        gets its first micro-batch copied there too, unused).  The step's result travels to pinned host memory with an
+        asynchronous copy and is read on the host once the NEXT step has been queued (drain() reads the last one), as a
+        training loop that logs its loss one step late does: the GPU never waits for the host between steps."""
         cfg, dev = self.cfg, self.device
         n = self.h1.shape[0]
         chunks = max(1, min(self.chunks, n))
@@ -564,6 +568,8 @@ class E2E:
         pieces, keep = [], []
         for (b0, b1), (f1, f2, ev) in zip(bounds, staged):
             main.wait_event(ev)
+            f1.record_stream(main)   # allocated on the copy stream, used (and later freed) under the main stream
+            f2.record_stream(main)
             if cfg["bwd"]:
                 f1.requires_grad_(True)
                 f2.requires_grad_(True)
@@ -598,12 +604,26 @@ class E2E:
             if flat is not None:
                 pieces.append(flat[:1000])
         res = torch.cat(pieces)
-        self.host_out[:res.numel()].copy_(res, non_blocking=True)
+        k = self.nstep & 1
+        self.nstep += 1
+        self.host_out[k][:res.numel()].copy_(res, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(main)
         self.d2h = res.numel() * 4
         if self.prefetch:
             self.prefetched = stage(*bounds[0])
-        main.synchronize()
-        return float(self.host_out[0])
+        self.drain()                    # the PREVIOUS step's result (this step is queued behind it)
+        self.pending = (done, k)
+        return self.last_value
+
+    def drain(self):
+        """Waits for the result of the last step whose result has not been read yet and reads it."""
+        if self.pending is not None:
+            ev, k = self.pending
+            ev.synchronize()
+            self.last_value = float(self.host_out[k][0])
+            self.pending = None
+        return self.last_value
 
 
 # --------------------------------------------------------------------------------------- CPU baseline
@@ -1075,6 +1095,7 @@ def main():
                      prefetch=not args.no_e2e_prefetch, f2_from_rank0=f2_from_rank0)
         for _ in range(min(args.warmup, 3)):   # warm-up runs the same pipeline (allocator steady state)
             runner.step()
+        runner.drain()
         per_step, host = [], []
         for _ in range(regions):
             barrier()
@@ -1084,6 +1105,7 @@ def main():
             for i in range(steps):
                 runner.prefetch = (not args.no_e2e_prefetch) and i < steps - 1   # the last step has no successor
                 runner.step()
+            runner.drain()   # the last step's result is read inside the timed region as well
             e1.record()
             host.append((time.perf_counter() - t0) / steps * 1e3)
             barrier()
@@ -1109,7 +1131,8 @@ def main():
                        + ".  What returns to the host every step: the two feature-gradient checksums of each micro-batch "
                          "and the summed attention-parameter gradients; the separated volumes and the feature gradients "
                          "stay on the device, where the model's next layers (cost aggregation, encoder backward) "
-                         "consume them")
+                         "consume them; the host reads a step's result (asynchronous copy to pinned memory) after it has "
+                         "queued the next step, and the last one before the timed region ends")
 
     extras = {}
     if not args.no_extras and args.config == 5 and args.batch == 0 and path == "level":
