@@ -234,6 +234,16 @@ __global__ void pack_interleaved_cf_kernel(const SlotSources src, float4* __rest
                                            int Qtot, int q0) {
   const int p = blockIdx.x * 256 + threadIdx.x, d0 = blockIdx.y * PI_DB, b = blockIdx.z;
   if (p >= n1p) return;
+  // per slot: the factor its values are multiplied by (0 = raw 32-bit copy): host scale times device scale
+  float fac[Q][4];
+#pragma unroll
+  for (int q = 0; q < Q; ++q)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const SlotSource& ss = src.s[4 * q + j];
+      fac[q][j] = ss.scale;
+      if (ss.dev != 0 && ss.src != nullptr) fac[q][j] = (ss.scale != 0.f ? ss.scale : 1.f) * __ldg(src.dev_scales + ss.dev - 1);
+    }
   uint32_t w[PI_DB][Q][4];
 #pragma unroll
   for (int i = 0; i < PI_DB; ++i)
@@ -257,8 +267,7 @@ __global__ void pack_interleaved_cf_kernel(const SlotSources src, float4* __rest
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const SlotSource& ss = src.s[4 * q + j];
-        v[j] = (ss.scale != 0.f && ss.src != nullptr) ? __uint_as_float(w[i][q][j]) * ss.scale : __uint_as_float(w[i][q][j]);
-        if (ss.dev != 0 && ss.src != nullptr) v[j] *= __ldg(src.dev_scales + ss.dev - 1);
+        v[j] = (fac[q][j] != 0.f && ss.src != nullptr) ? __uint_as_float(w[i][q][j]) * fac[q][j] : __uint_as_float(w[i][q][j]);
       }
       dst[(((size_t)b * D + d0 + i) * Qtot + q0 + q) * n1p + p] = make_float4(v[0], v[1], v[2], v[3]);
     }
