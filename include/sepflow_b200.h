@@ -290,7 +290,8 @@ int sfb_lookup4d_backward(const float* F1, const float* const* F2_levels, const 
  *   SFB_OPERANDS_TF32: rounded to TF32 (round to nearest), no scaling.
  *   SFB_OPERANDS_BF16: rounded to BF16 (8 mantissa bits; needs C % 8 == 0): the operand type BASELINE's bf16
  *     configuration asks for; gradients are then accurate to about 3e-3 instead of 3e-4.
- * The reference computes in FP32 only.  The setting is process-wide (a backward runs on another thread than the
+ * The reference computes in FP32 only.  The initial setting can be chosen with SFB_OPERANDS=tf32|bf16|fp16 in the
+ * environment.  The setting is process-wide (a backward runs on another thread than the
  * forward); sfb_set_sweep_operands returns the previous value, or -1 for an unknown one.  sfb_max_avg_forward_static,
  * sfb_corr_volume and the lookups always compute with TF32 / FP32 as documented at their declarations. */
 enum { SFB_OPERANDS_TF32 = 0, SFB_OPERANDS_BF16 = 1, SFB_OPERANDS_FP16 = 2 };

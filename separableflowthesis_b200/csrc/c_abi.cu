@@ -2,6 +2,7 @@
 // map encoding and the launch sequence of each op.  No torch types, no allocation.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <mutex>
@@ -189,7 +190,15 @@ void drain_timing_locked() {
 
 // Operand type of the contractions (sfb_set_sweep_operands): FP16 (default), TF32 or BF16.  Process-wide, because
 // a backward runs on an autograd worker thread, not on the thread that chose the precision.
-std::atomic<int> g_sweep_operands{SFB_OPERANDS_FP16};
+int initial_operands() {  // SFB_OPERANDS=tf32|bf16|fp16 in the environment chooses the initial setting
+  const char* e = getenv("SFB_OPERANDS");
+  if (e != nullptr) {
+    if (strcmp(e, "tf32") == 0) return SFB_OPERANDS_TF32;
+    if (strcmp(e, "bf16") == 0) return SFB_OPERANDS_BF16;
+  }
+  return SFB_OPERANDS_FP16;
+}
+std::atomic<int> g_sweep_operands{initial_operands()};
 
 // Test hook (sfb_debug_wait_timeout): time limit handed to the kernels' bounded waits and whether the next sweeps
 // leave out their last load.  Process-wide; 0 / 0 = normal operation.

@@ -498,7 +498,7 @@ def test_separation_level_with_bf16_sweep_operands(shape, cuda_device):
         g_sep_u = torch.randn(fw[0].shape, generator=g).to(dev)
         g_sep_v = torch.randn(fw[1].shape, generator=g).to(dev)
         bw = ops.separation_level_backward(F1d, F2d, wu, wv, *fw, g_sep_u, g_sep_v)
-    assert _lib_operands() == before == 2                         # restored to the default, FP16
+    assert _lib_operands() == before                              # restored
     F1b, F2b = F1.bfloat16().double(), F2.bfloat16().double()
     ref = orc.separation_level_forward(F1b, F2b, *[t.double() for t in params])
     assert relerr(fw[0][:, 0], ref[0][:, 0]) < 2e-5 and relerr(fw[1][:, 0], ref[1][:, 0]) < 2e-5
