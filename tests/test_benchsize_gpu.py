@@ -229,3 +229,27 @@ def test_five_ops_with_tf32_and_fp16_operands_agree(cuda_device):
         for got, ref in ((ma[:2], r_ma[:2]), (c, r_c), (mb, r_mb), (cb, r_cb), (sb, r_sb)):
             for x, r in zip(got, ref):
                 assert relerr(x, r) < TOL, kind
+
+
+def test_fp16_operand_scaling_edge_cases(cuda_device):
+    """Inputs that give the scale search nothing to work with: all-zero features (largest magnitude 0: scale 1, every
+    output 0, the arg-max the lowest index as for any tie), and all-zero upstream gradients (every gradient exactly 0).
+    No NaN or Inf may come out of the scale arithmetic."""
+    dev = cuda_device
+    F1, F2, params, gu, gv = level_inputs(1, 9, 14, 64, 2, dev, seed=506)
+    wu, bu, wv, bv = params
+    with ops.sweep_operands("fp16"):
+        fw0 = ops.separation_level_forward(torch.zeros_like(F1), torch.zeros_like(F2), wu, bu, wv, bv)
+        assert all(torch.isfinite(t.float()).all() for t in fw0)
+        assert fw0[0][:, :2].abs().max().item() == 0.0 and fw0[1][:, :2].abs().max().item() == 0.0
+        assert fw0[2].abs().max().item() == 0 and fw0[3].abs().max().item() == 0
+        fw = ops.separation_level_forward(F1, F2, wu, bu, wv, bv)
+        bw0 = ops.separation_level_backward(F1, F2, wu, wv, *fw, torch.zeros_like(gu), torch.zeros_like(gv))
+        for t in bw0:
+            assert torch.isfinite(t).all() and t.abs().max().item() == 0.0
+        # one feature map zero, the other not: S = 0 everywhere, gradients flow only to the zero map
+        bwz = ops.separation_level_backward(torch.zeros_like(F1), F2, wu, wv,
+                                            *ops.separation_level_forward(torch.zeros_like(F1), F2, wu, bu, wv, bv), gu, gv)
+        assert all(torch.isfinite(t).all() for t in bwz)
+        assert bwz[1].abs().max().item() == 0.0      # gF2 = G^T * F1 with F1 = 0
+        assert bwz[0].abs().max().item() > 0.0       # gF1 = G * F2
