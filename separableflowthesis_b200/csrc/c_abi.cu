@@ -220,7 +220,7 @@ struct Workspace {
   float* F1r;
   float* F2r;
   float* aux;
-  uint16_t* F1h;  // BF16 copies of the three arrays above (operands of the BF16 sweeps)
+  uint16_t* F1h;  // 16-bit copies (FP16 or BF16) of the three arrays above: operands of the kind::f16 sweeps
   uint16_t* F2h;
   uint16_t* auxh;
   float* xu;   // packed inputs indexed by (u, slot, pixel): (B, H2, Rx, n1p)
@@ -420,7 +420,7 @@ const float* sweep_out_scale(const Workspace& w, int op16) {
   return op16 == OP16_FP16 ? w.scales + SCALE_INV_F1F2 : nullptr;
 }
 
-// Tensor maps of the sweeps' operands in a workspace: the rounded FP32 copies or their BF16 copies (aux may be null).
+// Tensor maps of the sweeps' operands in a workspace: the rounded FP32 copies or the 16-bit copies (aux may be null).
 int map_sweep_operands(const Dims& d, const Workspace& w, int op16, CUtensorMap* f1, CUtensorMap* f2, CUtensorMap* aux) {
   if (op16) {
     SFB_TRY(map_f1_rows(f1, d, w.F1h, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, true));
@@ -534,7 +534,7 @@ int run_grad_pair(const Dims& d, const Workspace& w, int mode, int R4, int accum
   // number of rows, so that a 2 x 16 block of the image is 32 consecutive values).  Rows and columns of padding must
   // read as zero: they meet the G values of cells outside the image.
   const uint32_t crows = (uint32_t)((d.C + KBLK - 1) / KBLK * KBLK);  // channel rows of one feature block
-  // a row of 32 K-values is 128 bytes of FP32 or 64 bytes of BF16: the swizzle span follows
+  // a row of 32 K-values is 128 bytes of FP32 or 64 bytes of a 16-bit type: the swizzle span follows
   const CUtensorMapSwizzle fswz = op16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   const size_t f2t_per_sample = (size_t)d.C * ((d.W2 + GG_VT - 1) / GG_VT) * w.h2p * GG_VT;
   if (!accumulate) {  // later passes over further channel chunks reuse the copies of the first
@@ -705,7 +705,7 @@ int sfb_max_avg_forward_static(const float* F1, const float* F2, float* MA_u, fl
   SFB_TRY(check_shape(shape, false, &d));
   SFB_CHECK_PTR(F1); SFB_CHECK_PTR(F2); SFB_CHECK_PTR(MA_u); SFB_CHECK_PTR(MA_v);
   WsPlan plan = plan_for(SFB_OP_MAX_AVG_FORWARD, d);
-  plan.bf16 = false;  // this entry point always computes with TF32 operands: no room is set aside for BF16 copies
+  plan.bf16 = false;  // this entry point always computes with TF32 operands: no room is set aside for 16-bit copies
   const size_t need = carve(d, nullptr, plan).bytes;
   if (need > STATIC_SCRATCH_BYTES)
     return fail(SFB_ERR_UNSUPPORTED_SHAPE,

@@ -175,7 +175,8 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t a_tmem, u
       : "memory");
 }
 
-// The same with BF16 operands (K = 16 per instruction), FP32 accumulate.
+// The same with 16-bit operands (kind::f16: BF16 or FP16 as the instruction descriptor says; K = 16 per instruction),
+// FP32 accumulate.
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
@@ -186,7 +187,7 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       : "memory");
 }
 
-// BF16 operands with A in tensor memory: M lanes x 16 BF16 values = 8 columns (two values per 32-bit column, the
+// 16-bit operands (kind::f16) with A in tensor memory: M lanes x 16 values = 8 columns (two values per 32-bit column, the
 // lower K index in the low half), B in shared memory.
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {

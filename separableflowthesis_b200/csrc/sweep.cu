@@ -90,8 +90,8 @@ __device__ void sweep_producer(SweepSmem& sm, const SweepArgs& a, const SweepSch
 // ---------------------------------------------------------------------------------- MMA issuer
 __device__ void sweep_mma(SweepSmem& sm, const SweepArgs& a, const SweepSched& sc) {
   constexpr uint32_t idesc_tf32 = make_idesc_tf32(TILE_M, SW_TILE_N, false, false);
-  const uint32_t idesc_bf16 = make_idesc_op16(a.op16, TILE_M, SW_TILE_N);  // BF16 or FP16 operands
-  const bool bf16 = a.op16 != 0;
+  const uint32_t idesc_16 = make_idesc_op16(a.op16, TILE_M, SW_TILE_N);  // BF16 or FP16 operands
+  const bool op16 = a.op16 != 0;
   if (!mbar_wait(&sm.f1_full, 0, &sm.ctl, a.status, DEV_TIMEOUT_MMA)) return;
   tc_fence_after();
   uint32_t it = 0;
@@ -106,10 +106,10 @@ __device__ void sweep_mma(SweepSmem& sm, const SweepArgs& a, const SweepSched& s
       tc_fence_after();
       const uint64_t adesc = make_smem_desc_sw128(smem_u32(sm.f1[kb]), 16, 1024);
       const uint64_t bdesc = make_smem_desc_sw128(smem_u32(sm.f2[s]), 16, 1024);
-      if (bf16) {
+      if (op16) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k)  // one instruction consumes K = 16 BF16 values = 32 bytes of each row
-          umma_bf16(d_tmem, desc_advance(adesc, k * 32), desc_advance(bdesc, k * 32), idesc_bf16, (kb | k) != 0);
+        for (int k = 0; k < 4; ++k)  // one instruction consumes K = 16 16-bit values = 32 bytes of each row
+          umma_bf16(d_tmem, desc_advance(adesc, k * 32), desc_advance(bdesc, k * 32), idesc_16, (kb | k) != 0);
       } else {
 #pragma unroll
         for (int k = 0; k < KBLK / 8; ++k)  // one instruction consumes K = 8 TF32 values = 32 bytes of each row
