@@ -683,6 +683,25 @@ def time_cpu(cfg, budget_s, steps=None, warmup=1):
 
 
 # --------------------------------------------------------------------------------------- main
+def resolve_path(args, cfg):
+    if args.path == "auto":
+        return "level" if cfg["Kc"] > 0 and not args.unfused else "ops"
+    return args.path
+
+
+def workload_config(args, cfg, world):
+    """The `config` object of the JSON line.  Both arms print the same one for the same flags: it names the workload and
+    how `--gpus N` partitions it, not which implementation ran (what a CPU arm actually timed is in its
+    `cpu_baseline.sample`)."""
+    import math
+    g_batch = math.gcd(cfg["B"], world) if args.shard == "batch" else 1
+    cells = float(cfg["B"]) * (cfg["H"] * cfg["W"]) ** 2
+    return {"workload": cfg["name"], "path": resolve_path(args, cfg), "cells_per_step": cells,
+            "flop_per_cell": flops_per_cell(cfg),
+            "sharding": f"batch x rows = {g_batch} x {world // g_batch}",
+            "l2": "inputs larger than L2" if args.config >= 3 else "inputs smaller than L2 (launch-bound case)"}
+
+
 OPERAND_CODES = {"tf32": 0, "bf16": 1, "fp16": 2}
 DTYPE_TEXT = {
     "fp16": "fp16 operands (10 mantissa bits like TF32; per-tensor power-of-two scaling; fp32 in HBM), fp32 accumulate",
@@ -931,7 +950,7 @@ def main():
         line = {"impl": "reference", "metric": metric, "value": base["value"], "unit": unit, "n_gpus": args.gpus,
                 "steps": n_steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": {"workload": cfg["name"], "timed": base["sample"]},
+                "data": "synthetic", "config": workload_config(args, cfg, max(world, args.gpus)),
                 "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -959,8 +978,7 @@ def main():
             dist.barrier()
             dist.destroy_process_group()
         return
-    if path == "auto":
-        path = "level" if cfg["Kc"] > 0 and not args.unfused else "ops"
+    path = resolve_path(args, cfg)
     if path == "level" and cfg["Kc"] == 0:
         raise SystemExit("--path level needs attention channels")
     job = make_job(cfg, shard, device, path)
@@ -1160,10 +1178,7 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": DTYPE_TEXT[args.operands],
         "data": "synthetic",
-        "config": {"workload": cfg["name"], "path": path, "cells_per_step": total_cells,
-                   "flop_per_cell": flops_per_cell(cfg),
-                   "sharding": f"batch x rows = {shard.g_batch} x {shard.g_rows}",
-                   "l2": "inputs larger than L2" if args.config >= 3 else "inputs smaller than L2 (launch-bound case)"},
+        "config": workload_config(args, cfg, world),
         "useful_tflops": value * flops_per_cell(cfg) / 1e12,
         "repeats": spread, "host_ms_per_step": host_ms_per_step,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps,
