@@ -122,3 +122,23 @@ def test_operand_switch(lib):
     assert lib.sfb_set_sweep_operands(7) == -1 and lib.sfb_get_sweep_operands() == 0
     assert lib.sfb_set_sweep_operands(1) == 0
     assert lib.sfb_set_sweep_operands(2) == 1 and lib.sfb_get_sweep_operands() == 2
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    """No CPU or PyTorch fallback: with the shared library out of reach, loading raises and says how to build it."""
+    import subprocess
+    import sys
+    code = (
+        "import separableflowthesis_b200._lib as L\n"
+        f"L.LIB_PATH = {str(tmp_path / 'absent' / 'libsepflow_b200.so')!r}\n"
+        "L._lib = None\n"
+        "try:\n"
+        "    L.load()\n"
+        "except RuntimeError as e:\n"
+        "    assert 'is missing' in str(e) and 'no CPU or PyTorch fallback' in str(e), str(e)\n"
+        "    print('raised')\n"
+    )
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.strip().endswith("raised")
