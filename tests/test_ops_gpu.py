@@ -478,6 +478,59 @@ def test_ops_from_a_fresh_thread(cuda_device):
         assert torch.equal(x, y)
 
 
+def test_two_threads_on_their_own_streams(cuda_device):
+    """Two host threads, each on its own CUDA stream, run the ops on different shapes at the same time (the
+    DataParallel / serving-worker pattern).  Workspaces are kept per (device, stream), so neither sees the other's
+    operand copies, scales or status word: every result equals the one the same call gives when it runs alone."""
+    import threading
+    shapes = [(2, 17, 23, 8, 11, 64, 5), (1, 9, 130, 9, 130, 40, 4)]
+
+    def run_all(job):
+        a, params, ups = job
+        fw = ops.separation_level_forward(a[0], a[1], *params)
+        bw = ops.separation_level_backward(a[0], a[1], params[0], params[2], *fw, *ups)
+        return list(ops.max_argmax_avg_forward(*a[:2])) + list(ops.compression_forward(*a[:4])) + \
+            list(ops.compression_backward(*a)) + list(fw) + list(bw)
+
+    jobs = []
+    for i, shape in enumerate(shapes):
+        B, H1, W1, H2, W2, C, Kc = shape
+        F1, F2, A_u, A_v, g = make_inputs(shape, 60 + i)
+        gC_u = torch.randn(B, H1, W1, Kc, H2, generator=g)
+        gC_v = torch.randn(B, H1, W1, Kc, W2, generator=g)
+        args = [t.to(cuda_device) for t in (F1, F2, A_u, A_v, gC_u, gC_v)]
+        # the level calls stage their Conv3d weights in one per-device constant array: each thread has its own weights
+        params = [t.to(cuda_device) for t in (torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(Kc, generator=g) * 0.1,
+                                              torch.randn(Kc, 2, 3, 3, 3, generator=g) * 0.3, torch.randn(Kc, generator=g) * 0.1)]
+        fw = ops.separation_level_forward(args[0], args[1], *params)
+        ups = [torch.randn(fw[0].shape, generator=g).to(cuda_device), torch.randn(fw[1].shape, generator=g).to(cuda_device)]
+        args = (args, params, ups)
+        alone = run_all(args)
+        jobs.append((args, alone))
+    torch.cuda.synchronize()
+    errors, mismatches = [], []
+
+    def work(i):
+        try:
+            args, alone = jobs[i]
+            stream = torch.cuda.Stream(device=cuda_device)
+            with torch.cuda.stream(stream):
+                for _ in range(6):
+                    out = run_all(args)
+                    stream.synchronize()
+                    mismatches.extend((i, j) for j, (x, y) in enumerate(zip(out, alone)) if not torch.equal(x, y))
+        except Exception as e:  # surfaced below
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert not mismatches, mismatches
+
+
 @pytest.mark.parametrize("shape", [(2, 11, 19, 9, 21, 104, 3), (1, 24, 40, 24, 40, 256, 2)])
 def test_separation_level_with_bf16_sweep_operands(shape, cuda_device):
     """BF16 operands in the sweeps of the level calls (BASELINE's bf16 configuration): products of BF16 values are
