@@ -72,15 +72,12 @@ def test_module_matches_the_ctypes_layer(memorysaver, cuda_device):
         memorysaver.max_avg_forward(F1.transpose(1, 2), F2)
 
 
-@pytest.mark.gpu
-def test_reference_call_site_runs_on_the_module(memorysaver, cuda_device, golden_dir):
-    """The drop-in: the reference's AlternateCorrBlockSepflow (core/corr.py:335-510) and its three autograd Functions
-    (libs/MemorySaver/functions/MemorySaver.py), imported unmodified, with this module in the place of
-    ``libs/MemorySaver/build/lib/MemorySaver``; outputs and gradients against the vectors its dense CorrBlock produced
-    (tests/golden/make_golden.py).  Kc = 2, as the stored case."""
+def _import_reference_block(memorysaver):
+    """The reference's AlternateCorrBlockSepflow, imported unmodified from a checkout, with `memorysaver` in the place
+    of ``libs/MemorySaver/build/lib/MemorySaver`` (functions/MemorySaver.py:3); None without a checkout."""
     ref_root = _reference_root()
     if ref_root is None:
-        pytest.skip("no checkout of the reference beside this repository (set SFB_REFERENCE_ROOT)")
+        return None
     for pkg in ("libs.MemorySaver.build", "libs.MemorySaver.build.lib", "libs.GANet.build", "libs.GANet.build.lib"):
         m = types.ModuleType(pkg)
         m.__path__ = []
@@ -95,6 +92,35 @@ def test_reference_call_site_runs_on_the_module(memorysaver, cuda_device, golden
         from core.corr import AlternateCorrBlockSepflow as RefBlock
     finally:
         del sys.path[:2]
+    return RefBlock
+
+
+def test_reference_call_site_reaches_the_module(memorysaver):
+    """CPU: the reference's call site and autograd Functions import with this module in the place of their own build
+    and hand it their tensors -- shown by the module's own input check answering (CPU tensors are refused exactly as
+    the reference's CHECK_INPUT refuses them, MemorySaver_cuda.cpp:6-8), for the training and the inference Function."""
+    RefBlock = _import_reference_block(memorysaver)
+    if RefBlock is None:
+        pytest.skip("no checkout of the reference beside this repository (set SFB_REFERENCE_ROOT)")
+    g = torch.Generator().manual_seed(0)
+    f1 = torch.randn(1, 16, 9, 11, generator=g)
+    f2 = torch.randn(1, 16, 9, 11, generator=g)
+    convs = tuple(torch.nn.Conv3d(2, 2, 3, padding=1) for _ in range(2))
+    for support_backward in (True, False):
+        blk = RefBlock(f1, f2, None, support_backward=support_backward)
+        with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+            blk(None, sep=True, attention_weights=convs)
+
+
+@pytest.mark.gpu
+def test_reference_call_site_runs_on_the_module(memorysaver, cuda_device, golden_dir):
+    """The drop-in: the reference's AlternateCorrBlockSepflow (core/corr.py:335-510) and its three autograd Functions
+    (libs/MemorySaver/functions/MemorySaver.py), imported unmodified, with this module in the place of
+    ``libs/MemorySaver/build/lib/MemorySaver``; outputs and gradients against the vectors its dense CorrBlock produced
+    (tests/golden/make_golden.py).  Kc = 2, as the stored case."""
+    RefBlock = _import_reference_block(memorysaver)
+    if RefBlock is None:
+        pytest.skip("no checkout of the reference beside this repository (set SFB_REFERENCE_ROOT)")
     z = np.load(os.path.join(golden_dir, "block_dense_b2_c16_9x11_k2.npz"))
     dev = cuda_device
     f1 = torch.from_numpy(z["f1"]).float().to(dev).requires_grad_(True)
